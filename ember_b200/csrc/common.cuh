@@ -1,0 +1,90 @@
+// Shared helpers of the sm_100a kernels: error reporting through a C ABI, dtype codes,
+// loads that widen to float, warp/block reductions with a fixed order.
+//
+// Every exported function is `extern "C" int ember_<name>(..., void* stream)`: it
+// validates its arguments on the host, launches on the given stream, and returns 0 or a
+// non-zero code with a message readable through ember_last_error().  Kernels never trap:
+// an index that is out of range is skipped and recorded in a device error word that the
+// host can poll.
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+
+#define EMBER_API extern "C" __attribute__((visibility("default")))
+
+enum EmberDType : int { EMBER_F32 = 0, EMBER_BF16 = 1 };
+
+// Device error word bits (set with atomicOr by kernels, read by the host after a sync).
+enum EmberDeviceError : int {
+    EMBER_ERR_TOKEN_RANGE = 1,   // a token id outside the vocabulary
+    EMBER_ERR_PAGE_RANGE = 2,    // a page id outside the pool
+    EMBER_ERR_WAIT_LIMIT = 4,    // a bounded wait on a barrier ran out
+};
+
+namespace ember {
+
+inline char* error_buffer() {
+    static thread_local char buf[512] = {0};
+    return buf;
+}
+
+inline int fail(const char* fmt, ...) {
+    va_list ap;
+    va_start(ap, fmt);
+    vsnprintf(error_buffer(), 512, fmt, ap);
+    va_end(ap);
+    return 1;
+}
+
+inline int check_launch(const char* what) {
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return fail("%s: %s", what, cudaGetErrorString(e));
+    return 0;
+}
+
+__device__ __forceinline__ float to_float(float x) { return x; }
+__device__ __forceinline__ float to_float(__nv_bfloat16 x) { return __bfloat162float(x); }
+
+template <typename T>
+__device__ __forceinline__ T from_float(float x);
+template <>
+__device__ __forceinline__ float from_float<float>(float x) { return x; }
+template <>
+__device__ __forceinline__ __nv_bfloat16 from_float<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over a block of up to 1024 threads; the order of additions is fixed by the
+// thread layout, so the result does not depend on anything but the inputs.
+__device__ __forceinline__ float block_sum(float v, float* scratch /* >= 32 floats */) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    const int nwarps = (blockDim.x + 31) >> 5;
+    float r = (lane < nwarps) ? scratch[lane] : 0.0f;
+    r = warp_sum(r);
+    return r;
+}
+
+}  // namespace ember
+
+// Each shared library exports its own copy of the message reader.
+#define EMBER_DEFINE_LAST_ERROR \
+    EMBER_API const char* ember_last_error() { return ember::error_buffer(); }

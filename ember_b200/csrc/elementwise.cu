@@ -1,0 +1,206 @@
+// Embedding gather, RMSNorm, and the fused per-head norm + rotation + cache write.
+//
+// Reference formulas: src/backend/cpu/cpu_backend.cpp:34-39 (RMSNorm), :131-135 (embedding),
+// :156-172 (q/k norm, rotation, cache write), :263-272 (rotate-half).  The reference's own CUDA
+// counterparts are src/backend/cuda/k_elementwise.cu:45-126; these kernels are written for
+// sm_100a from the formulas and differ in layout: any head size up to 256 (even), partial
+// rotation, bf16 or fp32 activations and cache, pages of any size.
+#include "common.cuh"
+
+EMBER_DEFINE_LAST_ERROR
+
+namespace ember {
+
+// ------------------------------------------------------------------------------ embedding
+// h[t, :] = float(table[tokens[t], :]); no scaling.
+template <typename TW>
+__global__ void embed_kernel(const int* __restrict__ tokens, const TW* __restrict__ table,
+                             float* __restrict__ out, int H, int V, int* __restrict__ err) {
+    const int t = blockIdx.x;
+    const int tok = tokens[t];
+    float* o = out + (size_t)t * H;
+    if (tok < 0 || tok >= V) {
+        if (threadIdx.x == 0 && err) atomicOr(err, EMBER_ERR_TOKEN_RANGE);
+        for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = 0.0f;
+        return;
+    }
+    const TW* row = table + (size_t)tok * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = to_float(row[i]);
+}
+
+// -------------------------------------------------------------------------------- RMSNorm
+// out[r, i] = w[i] * (x[row(r), i] * (1 / sqrt(mean(x^2) + eps))), statistics in fp32.
+// `rows` (nullable) gathers input rows: the final norm runs only on the rows whose logits
+// are wanted.
+template <typename TO>
+__global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restrict__ rows,
+                               const float* __restrict__ w, float eps, TO* __restrict__ out, int H) {
+    __shared__ float scratch[32];
+    const int r = blockIdx.x;
+    const float* in = x + (size_t)(rows ? rows[r] : r) * H;
+    float ss = 0.0f;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) {
+        float v = in[i];
+        ss = fmaf(v, v, ss);
+    }
+    ss = block_sum(ss, scratch);
+    const float scale = 1.0f / sqrtf(ss / (float)H + eps);
+    TO* o = out + (size_t)r * H;
+    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = from_float<TO>(w[i] * (in[i] * scale));
+}
+
+// ------------------------------------------------- per-head norm + rotation + cache write
+// One warp per (token, head slot); slots are the query heads, then the key heads, then the
+// value heads of the fused projection row [q | k | v].
+//   q, k: optional RMSNorm over the head (weight shared by all heads), then rotate-half over
+//         the first `rotary` elements with angle = float(pos) * inv_freq[i] in fp32.
+//   q -> q_out[t, head, :];  k, v -> page bt[seq][pos / page], slot pos % page of the pools,
+//   layout [page][kv_head][slot][D].
+template <typename T>
+__global__ void qk_norm_rope_store_kernel(
+    const T* __restrict__ qkv, int ld, int n_heads, int n_kv, int D,
+    const float* __restrict__ q_norm_w, const float* __restrict__ k_norm_w, float eps,
+    const float* __restrict__ inv_freq, int rotary,
+    const int* __restrict__ positions, const int* __restrict__ seq_of,
+    const int* __restrict__ block_table, int max_blocks, int page, int num_pages,
+    T* __restrict__ q_out, T* __restrict__ k_pool, T* __restrict__ v_pool, int write_kv,
+    int* __restrict__ err) {
+    extern __shared__ float smem[];
+    const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x;
+    const int slot = blockIdx.y * warps + warp;
+    const int slots = n_heads + 2 * n_kv;
+    if (slot >= slots) return;
+    float* s = smem + (size_t)warp * D;
+
+    const int kind = slot < n_heads ? 0 : (slot < n_heads + n_kv ? 1 : 2);  // q, k, v
+    if (kind != 0 && !write_kv) return;
+    const T* src = qkv + (size_t)t * ld + (size_t)slot * D;
+
+    float ss = 0.0f;
+    for (int i = lane; i < D; i += 32) {
+        float v = to_float(src[i]);
+        s[i] = v;
+        ss = fmaf(v, v, ss);
+    }
+    const float* nw = kind == 0 ? q_norm_w : (kind == 1 ? k_norm_w : nullptr);
+    if (nw) {
+        ss = warp_sum(ss);
+        const float scale = 1.0f / sqrtf(ss / (float)D + eps);
+        for (int i = lane; i < D; i += 32) s[i] = nw[i] * (s[i] * scale);
+    }
+    __syncwarp();
+    const int pos = positions[t];
+    if (kind != 2 && inv_freq && rotary > 0) {
+        const int half = rotary >> 1;
+        for (int i = lane; i < half; i += 32) {
+            float sn, cs;
+            sincosf((float)pos * inv_freq[i], &sn, &cs);
+            const float a = s[i], b = s[i + half];
+            s[i] = a * cs - b * sn;
+            s[i + half] = b * cs + a * sn;
+        }
+        __syncwarp();
+    }
+    if (kind == 0) {
+        T* dst = q_out + ((size_t)t * n_heads + slot) * D;
+        for (int i = lane; i < D; i += 32) dst[i] = from_float<T>(s[i]);
+        return;
+    }
+    const int kvh = kind == 1 ? slot - n_heads : slot - n_heads - n_kv;
+    const int blk = block_table[(size_t)seq_of[t] * max_blocks + pos / page];
+    if (blk < 0 || blk >= num_pages) {
+        if (lane == 0 && err) atomicOr(err, EMBER_ERR_PAGE_RANGE);
+        return;
+    }
+    T* pool = kind == 1 ? k_pool : v_pool;
+    T* dst = pool + (((size_t)blk * n_kv + kvh) * page + (pos % page)) * D;
+    for (int i = lane; i < D; i += 32) dst[i] = from_float<T>(s[i]);
+}
+
+// out[m, j] = silu(x[m, 2j]) * x[m, 2j+1] for an unfused gate/up product (interleaved rows).
+template <typename T>
+__global__ void silu_mul_interleaved_kernel(const T* __restrict__ x, T* __restrict__ out, size_t n_out) {
+    size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_out) return;
+    const float g = to_float(x[2 * i]), u = to_float(x[2 * i + 1]);
+    out[i] = from_float<T>(g / (1.0f + expf(-g)) * u);
+}
+
+}  // namespace ember
+
+using namespace ember;
+
+EMBER_API int ember_embed(const int* tokens, const void* table, int table_dtype, float* out, int T, int H, int V,
+                          int* err, void* stream) {
+    if (T <= 0) return 0;
+    if (H <= 0 || V <= 0) return fail("embed: bad sizes H=%d V=%d", H, V);
+    cudaStream_t st = (cudaStream_t)stream;
+    const int threads = H >= 1024 ? 256 : 128;
+    if (table_dtype == EMBER_F32)
+        embed_kernel<float><<<T, threads, 0, st>>>(tokens, (const float*)table, out, H, V, err);
+    else if (table_dtype == EMBER_BF16)
+        embed_kernel<__nv_bfloat16><<<T, threads, 0, st>>>(tokens, (const __nv_bfloat16*)table, out, H, V, err);
+    else
+        return fail("embed: unsupported table dtype %d", table_dtype);
+    return check_launch("embed");
+}
+
+EMBER_API int ember_rmsnorm(const float* x, const int* rows, const float* w, float eps, void* out, int out_dtype,
+                            int n_rows, int H, void* stream) {
+    if (n_rows <= 0) return 0;
+    if (H <= 0) return fail("rmsnorm: bad width %d", H);
+    cudaStream_t st = (cudaStream_t)stream;
+    const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+    if (out_dtype == EMBER_F32)
+        rmsnorm_kernel<float><<<n_rows, threads, 0, st>>>(x, rows, w, eps, (float*)out, H);
+    else if (out_dtype == EMBER_BF16)
+        rmsnorm_kernel<__nv_bfloat16><<<n_rows, threads, 0, st>>>(x, rows, w, eps, (__nv_bfloat16*)out, H);
+    else
+        return fail("rmsnorm: unsupported output dtype %d", out_dtype);
+    return check_launch("rmsnorm");
+}
+
+EMBER_API int ember_qk_norm_rope_store(const void* qkv, int dtype, int T, int ld, int n_heads, int n_kv, int D,
+                                       const float* q_norm_w, const float* k_norm_w, float eps,
+                                       const float* inv_freq, int rotary, const int* positions, const int* seq_of,
+                                       const int* block_table, int max_blocks, int page, int num_pages,
+                                       void* q_out, void* k_pool, void* v_pool, int write_kv, int* err,
+                                       void* stream) {
+    if (T <= 0) return 0;
+    if (D <= 0 || D > 256 || (D & 1)) return fail("qk_norm_rope_store: head size %d is not an even number up to 256", D);
+    if (rotary < 0 || rotary > D || (rotary & 1)) return fail("qk_norm_rope_store: rotary size %d does not fit head size %d", rotary, D);
+    if (n_heads <= 0 || n_kv <= 0) return fail("qk_norm_rope_store: bad head counts %d/%d", n_heads, n_kv);
+    if (ld < (n_heads + 2 * n_kv) * D) return fail("qk_norm_rope_store: row stride %d is too small", ld);
+    if (page <= 0 || max_blocks <= 0 || num_pages <= 0) return fail("qk_norm_rope_store: bad cache geometry");
+    cudaStream_t st = (cudaStream_t)stream;
+    const int slots = n_heads + 2 * n_kv;
+    const int warps = slots < 8 ? slots : 8;
+    dim3 grid(T, (slots + warps - 1) / warps);
+    const size_t smem = (size_t)warps * D * sizeof(float);
+    if (dtype == EMBER_F32)
+        qk_norm_rope_store_kernel<float><<<grid, warps * 32, smem, st>>>(
+            (const float*)qkv, ld, n_heads, n_kv, D, q_norm_w, k_norm_w, eps, inv_freq, rotary, positions, seq_of,
+            block_table, max_blocks, page, num_pages, (float*)q_out, (float*)k_pool, (float*)v_pool, write_kv, err);
+    else if (dtype == EMBER_BF16)
+        qk_norm_rope_store_kernel<__nv_bfloat16><<<grid, warps * 32, smem, st>>>(
+            (const __nv_bfloat16*)qkv, ld, n_heads, n_kv, D, q_norm_w, k_norm_w, eps, inv_freq, rotary, positions,
+            seq_of, block_table, max_blocks, page, num_pages, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool,
+            (__nv_bfloat16*)v_pool, write_kv, err);
+    else
+        return fail("qk_norm_rope_store: unsupported dtype %d", dtype);
+    return check_launch("qk_norm_rope_store");
+}
+
+EMBER_API int ember_silu_mul_interleaved(const void* x, void* out, int dtype, long long n_out, void* stream) {
+    if (n_out <= 0) return 0;
+    cudaStream_t st = (cudaStream_t)stream;
+    const unsigned blocks = (unsigned)((n_out + 255) / 256);
+    if (dtype == EMBER_F32)
+        silu_mul_interleaved_kernel<float><<<blocks, 256, 0, st>>>((const float*)x, (float*)out, (size_t)n_out);
+    else if (dtype == EMBER_BF16)
+        silu_mul_interleaved_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)out, (size_t)n_out);
+    else
+        return fail("silu_mul: unsupported dtype %d", dtype);
+    return check_launch("silu_mul");
+}

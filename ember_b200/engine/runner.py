@@ -1,0 +1,113 @@
+"""The step function: one model, its cache, and ``step(entries) -> logits``.
+
+``ModelRunner`` is what generation, the benchmark and trace replay all drive.  A step runs
+only the tokens it is given, as one batch, against what earlier steps left in the cache, and
+returns fp32 logits at the wanted places (the reference's contract:
+src/backend/backend.hpp:104-117).  Pages for the new tokens are taken from the cache manager
+before the step (``reserve``) and given back by ``release``.
+"""
+from __future__ import annotations
+
+import os
+from typing import Hashable, List, Optional, Sequence
+
+import torch
+
+from ..cache.manager import CacheManager
+from ..cache.storage import CacheStorage
+from ..config.registry import load_config
+from ..config.spec import ModelSpec
+from ..model.causal_lm import CausalLM
+from ..parts.base import Runtime
+from ..weights.loader import WeightStore
+from .batch import BatchError, StepBatch, StepContext, StepEntry, Workspace, build_batch
+
+_DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
+           "f32": torch.float32}
+
+
+def parse_dtype(name) -> torch.dtype:
+    if isinstance(name, torch.dtype):
+        if name not in (torch.bfloat16, torch.float32):
+            raise ValueError(f"dtype must be bfloat16 or float32, got {name}")
+        return name
+    try:
+        return _DTYPES[str(name).lower()]
+    except KeyError:
+        raise ValueError(f"dtype must be bfloat16 or float32, got {name!r}") from None
+
+
+class DeviceError(RuntimeError):
+    pass
+
+
+class ModelRunner:
+    def __init__(self, spec: ModelSpec, store: WeightStore, dtype="bfloat16", device="cuda:0",
+                 capacity_tokens: int = 4096, max_batch_tokens: int = 2048, max_requests: int = 64,
+                 page_tokens: int = 16):
+        if not torch.cuda.is_available():
+            raise DeviceError("no CUDA device: this engine runs its model on a B200 only (there is no CPU path)")
+        self.device = torch.device(device)
+        torch.cuda.set_device(self.device)
+        self.spec = spec
+        self.dtype = parse_dtype(dtype)
+        self.rt = Runtime(device=self.device, dtype=self.dtype, page_tokens=page_tokens)
+        self.max_batch_tokens = int(max_batch_tokens)
+        self.max_requests = int(max_requests)
+        self.model = CausalLM(spec).load(store, self.rt)
+        self.cache = CacheManager(self.model.cache_needs(), page_tokens, int(capacity_tokens), self.max_requests)
+        self.storage = CacheStorage(self.cache, self.device, self.dtype)
+        self.workspace = Workspace(self.device)
+        self.err = torch.zeros(1, dtype=torch.int32, device=self.device)
+        self.steps = 0
+
+    # -------------------------------------------------------------- constructors
+    @classmethod
+    def from_dir(cls, model_dir: str, **kw) -> "ModelRunner":
+        """The model class is chosen by config.json's architecture, as everywhere."""
+        cfg = load_config(model_dir)
+        return cls(cfg.to_model_spec(), WeightStore.from_dir(model_dir), **kw)
+
+    # ------------------------------------------------------------------ requests
+    def admit(self, request: Hashable) -> bool:
+        rc = self.cache.admit(request)
+        if rc is None:
+            return False
+        self.storage.reset_slot(rc.slot)
+        return True
+
+    def reserve(self, request: Hashable, new_tokens: int) -> bool:
+        """Pages for ``new_tokens`` more tokens of the request; False if the pool cannot give them."""
+        return self.cache.ensure(request, self.cache.get(request).tokens + new_tokens)
+
+    def release(self, request: Hashable) -> None:
+        self.cache.release(request)
+
+    def cached_tokens(self, request: Hashable) -> int:
+        return self.cache.get(request).tokens
+
+    # ---------------------------------------------------------------------- step
+    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+        """Runs the entries as one batch; returns logits [wanted rows, vocab] fp32 on the device
+        (a view of a scratch buffer, valid until the next step), or None if nothing is wanted."""
+        batch = build_batch(entries, self.cache, self.spec.vocab_size, self.spec.max_positions)
+        return self.run_batch(batch)
+
+    def run_batch(self, batch: StepBatch) -> Optional[torch.Tensor]:
+        if batch.T > self.max_batch_tokens:
+            raise BatchError(f"the step has {batch.T} tokens; the limit is {self.max_batch_tokens}")
+        ctx = StepContext(batch, self.workspace, self.device, self.max_batch_tokens, err=self.err)
+        logits = self.model.forward(ctx, self.storage)
+        for s, req in enumerate(batch.requests):
+            self.cache.advance(req, int(batch.context_len[s]))
+        self.steps += 1
+        return logits
+
+    def check_device(self) -> None:
+        """Raises if a kernel recorded an out-of-range index (synchronises)."""
+        code = int(self.err.item())
+        if code:
+            self.err.zero_()
+            what = [n for b, n in ((1, "a token id outside the vocabulary"), (2, "a page id outside the pool"),
+                                   (4, "a bounded wait ran out")) if code & b]
+            raise DeviceError("a kernel reported: " + ", ".join(what))

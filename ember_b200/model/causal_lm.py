@@ -1,0 +1,85 @@
+"""A causal language model assembled from a ``ModelSpec``: embedding, blocks in schedule
+order, final norm, head.
+
+The model holds no sizes of its own.  ``forward`` runs exactly the tokens of the step's
+context against the cache and returns fp32 logits for the wanted rows (final norm and head run
+only on those rows, as in src/backend/cpu/cpu_backend.cpp:215-224).
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import torch
+
+from .. import ops
+from ..config.spec import ModelSpec
+from ..parts.base import CacheNeed, Runtime, WeightDecl
+from ..parts.linear import Linear
+from ..parts.registry import build_part, part_class
+from ..weights.loader import WeightStore
+
+
+class CausalLM:
+    def __init__(self, spec: ModelSpec):
+        self.spec = spec
+        self.blocks = [part_class("arrangement", ls.arrangement)(ls) for ls in spec.layers]
+        self.final_norm = build_part("norm", spec.final_norm, spec.final_norm_prefix)
+        self.rt: Optional[Runtime] = None
+
+    # ------------------------------------------------------------------ weights
+    def weight_decls(self) -> List[WeightDecl]:
+        s = self.spec
+        d = [WeightDecl(s.embedding_name, (s.vocab_size, s.hidden_size))]
+        if not s.tie_embeddings:
+            d.append(WeightDecl(s.head_name, (s.vocab_size, s.hidden_size), optional=s.head_optional))
+        d += self.final_norm.weight_decls()
+        for b in self.blocks:
+            d += b.weight_decls()
+        return d
+
+    def load(self, store: WeightStore, rt: Runtime) -> "CausalLM":
+        """Device copies of all weights; raises one ``WeightError`` listing every problem."""
+        s = self.spec
+        self.rt = rt
+        emb = store.take(s.embedding_name, (s.vocab_size, s.hidden_size))
+        self.embedding = rt.to_device(emb, rt.weight_dtype(emb.dtype)) if emb is not None else None
+        if s.tie_embeddings:
+            store.allow_unused(s.head_name)       # some files repeat the tied matrix
+            head = None
+        elif s.head_optional and not store.has(s.head_name):
+            head = None
+        else:
+            head = store.take(s.head_name, (s.vocab_size, s.hidden_size))
+        if self.embedding is not None:
+            self.head = Linear.from_host(head, rt) if head is not None else Linear(self.embedding)
+        self.final_norm.load(store, rt)
+        for b in self.blocks:
+            b.load(store, rt)
+        store.finish()
+        return self
+
+    # -------------------------------------------------------------------- cache
+    def cache_needs(self) -> Dict[int, Optional[CacheNeed]]:
+        """Need of every layer that owns a cache (a layer that only reads another's owns none)."""
+        owners = {(e.cache_of if e.cache_of >= 0 else e.layer) for e in self.spec.schedule}
+        return {l: self.blocks[l].mixer.cache_need() for l in sorted(owners)}
+
+    # ------------------------------------------------------------------ forward
+    def forward(self, ctx, storage) -> Optional[torch.Tensor]:
+        s, rt = self.spec, self.rt
+        h = ctx.buf("model.residual", (ctx.max_tokens, s.hidden_size), torch.float32)
+        ops.embed(ctx.tokens, self.embedding, h, err=ctx.err, stream=ctx.stream)
+        for e in s.schedule:
+            owner = e.cache_of if e.cache_of >= 0 else e.layer
+            self.blocks[e.layer].forward(ctx, h, storage.layer(owner), owns_cache=(owner == e.layer))
+        if ctx.R == 0:
+            return None
+        xn = ctx.buf_dyn("model.final_normed", ctx.R * s.hidden_size, rt.dtype).view(-1, s.hidden_size)
+        self.final_norm.forward(ctx, h, xn, ctx.R, rows=ctx.logit_rows)
+        logits = ctx.buf_dyn("model.logits", ctx.R * s.vocab_size, torch.float32).view(-1, s.vocab_size)
+        self.head(ctx, xn, logits, ctx.R, ops.EPI_STORE_F32)
+        return logits[:ctx.R]
+
+
+def build_model(spec: ModelSpec) -> CausalLM:
+    return CausalLM(spec)

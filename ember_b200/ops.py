@@ -1,0 +1,220 @@
+"""Python face of the CUDA kernels: argument checks, then a ctypes call on the current stream.
+
+There is no CPU fall-back and no library stand-in: every function raises ``KernelError`` if
+its tensors are not on a CUDA device or if the compiled library is missing or refuses the
+sizes.  Tensors are torch tensors used as typed device buffers.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import c_float, c_int, c_longlong, c_void_p
+from typing import Optional
+
+import torch
+
+from .csrc import build
+
+F32, BF16 = 0, 1
+EPI_STORE, EPI_STORE_F32, EPI_ADD_F32, EPI_SILU_MUL = 0, 1, 2, 3
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+def dtype_code(dt: torch.dtype) -> int:
+    if dt == torch.float32:
+        return F32
+    if dt == torch.bfloat16:
+        return BF16
+    raise KernelError(f"kernels take float32 or bfloat16 tensors, got {dt}")
+
+
+def _check(t: torch.Tensor, name: str, dtype=None) -> None:
+    if not t.is_cuda:
+        raise KernelError(f"{name} is on {t.device}; the kernels run on a CUDA device only (there is no CPU path)")
+    if not t.is_contiguous():
+        raise KernelError(f"{name} must be contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{name} must be {dtype}, got {t.dtype}")
+
+
+def _p(t: Optional[torch.Tensor]):
+    return c_void_p(t.data_ptr()) if t is not None else c_void_p(0)
+
+
+def current_stream_ptr() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+_libs = {}
+
+
+def _lib(name: str):
+    lib = _libs.get(name)
+    if lib is None:
+        try:
+            lib = build.load(name)
+        except (build.BuildError, OSError) as e:
+            raise KernelError(f"the CUDA kernel library '{name}' is not available: {e}") from e
+        _libs[name] = lib
+    return lib
+
+
+def _call(lib, fn, *args):
+    rc = fn(*args)
+    if rc != 0:
+        raise KernelError(lib.ember_last_error().decode("utf-8", "replace"))
+
+
+# ------------------------------------------------------------------------------ elementwise
+def embed(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor, err: Optional[torch.Tensor] = None,
+          stream: Optional[int] = None) -> None:
+    """out[t, :] = float(table[tokens[t], :])."""
+    _check(tokens, "tokens", torch.int32)
+    _check(table, "table")
+    _check(out, "out", torch.float32)
+    T, (V, H) = tokens.numel(), table.shape
+    if out.shape[-1] != H or out.numel() < T * H:
+        raise KernelError(f"embed: output {tuple(out.shape)} does not fit {T} rows of width {H}")
+    lib = _lib("elementwise")
+    _call(lib, lib.ember_embed, _p(tokens), _p(table), c_int(dtype_code(table.dtype)), _p(out), c_int(T), c_int(H),
+          c_int(V), _p(err), c_void_p(stream if stream is not None else current_stream_ptr()))
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor, n_rows: int,
+            rows: Optional[torch.Tensor] = None, stream: Optional[int] = None) -> None:
+    """out[r] = weight * x[rows[r] or r] * rsqrt(mean(x^2) + eps); x is fp32, statistics fp32."""
+    _check(x, "x", torch.float32)
+    _check(weight, "weight", torch.float32)
+    _check(out, "out")
+    H = x.shape[-1]
+    if weight.numel() != H or out.shape[-1] != H or out.numel() < n_rows * H:
+        raise KernelError(f"rmsnorm: width {H}, weight {tuple(weight.shape)}, out {tuple(out.shape)} for {n_rows} rows")
+    if rows is not None:
+        _check(rows, "rows", torch.int32)
+    lib = _lib("elementwise")
+    _call(lib, lib.ember_rmsnorm, _p(x), _p(rows), _p(weight), c_float(eps), _p(out), c_int(dtype_code(out.dtype)),
+          c_int(n_rows), c_int(H), c_void_p(stream if stream is not None else current_stream_ptr()))
+
+
+def qk_norm_rope_store(qkv: torch.Tensor, T: int, n_heads: int, n_kv: int, head_dim: int,
+                       q_norm_w: Optional[torch.Tensor], k_norm_w: Optional[torch.Tensor], eps: float,
+                       inv_freq: Optional[torch.Tensor], rotary: int, positions: torch.Tensor, seq_of: torch.Tensor,
+                       block_table: torch.Tensor, page: int, k_pool: torch.Tensor, v_pool: torch.Tensor,
+                       q_out: torch.Tensor, write_kv: bool = True, err: Optional[torch.Tensor] = None,
+                       stream: Optional[int] = None) -> None:
+    """Per head: optional RMSNorm, rotate-half rotation, q to ``q_out``, k/v into their pages."""
+    _check(qkv, "qkv")
+    _check(q_out, "q_out", qkv.dtype)
+    _check(k_pool, "k_pool", qkv.dtype)
+    _check(v_pool, "v_pool", qkv.dtype)
+    _check(positions, "positions", torch.int32)
+    _check(seq_of, "seq_of", torch.int32)
+    _check(block_table, "block_table", torch.int32)
+    for w, n in ((q_norm_w, "q_norm_w"), (k_norm_w, "k_norm_w"), (inv_freq, "inv_freq")):
+        if w is not None:
+            _check(w, n, torch.float32)
+    if k_pool.dim() != 4 or k_pool.shape[1] != n_kv or k_pool.shape[2] != page or k_pool.shape[3] != head_dim:
+        raise KernelError(f"qk_norm_rope_store: key pool {tuple(k_pool.shape)} is not [pages, {n_kv}, {page}, {head_dim}]")
+    if v_pool.shape != k_pool.shape:
+        raise KernelError("qk_norm_rope_store: key and value pools differ in shape")
+    if inv_freq is not None and inv_freq.numel() * 2 != rotary:
+        raise KernelError(f"qk_norm_rope_store: {inv_freq.numel()} frequencies for a rotation of {rotary}")
+    lib = _lib("elementwise")
+    _call(lib, lib.ember_qk_norm_rope_store, _p(qkv), c_int(dtype_code(qkv.dtype)), c_int(T), c_int(qkv.shape[-1]),
+          c_int(n_heads), c_int(n_kv), c_int(head_dim), _p(q_norm_w), _p(k_norm_w), c_float(eps), _p(inv_freq),
+          c_int(rotary if inv_freq is not None else 0), _p(positions), _p(seq_of), _p(block_table),
+          c_int(block_table.shape[-1]), c_int(page), c_int(k_pool.shape[0]), _p(q_out), _p(k_pool), _p(v_pool),
+          c_int(1 if write_kv else 0), _p(err), c_void_p(stream if stream is not None else current_stream_ptr()))
+
+
+def silu_mul_interleaved(x: torch.Tensor, out: torch.Tensor, n_out: int, stream: Optional[int] = None) -> None:
+    _check(x, "x")
+    _check(out, "out", x.dtype)
+    lib = _lib("elementwise")
+    _call(lib, lib.ember_silu_mul_interleaved, _p(x), _p(out), c_int(dtype_code(x.dtype)), c_longlong(n_out),
+          c_void_p(stream if stream is not None else current_stream_ptr()))
+
+
+# ------------------------------------------------------------------------------------ GEMM
+def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, M: int, epilogue: int = EPI_STORE,
+              bias: Optional[torch.Tensor] = None, stream: Optional[int] = None) -> None:
+    """out (+)= a[:M] @ w.T on the fp32 SIMT pipes (true 32-bit when both are float32)."""
+    _check(a, "a")
+    _check(w, "w")
+    _check(out, "out")
+    N, K = w.shape
+    if a.shape[-1] != K:
+        raise KernelError(f"gemm: activations of width {a.shape[-1]} against weights {tuple(w.shape)}")
+    n_out = N // 2 if epilogue == EPI_SILU_MUL else N
+    want = a.dtype if epilogue in (EPI_STORE, EPI_SILU_MUL) else torch.float32
+    if out.dtype != want:
+        raise KernelError(f"gemm: epilogue {epilogue} writes {want}, the output is {out.dtype}")
+    if out.shape[-1] != n_out or out.numel() < M * n_out or a.numel() < M * K:
+        raise KernelError(f"gemm: output {tuple(out.shape)} / input {tuple(a.shape)} do not fit M={M} N={n_out}")
+    if bias is not None:
+        _check(bias, "bias", torch.float32)
+        if bias.numel() != N:
+            raise KernelError(f"gemm: bias of {bias.numel()} for N={N}")
+    lib = _lib("gemm_simt")
+    _call(lib, lib.ember_gemm_simt, _p(a), c_int(dtype_code(a.dtype)), c_int(K), _p(w), c_int(dtype_code(w.dtype)),
+          c_int(K), _p(bias), _p(out), c_int(n_out), c_int(M), c_int(N), c_int(K), c_int(epilogue),
+          c_void_p(stream if stream is not None else current_stream_ptr()))
+
+
+# ------------------------------------------------------------------------------- attention
+def attention_tile_queries(group: int) -> int:
+    """How many query tokens one tile of the general attention kernel may hold."""
+    lib = _lib("attention")
+    n = lib.ember_attention_tile_queries(c_int(group))
+    if n <= 0:
+        raise KernelError(f"attention: {group} query heads per key/value head is more than the kernel takes")
+    return n
+
+
+def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: torch.Tensor, T: int,
+              n_heads: int, n_kv: int, head_dim: int, tiles: torch.Tensor, n_tiles: int, tile_q: int,
+              block_table: torch.Tensor, page: int, window: int, scale: float, n_splits: int = 1,
+              split_keys: int = 0, part_o: Optional[torch.Tensor] = None, part_ml: Optional[torch.Tensor] = None,
+              err: Optional[torch.Tensor] = None, stream: Optional[int] = None) -> None:
+    """Causal attention of the step's tokens over the paged cache (general SIMT kernel)."""
+    _check(q, "q")
+    _check(out, "out", q.dtype)
+    _check(k_pool, "k_pool", q.dtype)
+    _check(v_pool, "v_pool", q.dtype)
+    _check(tiles, "tiles", torch.int32)
+    _check(block_table, "block_table", torch.int32)
+    if k_pool.dim() != 4 or tuple(k_pool.shape[1:]) != (n_kv, page, head_dim) or v_pool.shape != k_pool.shape:
+        raise KernelError(f"attention: pools {tuple(k_pool.shape)} are not [pages, {n_kv}, {page}, {head_dim}]")
+    if q.numel() < T * n_heads * head_dim or out.numel() < T * n_heads * head_dim:
+        raise KernelError("attention: q/out too small for the step")
+    if n_splits > 1:
+        _check(part_o, "part_o", torch.float32)
+        _check(part_ml, "part_ml", torch.float32)
+        if part_o.numel() < T * n_heads * n_splits * head_dim or part_ml.numel() < T * n_heads * n_splits * 2:
+            raise KernelError("attention: split buffers too small")
+    lib = _lib("attention")
+    _call(lib, lib.ember_attention, _p(q), _p(k_pool), _p(v_pool), _p(out), c_int(dtype_code(q.dtype)), c_int(T),
+          c_int(n_heads), c_int(n_kv), c_int(head_dim), _p(tiles), c_int(n_tiles), c_int(tile_q), _p(block_table),
+          c_int(block_table.shape[-1]), c_int(page), c_int(k_pool.shape[0]), c_int(window), c_float(scale),
+          c_int(n_splits), c_int(split_keys), _p(part_o), _p(part_ml), _p(err),
+          c_void_p(stream if stream is not None else current_stream_ptr()))
+
+
+# ------------------------------------------------------------- tensor-core kernels (bf16)
+def gemm_tc_usable(x: torch.Tensor, w: torch.Tensor, bias, epilogue: int) -> bool:
+    """Whether the tcgen05 product takes these operands."""
+    return False
+
+
+def gemm_tc(linear, x, out, m, epilogue, stream=None) -> None:
+    raise KernelError("the tensor-core product is not built")
+
+
+def attention_tc_usable(dtype: torch.dtype, head_dim: int, group: int, page_tokens: int) -> bool:
+    return False
+
+
+def attention_tc(*args, **kw) -> None:
+    raise KernelError("the tensor-core attention is not built")

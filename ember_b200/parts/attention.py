@@ -1,0 +1,118 @@
+"""Grouped-query causal attention over a paged key/value cache.
+
+Order of operations (src/backend/cpu/cpu_backend.cpp:141-200): fused q/k/v projection (+bias),
+per-head RMSNorm of q and k, rotation of q and k, write of k and v to the request's pages,
+attention of every new token over keys 0..pos (or the last ``window`` keys), output projection
+added to the residual stream.  Sizes and constants come from ``AttentionSpec``.
+
+Device layout of the weights is this part's own: q, k and v rows are concatenated into one
+[q_dim + 2 kv_dim, hidden] matrix so the projection is one product.
+"""
+from __future__ import annotations
+
+import math
+from typing import List, Optional
+
+import torch
+
+from .. import ops
+from ..config.spec import ConfigError
+from .base import CacheNeed, Mixer, Runtime, WeightDecl
+from .linear import Linear
+from .registry import build_part, register_part
+
+
+class Attention(Mixer):
+    # keys per split and the most tokens in a step for which long key ranges are split
+    SPLIT_KEYS = 256
+    SPLIT_MAX_TOKENS = 256
+
+    def __init__(self, spec, prefix: str = ""):
+        super().__init__(spec, prefix)
+        s = spec
+        if s.num_heads <= 0 or s.num_kv_heads <= 0 or s.num_heads % s.num_kv_heads:
+            raise ConfigError(f"{s.num_heads} heads do not divide into {s.num_kv_heads} key/value heads")
+        if s.head_dim <= 0 or s.head_dim % 2 or s.head_dim > 256:
+            raise ConfigError(f"head_dim {s.head_dim} must be even and at most 256")
+        if s.window < 0:
+            raise ConfigError("window must be >= 0")
+        self.position = build_part("position", s.position)
+        self.scale = s.softmax_scale if s.softmax_scale is not None else 1.0 / math.sqrt(s.head_dim)
+
+    # ------------------------------------------------------------------ weights
+    def weight_decls(self) -> List[WeightDecl]:
+        s, p = self.spec, self.prefix
+        d = [WeightDecl(p + "q_proj.weight", (s.q_dim, s.hidden_size)),
+             WeightDecl(p + "k_proj.weight", (s.kv_dim, s.hidden_size)),
+             WeightDecl(p + "v_proj.weight", (s.kv_dim, s.hidden_size)),
+             WeightDecl(p + "o_proj.weight", (s.hidden_size, s.q_dim))]
+        if s.qk_norm:
+            d += [WeightDecl(p + "q_norm.weight", (s.head_dim,), init="norm"),
+                  WeightDecl(p + "k_norm.weight", (s.head_dim,), init="norm")]
+        if s.bias:
+            d += [WeightDecl(p + "q_proj.bias", (s.q_dim,), init="zeros"),
+                  WeightDecl(p + "k_proj.bias", (s.kv_dim,), init="zeros"),
+                  WeightDecl(p + "v_proj.bias", (s.kv_dim,), init="zeros")]
+        return d
+
+    def load(self, store, rt: Runtime) -> None:
+        s, p = self.spec, self.prefix
+        self.rt = rt
+        got = {d.name: store.take(d.name, d.shape) for d in self.weight_decls()}
+        if any(v is None for v in got.values()):
+            return  # the store reports what is missing
+        q, k, v = (got[p + n + "_proj.weight"] for n in "qkv")
+        wd = rt.weight_dtype(torch.result_type(q, k))
+        qkv = torch.cat([rt.to_device(t, wd) for t in (q, k, v)], dim=0)
+        bias = None
+        if s.bias:
+            bias = torch.cat([got[p + n + "_proj.bias"].float() for n in "qkv"]).to(rt.device)
+        self.qkv = Linear(qkv, bias)
+        self.o = Linear.from_host(got[p + "o_proj.weight"], rt)
+        self.q_norm_w = rt.to_device(got[p + "q_norm.weight"], torch.float32) if s.qk_norm else None
+        self.k_norm_w = rt.to_device(got[p + "k_norm.weight"], torch.float32) if s.qk_norm else None
+        self.inv_freq, self.rotary = self.position.rotary_table(rt)
+
+    # -------------------------------------------------------------------- cache
+    def cache_need(self) -> CacheNeed:
+        s = self.spec
+        return CacheNeed(kind="window" if s.window > 0 else "full", num_kv_heads=s.num_kv_heads,
+                         head_dim=s.head_dim, window=s.window)
+
+    # ------------------------------------------------------------------ forward
+    def forward(self, ctx, x: torch.Tensor, residual: torch.Tensor, cache, owns_cache: bool = True) -> None:
+        s, rt = self.spec, self.rt
+        T, mt = ctx.T, ctx.max_tokens
+        qkv = ctx.buf("attention.qkv", (mt, s.q_dim + 2 * s.kv_dim), rt.dtype)
+        q = ctx.buf("attention.q", (mt, s.q_dim), rt.dtype)
+        att = ctx.buf("attention.out", (mt, s.q_dim), rt.dtype)
+        self.qkv(ctx, x, qkv, T, ops.EPI_STORE)
+        table = ctx.block_table(cache.group)
+        ops.qk_norm_rope_store(qkv, T, s.num_heads, s.num_kv_heads, s.head_dim, self.q_norm_w, self.k_norm_w,
+                               s.qk_norm_eps, self.inv_freq, self.rotary, ctx.positions, ctx.seq_of, table,
+                               cache.page_tokens, cache.k, cache.v, q, write_kv=owns_cache, err=ctx.err,
+                               stream=ctx.stream)
+        self.attend(ctx, q, cache, table, att)
+        self.o(ctx, att, residual, T, ops.EPI_ADD_F32)
+
+    def attend(self, ctx, q: torch.Tensor, cache, table: torch.Tensor, out: torch.Tensor) -> None:
+        """out[t, h, :] = softmax over the visible keys of (q . k * scale) times v."""
+        s = self.spec
+        if ops.attention_tc_usable(q.dtype, s.head_dim, s.group, cache.page_tokens):
+            ops.attention_tc(ctx, q, cache, table, out, s.num_heads, s.num_kv_heads, s.head_dim, s.window, self.scale)
+            return
+        tile_q = ops.attention_tile_queries(s.group)
+        tiles, n_tiles = ctx.attention_tiles(tile_q)
+        # long key ranges of a small step are cut into fixed splits so that more SMs share them
+        span = ctx.max_context if s.window <= 0 else min(ctx.max_context, s.window + tile_q)
+        n_splits, part_o, part_ml = 1, None, None
+        if ctx.T <= self.SPLIT_MAX_TOKENS and span > 2 * self.SPLIT_KEYS:
+            n_splits = (ctx.max_context + self.SPLIT_KEYS - 1) // self.SPLIT_KEYS
+            part_o = ctx.buf_dyn("attention.part_o", ctx.T * s.num_heads * n_splits * s.head_dim, torch.float32)
+            part_ml = ctx.buf_dyn("attention.part_ml", ctx.T * s.num_heads * n_splits * 2, torch.float32)
+        ops.attention(q, cache.k, cache.v, out, ctx.T, s.num_heads, s.num_kv_heads, s.head_dim, tiles, n_tiles,
+                      tile_q, table, cache.page_tokens, s.window, self.scale, n_splits, self.SPLIT_KEYS,
+                      part_o, part_ml, err=ctx.err, stream=ctx.stream)
+
+
+register_part("mixer", "attention", Attention)

@@ -1,0 +1,125 @@
+"""What every part is: a spec, the tensors it declares, device copies, and a forward.
+
+A part is built from its spec alone (no device needed), so a model's tensor names and
+shapes can be listed — for loading, for the error that lists what is missing, and for the
+random-weights mode — before anything touches a GPU.  ``load`` makes the device copies.
+
+Interfaces (what a new part must provide):
+
+* ``Norm``:          ``forward(ctx, x_f32[rows, size], out[n_rows, size], n_rows, rows=None)``
+* ``PositionEncoding``: ``rotary_table(rt) -> (inv_freq_f32[rotary/2] | None, rotary_dim)``; encodings that
+  act elsewhere may instead override ``on_embedding(ctx, h)``.
+* ``Mixer``:         ``cache_need() -> CacheNeed | None`` and
+  ``forward(ctx, x[T, hidden], residual_f32[T, hidden], cache: LayerCache | None, owns_cache: bool)``;
+  it *adds* its result to ``residual``.
+* ``FeedForward``:   ``forward(ctx, x[T, hidden], residual_f32[T, hidden])``; it adds its result.
+
+No part knows which model it is in: sizes and constants come from its spec, weights from the
+names under the prefix it is given.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Optional, Sequence, Tuple
+
+import torch
+
+from ..config.spec import PartSpec
+
+
+@dataclass(frozen=True)
+class WeightDecl:
+    """A tensor a part reads: its full name, shape, and how the random-weights mode fills it."""
+
+    name: str
+    shape: Tuple[int, ...]
+    init: str = "linear"      # "linear": N(0, std) | "norm": 1 + N(0, norm_std) | "zeros"
+    optional: bool = False    # may be absent from the file (the part then does without)
+
+
+@dataclass(frozen=True)
+class CacheNeed:
+    """What a mixer asks of the cache manager, per layer.
+
+    kind "full":   pages holding every key/value of the request.
+    kind "window": pages holding the last ``window`` keys; older pages are given back.
+    kind "state":  no pages; one slot of ``state_shape`` elements of ``state_dtype`` per request.
+    Layers whose needs are equal share a group (one block table, one page pool per group).
+    """
+
+    kind: str
+    num_kv_heads: int = 0
+    head_dim: int = 0
+    window: int = 0
+    state_shape: Tuple[int, ...] = ()
+    state_dtype: str = "float32"
+
+
+@dataclass
+class Runtime:
+    """Where and how a model computes."""
+
+    device: torch.device
+    dtype: torch.dtype                 # activations and cache: torch.bfloat16 (serving) or torch.float32
+    page_tokens: int = 16
+
+    def weight_dtype(self, stored: torch.dtype) -> torch.dtype:
+        """Matrix weights: widened to float32 on the float32 path, stored precision kept otherwise."""
+        if self.dtype == torch.float32:
+            return torch.float32
+        return torch.float32 if stored == torch.float32 else torch.bfloat16
+
+    def to_device(self, t: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+        return t.to(device=self.device, dtype=dtype).contiguous()
+
+
+class Part:
+    family = ""
+
+    def __init__(self, spec: PartSpec, prefix: str = ""):
+        self.spec = spec
+        self.prefix = prefix
+
+    def weight_decls(self) -> List[WeightDecl]:
+        return []
+
+    def load(self, store, rt: Runtime) -> None:
+        """Takes the declared tensors from ``store`` and makes device copies."""
+
+    def workspace_need(self, max_tokens: int, rt: Runtime) -> None:
+        return None
+
+
+class Norm(Part):
+    family = "norm"
+
+    def forward(self, ctx, x: torch.Tensor, out: torch.Tensor, n_rows: int, rows: Optional[torch.Tensor] = None) -> None:
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    family = "position"
+
+    def rotary_table(self, rt: Runtime):
+        """(inv_freq float32 device tensor of rotary_dim/2, rotary_dim), or (None, 0) for no rotation."""
+        return None, 0
+
+    def on_embedding(self, ctx, h: torch.Tensor) -> None:
+        """Hook for encodings that are added to the embedded tokens; rotary ones do nothing here."""
+
+
+class Mixer(Part):
+    family = "mixer"
+
+    def cache_need(self) -> Optional[CacheNeed]:
+        return None
+
+    def forward(self, ctx, x: torch.Tensor, residual: torch.Tensor, cache, owns_cache: bool = True) -> None:
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    family = "feed_forward"
+
+    def forward(self, ctx, x: torch.Tensor, residual: torch.Tensor) -> None:
+        raise NotImplementedError

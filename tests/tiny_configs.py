@@ -1,0 +1,33 @@
+"""The tests' own tiny Qwen3 configurations.  They differ in every size and option: layers,
+width, heads and groups, head size, projection width vs model width, feed-forward width,
+vocabulary (one a power of two, one not), rope theta, norm eps, tied vs untied head, initial
+scales, position limit."""
+from __future__ import annotations
+
+import numpy as np
+
+from ember_b200.config import Qwen3Config
+
+TINY = {
+    "a": dict(seed=11, std=0.02, norm_std=0.05,
+              json=dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=512, hidden_size=64,
+                        intermediate_size=192, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                        head_dim=16, rope_theta=10000.0, rms_norm_eps=1e-6, tie_word_embeddings=True,
+                        max_position_embeddings=128, attention_bias=False)),
+    "b": dict(seed=23, std=0.03, norm_std=0.1,
+              json=dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=1000, hidden_size=96,
+                        intermediate_size=256, num_hidden_layers=3, num_attention_heads=6, num_key_value_heads=1,
+                        head_dim=32, rope_theta=1000000.0, rms_norm_eps=1e-5, tie_word_embeddings=False,
+                        max_position_embeddings=256, attention_bias=False)),
+}
+
+
+def tiny_config(name: str) -> Qwen3Config:
+    return Qwen3Config.from_json(TINY[name]["json"])
+
+
+def tiny_prompts(name: str):
+    rng = np.random.default_rng(1234 + ord(name))
+    vocab = TINY[name]["json"]["vocab_size"]
+    lengths = (5, 17, 33) if name == "a" else (1, 31, 64, 100)
+    return [rng.integers(0, vocab, size=n).tolist() for n in lengths]
