@@ -202,6 +202,20 @@ def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: 
           c_void_p(stream if stream is not None else current_stream_ptr()))
 
 
+# -------------------------------------------------------------------------------- sampling
+def sample(logits: torch.Tensor, params: torch.Tensor, out: torch.Tensor, rows: int,
+           stream: Optional[int] = None) -> None:
+    """out[r] = token drawn from logits[r] under the packed 32-byte parameter row r."""
+    _check(logits, "logits", torch.float32)
+    _check(params, "params", torch.uint8)
+    _check(out, "out", torch.int32)
+    if logits.dim() != 2 or logits.shape[0] < rows or params.numel() < rows * 32 or out.numel() < rows:
+        raise KernelError("sample: buffers do not fit the rows")
+    lib = _lib("sampling")
+    _call(lib, lib.ember_sample, _p(logits), c_int(rows), c_int(logits.shape[1]), _p(params), _p(out),
+          c_void_p(stream if stream is not None else current_stream_ptr()))
+
+
 # ------------------------------------------------------------- tensor-core kernels (bf16)
 def gemm_tc_usable(x: torch.Tensor, w: torch.Tensor, bias, epilogue: int) -> bool:
     """Whether the tcgen05 product takes these operands."""

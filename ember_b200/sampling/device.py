@@ -1,0 +1,35 @@
+"""Device sampler: one kernel launch for all rows of a step."""
+from __future__ import annotations
+
+import struct
+from typing import Optional, Sequence
+
+import numpy as np
+import torch
+
+from .. import ops
+from .params import SamplingParams
+
+_ROW = struct.Struct("<fiffQQ")   # temperature, top_k, top_p, min_p, seed, counter: 32 bytes
+
+
+def pack_params(params: Sequence[SamplingParams], counters: Sequence[int]) -> np.ndarray:
+    buf = bytearray(_ROW.size * len(params))
+    for i, (p, c) in enumerate(zip(params, counters)):
+        _ROW.pack_into(buf, i * _ROW.size, float(p.temperature), int(p.top_k), float(p.top_p), float(p.min_p),
+                       int(p.seed) & ((1 << 64) - 1), int(c) & ((1 << 64) - 1))
+    return np.frombuffer(bytes(buf), dtype=np.uint8)
+
+
+def sample(logits: torch.Tensor, params: Sequence[SamplingParams], counters: Sequence[int],
+           out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One token id per row of ``logits`` [rows, vocab] (fp32, device); returns int32 [rows] on the device."""
+    rows, vocab = logits.shape
+    if len(params) != rows or len(counters) != rows:
+        raise ops.KernelError(f"sample: {len(params)} parameter sets for {rows} rows")
+    host = torch.from_numpy(pack_params(params, counters).copy())
+    dev = host.to(logits.device, non_blocking=False)
+    if out is None:
+        out = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    ops.sample(logits, dev, out, rows)
+    return out
