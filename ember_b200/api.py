@@ -1,0 +1,82 @@
+"""The Python entry point: a model folder (or a configuration and a seed) to generated tokens.
+
+    import ember_b200
+    llm = ember_b200.load("path/to/model", dtype="bfloat16")
+    ids = llm.generate([1, 2, 3], max_tokens=16)                       # greedy by default
+    ids = llm.generate([[1, 2, 3], [4, 5]], sampling=ember_b200.SamplingParams(temperature=0.7, top_k=20))
+
+Option names and meanings are the reference's (src/backend/backend.hpp:39-53,
+src/engine/engine.hpp:77-84, tools/cli_args.hpp:57-88) where it has them.
+"""
+from __future__ import annotations
+
+import os
+import tempfile
+from typing import List, Optional, Sequence, Union
+
+import torch
+
+from .config.registry import load_config
+from .engine.engine import Engine
+from .engine.runner import ModelRunner
+from .sampling.params import SamplingParams
+from .weights.loader import WeightStore
+from .weights.random_init import random_tensors
+
+
+class LLM:
+    """A loaded model with its engine."""
+
+    def __init__(self, runner: ModelRunner, max_prefill_chunk: int = 512, max_context: Optional[int] = None):
+        self.runner = runner
+        self.engine = Engine(runner, max_prefill_chunk=max_prefill_chunk, max_context=max_context)
+
+    @property
+    def spec(self):
+        return self.runner.spec
+
+    def generate(self, prompts, sampling: Optional[SamplingParams] = None, max_tokens: int = 256,
+                 ignore_eos: bool = False, stop_tokens: Sequence[int] = ()):
+        """Token ids in (one prompt or a list of prompts), generated token ids out (host lists)."""
+        return self.engine.generate(prompts, sampling=sampling, max_tokens=max_tokens, ignore_eos=ignore_eos,
+                                    stop_tokens=stop_tokens)
+
+    def step(self, entries):
+        """The step function itself: ``[StepEntry(request, tokens, want)] -> logits`` (device, fp32)."""
+        return self.runner.step(entries)
+
+    @property
+    def stats(self):
+        return self.engine.stats
+
+
+def load(model: str, dtype: str = "bfloat16", device: str = "cuda:0", kv_cache_tokens: int = 0,
+         max_batch_tokens: int = 2048, max_seqs: int = 64, prefill_chunk: int = 512,
+         max_context: Optional[int] = None, page_tokens: int = 16) -> LLM:
+    """Loads a model folder (config.json + safetensors).  ``kv_cache_tokens`` 0 sizes the cache
+    for ``max_seqs`` requests of the model's position limit, capped at 262,144 tokens."""
+    cfg = load_config(model)
+    spec = cfg.to_model_spec()
+    if kv_cache_tokens <= 0:
+        kv_cache_tokens = min(max_seqs * spec.max_positions, 262144)
+    runner = ModelRunner(spec, WeightStore.from_dir(model), dtype=dtype, device=device,
+                         capacity_tokens=kv_cache_tokens, max_batch_tokens=max_batch_tokens,
+                         max_requests=max_seqs, page_tokens=page_tokens)
+    return LLM(runner, max_prefill_chunk=prefill_chunk, max_context=max_context)
+
+
+def load_random(config, seed: int = 0, dtype: str = "bfloat16", device: str = "cuda:0", kv_cache_tokens: int = 0,
+                max_batch_tokens: int = 2048, max_seqs: int = 64, prefill_chunk: int = 512,
+                max_context: Optional[int] = None, page_tokens: int = 16, weight_dtype=torch.bfloat16,
+                std: Optional[float] = None, norm_std: Optional[float] = None) -> LLM:
+    """Random-weights mode without a folder: the tensors are made from ``seed`` in memory
+    (on the device when it is a CUDA device) and loaded as if they came from a file."""
+    spec = config.to_model_spec()
+    gen_device = device if torch.cuda.is_available() else "cpu"
+    store = WeightStore.from_tensors(dict(random_tensors(spec, seed, weight_dtype, std, norm_std, device=gen_device)),
+                                     description=f"random weights (seed {seed})")
+    if kv_cache_tokens <= 0:
+        kv_cache_tokens = min(max_seqs * spec.max_positions, 262144)
+    runner = ModelRunner(spec, store, dtype=dtype, device=device, capacity_tokens=kv_cache_tokens,
+                         max_batch_tokens=max_batch_tokens, max_requests=max_seqs, page_tokens=page_tokens)
+    return LLM(runner, max_prefill_chunk=prefill_chunk, max_context=max_context)

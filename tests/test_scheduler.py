@@ -1,0 +1,144 @@
+"""The scheduler's decisions, driven through the engine with a fake model that reads the cache
+back (no GPU)."""
+import random
+
+import pytest
+
+from ember_b200 import Request, SamplingParams
+from ember_b200.engine.engine import Engine
+from tests.fake_runner import FakeRunner, argmax_sampler, expected_generation
+
+GREEDY = SamplingParams(temperature=0.0)
+
+
+def make(capacity, **kw):
+    opts = {k: kw.pop(k) for k in ("max_batch_tokens", "max_seqs", "max_prefill_chunk", "max_context") if k in kw}
+    runner = FakeRunner(capacity, **kw)
+    return runner, Engine(runner, sampler=argmax_sampler, **opts)
+
+
+def run_all(eng, runner, seqs, limit=100000):
+    n = 0
+    while any(s.finished is None for s in seqs):
+        assert eng.step(), "the engine went idle with unfinished requests"
+        assert runner.cache.check() == ""
+        n += 1
+        assert n < limit
+    return n
+
+
+def test_single_request_matches_the_fake_model():
+    runner, eng = make(256)
+    prompt = [3, 1, 4, 1, 5, 9, 2, 6]
+    out = eng.generate(prompt, max_tokens=20, ignore_eos=True)
+    assert out == expected_generation(prompt, 20, 977)
+    assert runner.cache.used_pages() == [0] and runner.cache.free_slots() == 64
+
+
+def test_decode_first_then_portions_under_the_budget():
+    runner, eng = make(4096, max_batch_tokens=64, max_prefill_chunk=48)
+    a = eng.submit(Request(prompt=list(range(1, 11)), sampling=GREEDY, max_tokens=50, ignore_eos=True))
+    assert eng.step()                                   # a: whole prompt, first token
+    b = eng.submit(Request(prompt=list(range(1, 201)), sampling=GREEDY, max_tokens=5, ignore_eos=True))
+    batch = eng.scheduler.schedule()
+    # the decoding request comes first with one token, then a portion of b bounded by chunk and budget
+    assert [(s.id, n) for s, n in batch] == [(a.id, 1), (b.id, 48)]
+    eng.scheduler.commit(batch, [7])                    # a's sampled token
+    batch = eng.scheduler.schedule()
+    assert [(s.id, n) for s, n in batch] == [(a.id, 1), (b.id, 48)]
+    assert not eng.scheduler.wants_logits(b, 48)
+
+
+def test_many_requests_few_pages_preempt_and_still_agree():
+    """60 requests in 40 pages with portions of 40 (the reference's shape: tests/test_engine.cpp:91-116)."""
+    rng = random.Random(3)
+    runner, eng = make(40 * 16, max_batch_tokens=256, max_prefill_chunk=40, max_seqs=16)
+    reqs = []
+    for _ in range(60):
+        prompt = [rng.randrange(977) for _ in range(rng.randint(1, 120))]
+        n = rng.randint(1, 60)
+        reqs.append((prompt, n, eng.submit(Request(prompt=prompt, sampling=GREEDY, max_tokens=n, ignore_eos=True))))
+    run_all(eng, runner, [s for _, _, s in reqs])
+    for prompt, n, s in reqs:
+        assert s.finished == "length" and s.output == expected_generation(prompt, n, 977)
+    assert eng.stats.preemptions > 0                    # the pool was too small on purpose
+    assert runner.cache.used_pages() == [0] and runner.cache.free_slots() == 64
+
+
+def test_preemption_takes_the_newest_and_requeues_it_first():
+    runner, eng = make(4 * 16, max_batch_tokens=64, max_prefill_chunk=64, max_seqs=4)   # 4 pages
+    a = eng.submit(Request(prompt=[1] * 30, sampling=GREEDY, max_tokens=30, ignore_eos=True))   # 2 pages
+    b = eng.submit(Request(prompt=[2] * 30, sampling=GREEDY, max_tokens=30, ignore_eos=True))   # 2 pages
+    assert eng.step()
+    assert [s.id for s in eng.scheduler.running] == [a.id, b.id]
+    eng.step()
+    eng.step()                                          # both at 32 tokens: the next token needs a third page each
+    before = eng.stats.preemptions
+    eng.step()
+    assert eng.stats.preemptions == before + 1
+    assert [s.id for s in eng.scheduler.running] == [a.id] and eng.scheduler.waiting[0].id == b.id
+    assert b.computed == 0 and not runner.cache.has(b.id)
+    run_all(eng, runner, [a, b])
+    assert a.output == expected_generation([1] * 30, 30, 977) and b.output == expected_generation([2] * 30, 30, 977)
+    assert b.preemptions >= 1
+
+
+def test_request_larger_than_the_pool_ends_with_an_error():
+    runner, eng = make(2 * 16, max_context=4096)
+    ok = eng.submit(Request(prompt=[5] * 10, sampling=GREEDY, max_tokens=4, ignore_eos=True))
+    with pytest.raises(ValueError, match="context limit"):
+        eng.submit(Request(prompt=[5] * 40, sampling=GREEDY))      # the context limit is the pool's 32 tokens
+    run_all(eng, runner, [ok])
+    assert ok.finished == "length"
+
+
+def test_finish_rules_stop_token_is_not_delivered():
+    prompt = [9, 8, 7]
+    gen = expected_generation(prompt, 6, 977)
+    runner, eng = make(256, eos_ids=(gen[2],))
+    s = eng.submit(Request(prompt=prompt, sampling=GREEDY, max_tokens=6))
+    run_all(eng, runner, [s])
+    assert s.finished == "stop" and s.output == gen[:2]
+    s2 = eng.submit(Request(prompt=prompt, sampling=GREEDY, max_tokens=6, ignore_eos=True))
+    run_all(eng, runner, [s2])
+    assert s2.finished == "length" and s2.output == gen
+    s3 = eng.submit(Request(prompt=prompt, sampling=GREEDY, max_tokens=6, stop_tokens=(gen[0],)))
+    run_all(eng, runner, [s3])
+    assert s3.finished == "stop" and s3.output == []
+    runner2, eng2 = make(256, max_context=6)
+    s4 = eng2.submit(Request(prompt=prompt, sampling=GREEDY, max_tokens=50, ignore_eos=True))
+    run_all(eng2, runner2, [s4])
+    assert s4.finished == "length" and len(s4.tokens) == 6
+
+
+def test_cancel_and_step_failure_give_pages_back():
+    runner, eng = make(256)
+    a = eng.submit(Request(prompt=[1, 2, 3], sampling=GREEDY, max_tokens=30, ignore_eos=True))
+    b = eng.submit(Request(prompt=[4, 5, 6], sampling=GREEDY, max_tokens=30, ignore_eos=True))
+    eng.step()
+    a.cancelled = True
+    eng.step()
+    assert a.finished == "cancelled" and not runner.cache.has(a.id)
+    runner.fail_next = True
+    with pytest.raises(RuntimeError, match="injected"):
+        eng.step()
+    assert b.finished == "error" and runner.cache.used_pages() == [0] and runner.cache.check() == ""
+    c = eng.submit(Request(prompt=[7, 7], sampling=GREEDY, max_tokens=3, ignore_eos=True))   # the engine keeps serving
+    run_all(eng, runner, [c])
+    assert c.output == expected_generation([7, 7], 3, 977)
+
+
+def test_window_group_frees_pages_while_decoding():
+    runner, eng = make(6 * 16, window=24, max_context=4096, max_positions=4096)
+    prompt = [11, 12, 13]
+    s = eng.submit(Request(prompt=prompt, sampling=GREEDY, max_tokens=300, ignore_eos=True))
+    run_all(eng, runner, [s])
+    assert s.output == expected_generation(prompt, 300, 977, window=24)    # 303 tokens through 6 pages
+
+
+def test_seed_zero_gets_a_seed_and_greedy_is_left_alone():
+    runner, eng = make(256)
+    s = eng.submit(Request(prompt=[1], sampling=SamplingParams(temperature=0.8), max_tokens=1))
+    assert s.request.sampling.seed != 0
+    g = eng.submit(Request(prompt=[1], sampling=GREEDY, max_tokens=1))
+    assert g.request.sampling.seed == 0
