@@ -61,7 +61,17 @@ def _lib(name: str):
     return lib
 
 
+_launches = 0
+
+
+def launch_count() -> int:
+    """How many kernel-launching calls this process has made (each launches one or two kernels)."""
+    return _launches
+
+
 def _call(lib, fn, *args):
+    global _launches
+    _launches += 1
     rc = fn(*args)
     if rc != 0:
         raise KernelError(lib.ember_last_error().decode("utf-8", "replace"))

@@ -1,0 +1,107 @@
+"""Greedy and sampled generation through the Python entry point, long decoding, first tokens."""
+import numpy as np
+import pytest
+import torch
+
+from tests.plain.qwen3_plain import PlainQwen3
+from tests.tiny_configs import TINY
+
+pytestmark = pytest.mark.gpu
+
+
+def load(tiny_model_dirs, name, dtype, **kw):
+    import ember_b200
+    opts = dict(kv_cache_tokens=1024, max_batch_tokens=256, max_seqs=8)
+    opts.update(kw)
+    return ember_b200.load(tiny_model_dirs[name], dtype=dtype, **opts)
+
+
+@pytest.mark.parametrize("name", sorted(TINY))
+def test_greedy_generation_float32_equals_plain(name, tiny_model_dirs):
+    plain = PlainQwen3(tiny_model_dirs[name], torch.float64)
+    llm = load(tiny_model_dirs, name, "float32")
+    rng = np.random.default_rng(0)
+    vocab = TINY[name]["json"]["vocab_size"]
+    prompts = [rng.integers(0, vocab, size=n).tolist() for n in (1, 5, 17, 33)]
+    outs = llm.generate(prompts, max_tokens=16, ignore_eos=True)      # batched, continuous batching
+    for p, o in zip(prompts, outs):
+        assert o == plain.greedy(p, 16)
+    assert llm.generate(prompts[2], max_tokens=16, ignore_eos=True) == outs[2]   # alone: the same tokens
+    assert llm.runner.cache.used_pages() == [0]
+
+
+def test_greedy_generation_bfloat16_follows_plain_logits(tiny_model_dirs):
+    """bfloat16 may pick another token where two logits are close; every token it picks must be
+    within bfloat16 reach of the plain implementation's maximum at that position."""
+    name = "a"
+    plain = PlainQwen3(tiny_model_dirs[name], torch.float64)
+    llm = load(tiny_model_dirs, name, "bfloat16")
+    prompt = [5, 100, 37, 8, 250, 11]
+    out = llm.generate(prompt, max_tokens=12, ignore_eos=True)
+    logits = plain.logits(prompt + out).numpy()
+    for i, tok in enumerate(out):
+        row = logits[len(prompt) - 1 + i]
+        assert row.max() - row[tok] < 0.03 * (row.max() - row.min())
+
+
+def test_long_decoding_float32(tiny_model_dirs):
+    """100 decoded tokens one by one after a short prompt: position 101 must still agree."""
+    name = "a"          # position limit 128
+    from ember_b200 import StepEntry
+    plain = PlainQwen3(tiny_model_dirs[name], torch.float64)
+    llm = load(tiny_model_dirs, name, "float32")
+    toks = np.random.default_rng(4).integers(0, 512, size=120).tolist()
+    want = plain.logits(toks).numpy()
+    r = llm.runner
+    r.admit("x")
+    r.reserve("x", 8)
+    r.step([StepEntry("x", toks[:8], ())])
+    worst = 0.0
+    for t in range(8, 120):
+        assert r.reserve("x", 1)
+        lg = r.step([StepEntry("x", [toks[t]], (0,))])[0].cpu().numpy()
+        worst = max(worst, float(np.linalg.norm(lg - want[t]) / np.linalg.norm(want[t])))
+    assert worst < 2e-5
+
+
+def test_first_tokens_of_a_sequence(tiny_model_dirs):
+    """Positions 0, 1, 2 fed one at a time (a one-token prompt included)."""
+    from ember_b200 import StepEntry
+    for name in sorted(TINY):
+        plain = PlainQwen3(tiny_model_dirs[name], torch.float64)
+        llm = load(tiny_model_dirs, name, "float32")
+        toks = [3, 1, 4]
+        want = plain.logits(toks).numpy()
+        r = llm.runner
+        r.admit("f")
+        for t in range(3):
+            r.reserve("f", 1)
+            lg = r.step([StepEntry("f", [toks[t]], (0,))])[0].cpu().numpy()
+            assert np.linalg.norm(lg - want[t]) / np.linalg.norm(want[t]) < 2e-5
+
+
+def test_temperature_sampling_is_a_function_of_seed_and_position(tiny_model_dirs):
+    from ember_b200 import SamplingParams
+    llm = load(tiny_model_dirs, "b", "float32")
+    sp = SamplingParams(temperature=0.8, top_k=50, top_p=0.95, seed=1234)
+    rng = np.random.default_rng(2)
+    prompts = [rng.integers(0, 1000, size=n).tolist() for n in (1, 31, 64, 100)]
+    together = llm.generate(prompts, sampling=sp, max_tokens=24, ignore_eos=True)
+    alone = [llm.generate(p, sampling=sp, max_tokens=24, ignore_eos=True) for p in prompts]
+    assert together == alone                                   # the batch does not change the draws
+    other = llm.generate(prompts[1], sampling=SamplingParams(temperature=0.8, top_k=50, top_p=0.95, seed=99),
+                         max_tokens=24, ignore_eos=True)
+    assert other != alone[1]
+
+
+def test_preemption_on_the_device_keeps_the_tokens(tiny_model_dirs):
+    """So few pages that requests are preempted and recomputed: the tokens stay the same."""
+    name = "a"
+    plain = PlainQwen3(tiny_model_dirs[name], torch.float64)
+    llm = load(tiny_model_dirs, name, "float32", kv_cache_tokens=96, max_seqs=4)
+    rng = np.random.default_rng(8)
+    prompts = [rng.integers(0, 512, size=n).tolist() for n in (20, 25, 30, 18)]
+    outs = llm.generate(prompts, max_tokens=30, ignore_eos=True)
+    assert llm.stats.preemptions > 0
+    for p, o in zip(prompts, outs):
+        assert o == plain.greedy(p, 30)
