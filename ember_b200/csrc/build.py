@@ -24,7 +24,7 @@ ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--shared", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
               "--expt-relaxed-constexpr"]
 SOURCES = ("elementwise", "gemm_simt", "attention", "sampling", "gemm_tc", "attention_tc", "no_alloc")
-_EXTRA_LIBS = {"gemm_tc": ["-lcuda"]}
+_EXTRA_LIBS = {}
 
 _lock = threading.Lock()
 _dir_lock = threading.Lock()

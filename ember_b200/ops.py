@@ -227,13 +227,57 @@ def sample(logits: torch.Tensor, params: torch.Tensor, out: torch.Tensor, rows: 
 
 
 # ------------------------------------------------------------- tensor-core kernels (bf16)
+_tc_scratch = {}
+_num_sms = {}
+TC_ENABLED = True          # tests switch the tensor-core kernels off to check the general ones alone
+
+
+def _sms(device) -> int:
+    n = _num_sms.get(device)
+    if n is None:
+        n = torch.cuda.get_device_properties(device).multi_processor_count
+        _num_sms[device] = n
+    return n
+
+
+def _scratch(device, floats: int) -> torch.Tensor:
+    """Zero-filled fp32 scratch for split-K partial sums; the kernels leave it zeroed."""
+    t = _tc_scratch.get(device)
+    if t is None or t.numel() < floats:
+        t = torch.zeros(max(floats, 1 << 20), dtype=torch.float32, device=device)
+        _tc_scratch[device] = t
+    return t
+
+
 def gemm_tc_usable(x: torch.Tensor, w: torch.Tensor, bias, epilogue: int) -> bool:
-    """Whether the tcgen05 product takes these operands."""
-    return False
+    """Whether the tcgen05 product takes these operands: bf16 activations and weights, no bias,
+    K a multiple of 8 (TMA row pitch), an even N for the gated epilogue."""
+    if not TC_ENABLED or bias is not None or x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
+        return False
+    n, k = w.shape
+    return k % 8 == 0 and not (epilogue == EPI_SILU_MUL and n % 2)
 
 
-def gemm_tc(linear, x, out, m, epilogue, stream=None) -> None:
-    raise KernelError("the tensor-core product is not built")
+def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, M: int, epilogue: int = EPI_STORE,
+            err: Optional[torch.Tensor] = None, stream: Optional[int] = None) -> None:
+    """out (+)= a[:M] @ w.T on the tcgen05 tensor cores (bf16 in, fp32 accumulate)."""
+    _check(a, "a", torch.bfloat16)
+    _check(w, "w", torch.bfloat16)
+    _check(out, "out")
+    N, K = w.shape
+    if a.shape[-1] != K:
+        raise KernelError(f"gemm: activations of width {a.shape[-1]} against weights {tuple(w.shape)}")
+    n_out = N // 2 if epilogue == EPI_SILU_MUL else N
+    want = torch.bfloat16 if epilogue in (EPI_STORE, EPI_SILU_MUL) else torch.float32
+    if out.dtype != want:
+        raise KernelError(f"gemm: epilogue {epilogue} writes {want}, the output is {out.dtype}")
+    if out.shape[-1] != n_out or out.numel() < M * n_out or a.numel() < M * K:
+        raise KernelError(f"gemm: output {tuple(out.shape)} / input {tuple(a.shape)} do not fit M={M} N={n_out}")
+    scratch = _scratch(a.device, min(M, 128) * N) if M <= 128 else None
+    lib = _lib("gemm_tc")
+    _call(lib, lib.ember_gemm_tc, _p(a), _p(w), _p(out), c_int(n_out), c_int(M), c_int(N), c_int(K), c_int(epilogue),
+          _p(scratch), c_longlong(scratch.numel() if scratch is not None else 0), c_int(_sms(a.device)), _p(err),
+          c_void_p(stream if stream is not None else current_stream_ptr()))
 
 
 def attention_tc_usable(dtype: torch.dtype, head_dim: int, group: int, page_tokens: int) -> bool:

@@ -31,6 +31,6 @@ class Linear:
         if m <= 0:
             return
         if ops.gemm_tc_usable(x, self.weight, self.bias, epilogue):
-            ops.gemm_tc(self, x, out, m, epilogue, stream=ctx.stream)
+            ops.gemm_tc(x, self.weight, out, m, epilogue, err=ctx.err, stream=ctx.stream)
         else:
             ops.gemm_simt(x, self.weight, out, m, epilogue, bias=self.bias, stream=ctx.stream)

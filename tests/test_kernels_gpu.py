@@ -1,0 +1,234 @@
+"""Each kernel alone against a plain fp32 PyTorch statement of the same operation, at sizes other
+than the engine's."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+
+def rel(a, b):
+    a, b = a.double().flatten(), b.double().flatten()
+    return float((a - b).norm() / b.norm().clamp_min(1e-30))
+
+
+def ref_epilogue(c, epilogue, prev=None):
+    if epilogue == 3:
+        g, u = c[:, 0::2], c[:, 1::2]
+        return g / (1 + torch.exp(-g)) * u
+    if epilogue == 2:
+        return prev + c
+    return c
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 512, 64), (3, 1000, 96), (17, 192, 200), (64, 2048, 2048), (65, 130, 72),
+                                   (128, 256, 512), (129, 1000, 264), (300, 1536, 1024), (1000, 520, 136)])
+@pytest.mark.parametrize("epilogue", [0, 1, 2, 3])
+def test_gemm_tc(M, N, K, epilogue):
+    from ember_b200 import ops
+    torch.manual_seed(M * 7 + N + K + epilogue)
+    a = (torch.randn(M, K, device="cuda") * 0.5).bfloat16()
+    w = (torch.randn(N, K, device="cuda") * 0.5).bfloat16()
+    n_out = N // 2 if epilogue == 3 else N
+    prev = torch.randn(M, n_out, device="cuda")
+    out = prev.clone() if epilogue in (1, 2) else torch.zeros(M, n_out, device="cuda", dtype=torch.bfloat16)
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    assert ops.gemm_tc_usable(a, w, None, epilogue)
+    ops.gemm_tc(a, w, out, M, epilogue, err=err)
+    want = ref_epilogue(a.float() @ w.float().t(), epilogue, prev)
+    assert int(err.item()) == 0
+    tol = 5e-3 if epilogue in (0, 3) else 1e-5          # bf16 rounding of the output, else fp32 accumulation only
+    assert rel(out.float(), want) < tol
+    if M <= 128:                                        # the split-K scratch is left zeroed
+        assert float(ops._tc_scratch[a.device].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("M,N,K", [(1, 50, 7), (5, 1000, 96), (70, 130, 33), (200, 192, 64)])
+@pytest.mark.parametrize("epilogue", [0, 1, 2, 3])
+@pytest.mark.parametrize("adt,wdt", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16),
+                                     (torch.bfloat16, torch.float32)])
+def test_gemm_simt(M, N, K, epilogue, adt, wdt):
+    from ember_b200 import ops
+    torch.manual_seed(M + N + K)
+    a = (torch.randn(M, K, device="cuda") * 0.5).to(adt)
+    w = (torch.randn(N, K, device="cuda") * 0.5).to(wdt)
+    bias = torch.randn(N, device="cuda")
+    n_out = N // 2 if epilogue == 3 else N
+    prev = torch.randn(M, n_out, device="cuda")
+    out = prev.clone() if epilogue in (1, 2) else torch.zeros(M, n_out, device="cuda", dtype=adt)
+    ops.gemm_simt(a, w, out, M, epilogue, bias=bias)
+    c = (a.double() @ w.double().t() + bias.double()).float()
+    want = ref_epilogue(c, epilogue, prev)
+    tol = 5e-3 if (adt == torch.bfloat16 and epilogue in (0, 3)) else 2e-6
+    assert rel(out.float(), want) < tol
+
+
+def test_gemm_simt_is_independent_of_the_batch():
+    """A row's fp32 result is bit-identical whatever else is in the batch."""
+    from ember_b200 import ops
+    torch.manual_seed(0)
+    a = torch.randn(150, 200, device="cuda")
+    w = torch.randn(300, 200, device="cuda")
+    full = torch.empty(150, 300, device="cuda")
+    ops.gemm_simt(a, w, full, 150, 1)
+    one = torch.empty(1, 300, device="cuda")
+    ops.gemm_simt(a[77:78].contiguous(), w, one, 1, 1)
+    assert torch.equal(one[0], full[77])
+
+
+@pytest.mark.parametrize("H", [64, 96, 1000, 2048, 5120])
+@pytest.mark.parametrize("odt", [torch.float32, torch.bfloat16])
+def test_rmsnorm(H, odt):
+    from ember_b200 import ops
+    torch.manual_seed(H)
+    x = torch.randn(37, H, device="cuda") * 3
+    w = 1 + 0.1 * torch.randn(H, device="cuda")
+    rows = torch.tensor([5, 0, 36, 5], dtype=torch.int32, device="cuda")
+    for eps in (1e-6, 1e-5):
+        out = torch.empty(37, H, device="cuda", dtype=odt)
+        ops.rmsnorm(x, w, eps, out, 37)
+        want = w * (x * torch.rsqrt((x.double() ** 2).mean(-1, keepdim=True) + eps).float())
+        assert rel(out.float(), want) < (4e-3 if odt == torch.bfloat16 else 1e-6)
+        g = torch.empty(4, H, device="cuda", dtype=odt)
+        ops.rmsnorm(x, w, eps, g, 4, rows=rows)
+        assert torch.equal(g, out[rows.long()])
+
+
+@pytest.mark.parametrize("tdt", [torch.float32, torch.bfloat16])
+def test_embed(tdt):
+    from ember_b200 import ops
+    table = torch.randn(1000, 96, device="cuda").to(tdt)
+    toks = torch.tensor([0, 999, 5, 5, 123], dtype=torch.int32, device="cuda")
+    out = torch.empty(5, 96, device="cuda")
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    ops.embed(toks, table, out, err=err)
+    assert torch.equal(out, table[toks.long()].float()) and int(err.item()) == 0
+    bad = torch.tensor([3, 1000], dtype=torch.int32, device="cuda")
+    ops.embed(bad, table, out, err=err)                 # out of range: recorded, not trapped
+    assert int(err.item()) == 1 and float(out[1].abs().max()) == 0.0
+
+
+def rope_ref(x, pos, inv_freq, rotary):
+    half = rotary // 2
+    ang = pos.float()[:, None] * inv_freq[None, :]
+    cs, sn = torch.cos(ang)[:, None, :], torch.sin(ang)[:, None, :]
+    a, b = x[..., :half], x[..., half:rotary]
+    return torch.cat([a * cs - b * sn, b * cs + a * sn, x[..., rotary:]], dim=-1)
+
+
+@pytest.mark.parametrize("heads,kv,D,rotary,page", [(4, 2, 16, 16, 16), (6, 1, 32, 32, 16), (5, 5, 48, 24, 32),
+                                                    (16, 8, 128, 128, 16), (3, 1, 256, 256, 64), (2, 2, 80, 0, 16)])
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("norm", [True, False])
+def test_qk_norm_rope_store(heads, kv, D, rotary, page, dt, norm):
+    from ember_b200 import ops
+    torch.manual_seed(heads * D + rotary)
+    dev = "cuda"
+    lens, starts = [5, 1, 40], [3, 77, 0]                 # three runs at different positions
+    T = sum(lens)
+    pos = torch.cat([torch.arange(s, s + n) for s, n in zip(starts, lens)]).int().to(dev)
+    seq = torch.cat([torch.full((n,), i) for i, n in enumerate(lens)]).int().to(dev)
+    nblk = max((s + n + page - 1) // page for s, n in zip(starts, lens))
+    pages = 3 * nblk + 2
+    perm = torch.randperm(pages)[:3 * nblk].reshape(3, nblk).int().to(dev)      # scattered, out-of-order pages
+    ld = (heads + 2 * kv) * D
+    qkv = (torch.randn(T, ld, device=dev) * 2).to(dt)
+    qw, kw = (1 + 0.1 * torch.randn(D, device=dev), 1 + 0.1 * torch.randn(D, device=dev)) if norm else (None, None)
+    inv = (1.0 / (10000.0 ** (torch.arange(rotary // 2, device=dev).float() * 2 / max(rotary, 1)))) if rotary else None
+    kp = torch.zeros(pages, kv, page, D, device=dev, dtype=dt)
+    vp = torch.zeros_like(kp)
+    q = torch.empty(T, heads * D, device=dev, dtype=dt)
+    err = torch.zeros(1, dtype=torch.int32, device=dev)
+    ops.qk_norm_rope_store(qkv, T, heads, kv, D, qw, kw, 1e-5, inv, rotary, pos, seq, perm, page, kp, vp, q, err=err)
+    assert int(err.item()) == 0
+    x = qkv.float()
+    qq, kk, vv = x[:, :heads * D].view(T, heads, D), x[:, heads * D:(heads + kv) * D].view(T, kv, D), x[:, (heads + kv) * D:].view(T, kv, D)
+
+    def nrm(t, w):
+        return w * (t * torch.rsqrt((t.double() ** 2).mean(-1, keepdim=True) + 1e-5).float()) if norm else t
+
+    qq, kk = nrm(qq, qw), nrm(kk, kw)
+    if rotary:
+        qq, kk = rope_ref(qq, pos, inv, rotary), rope_ref(kk, pos, inv, rotary)
+    tol = 6e-3 if dt == torch.bfloat16 else 2e-6
+    assert rel(q.float().view(T, heads, D), qq) < tol
+    for t in range(T):
+        blk, slot = int(perm[seq[t], pos[t] // page]), int(pos[t]) % page
+        assert rel(kp[blk, :, slot].float(), kk[t]) < tol
+        assert torch.equal(vp[blk, :, slot].float(), vv[t].to(dt).float())
+    written = torch.zeros(pages, page, dtype=torch.bool)
+    for t in range(T):
+        written[int(perm[seq[t], pos[t] // page]), int(pos[t]) % page] = True
+    untouched = kp.permute(0, 2, 1, 3)[~written.to(dev)]
+    assert float(untouched.abs().max() if untouched.numel() else 0) == 0.0             # nothing else was touched
+
+
+def attention_ref(q, k, v, scale, window):
+    T, H, D = q.shape
+    G = H // k.shape[1]
+    out = torch.zeros_like(q)
+    n = k.shape[0]
+    for h in range(H):
+        s = (q[:, h] @ k[:, h // G].t()) * scale
+        qpos = torch.arange(n - T, n, device=q.device)[:, None]
+        kpos = torch.arange(n, device=q.device)[None, :]
+        vis = kpos <= qpos
+        if window:
+            vis &= kpos > qpos - window
+        out[:, h] = torch.softmax(s.masked_fill(~vis, float("-inf")), -1) @ v[:, h // G]
+    return out
+
+
+@pytest.mark.parametrize("heads,kv,D,page", [(4, 2, 16, 16), (6, 1, 32, 16), (8, 8, 64, 32), (16, 8, 128, 16), (2, 1, 256, 16),
+                                             (12, 4, 80, 16)])
+@pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("window", [0, 37])
+def test_attention_general(heads, kv, D, page, dt, window):
+    """Runs of different lengths at different cache depths, scattered pages, one far key made to
+    stand out so that a wrong page or a wrong mask shows."""
+    from ember_b200 import ops
+    from ember_b200.engine.batch import StepBatch, attention_tiles
+    torch.manual_seed(heads + D + window)
+    dev = "cuda"
+    ctx_lens, new = [300, 45, 1, 700], [33, 45, 1, 1]       # tokens cached after the step, new tokens of it
+    S = len(ctx_lens)
+    nblk = max((c + page - 1) // page for c in ctx_lens)
+    pages = S * nblk + 3
+    perm = torch.randperm(pages)[:S * nblk].reshape(S, nblk).int()
+    kp = torch.zeros(pages, kv, page, D, dtype=dt)
+    vp = torch.zeros_like(kp)
+    ks, vs, qs = [], [], []
+    for s in range(S):
+        k = torch.randn(ctx_lens[s], kv, D) * 0.5
+        v = torch.randn(ctx_lens[s], kv, D)
+        q = torch.randn(new[s], heads, D) * 0.5
+        if ctx_lens[s] > 100:                               # one far key stands out for the last query
+            far = 7 if not window else ctx_lens[s] - window + 1
+            k[far] = q[-1, ::heads // kv] * 6.0
+        ks.append(k.to(dt).float()), vs.append(v.to(dt).float()), qs.append(q.to(dt).float())
+        for j in range(ctx_lens[s]):
+            kp[perm[s, j // page], :, j % page] = k[j].to(dt)
+            vp[perm[s, j // page], :, j % page] = v[j].to(dt)
+    T = sum(new)
+    q_all = torch.cat(qs).to(dt).to(dev).contiguous()
+    qstart = np.cumsum([0] + new).astype(np.int32)
+    positions = np.concatenate([np.arange(c - n, c) for c, n in zip(ctx_lens, new)]).astype(np.int32)
+    batch = StepBatch(requests=list(range(S)), tokens=np.zeros(T, np.int32), positions=positions,
+                      seq_of=np.repeat(np.arange(S), new).astype(np.int32), query_start=qstart,
+                      context_len=np.asarray(ctx_lens, np.int32), block_tables=[perm.numpy()],
+                      state_slots=np.zeros(S, np.int32), logit_rows=np.zeros(0, np.int32))
+    tile_q = ops.attention_tile_queries(heads // kv)
+    tiles = torch.from_numpy(attention_tiles(batch, tile_q)).to(dev)
+    scale = 1.0 / math.sqrt(D)
+    want = torch.cat([attention_ref(qs[s].to(dev), ks[s].to(dev), vs[s].to(dev), scale, window) for s in range(S)])
+    err = torch.zeros(1, dtype=torch.int32, device=dev)
+    for n_splits, split_keys in ((1, 0), (6, 128)):
+        out = torch.zeros(T, heads * D, device=dev, dtype=dt)
+        po = torch.empty(T * heads * n_splits * D, device=dev)
+        pml = torch.empty(T * heads * n_splits * 2, device=dev)
+        ops.attention(q_all.view(T, -1), kp.to(dev), vp.to(dev), out, T, heads, kv, D, tiles, tiles.shape[0], tile_q,
+                      perm.to(dev), page, window, scale, n_splits, split_keys, po, pml, err=err)
+        assert int(err.item()) == 0
+        assert rel(out.float().view(T, heads, D), want) < (6e-3 if dt == torch.bfloat16 else 3e-6)
