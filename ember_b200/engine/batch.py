@@ -117,12 +117,15 @@ def build_batch(entries: Sequence[StepEntry], cache: CacheManager, vocab_size: i
         state_slots=np.asarray(slots, dtype=np.int32), logit_rows=np.asarray(rows, dtype=np.int32))
 
 
-def attention_tiles(batch: StepBatch, tile_q: int) -> np.ndarray:
-    """Cuts every run into tiles of at most ``tile_q`` consecutive queries:
-    rows of (run, first token row, queries, position of the first query)."""
+def attention_tiles(batch: StepBatch, tile_q: int, kind: str = "all") -> np.ndarray:
+    """Cuts runs into tiles of at most ``tile_q`` consecutive queries:
+    rows of (run, first token row, queries, position of the first query).
+    ``kind`` selects the runs: "all", "multi" (two or more new tokens) or "single" (one)."""
     out = []
     for s in range(batch.S):
         a, b = int(batch.query_start[s]), int(batch.query_start[s + 1])
+        if (kind == "multi" and b - a < 2) or (kind == "single" and b - a != 1):
+            continue
         for r in range(a, b, tile_q):
             out.append((s, r, min(tile_q, b - r), int(batch.positions[r])))
     return np.asarray(out, dtype=np.int32).reshape(-1, 4)
@@ -190,7 +193,8 @@ class StepContext:
         self.query_start_host = batch.query_start
         self.positions_host = batch.positions
         self.state_slots_host = batch.state_slots
-        self._tiles_host = {tq: attention_tiles(batch, tq) for tq in tile_sizes}
+        # tile_sizes: (tile_q, kind) pairs the model's mixers asked for ahead of time
+        self._tiles_host = {key: attention_tiles(batch, key[0], key[1]) for key in tile_sizes}
         # one packed upload
         parts = [batch.tokens, batch.positions, batch.seq_of, batch.query_start, batch.context_len,
                  batch.state_slots, batch.logit_rows] + [t.reshape(-1) for t in batch.block_tables] + \
@@ -217,22 +221,29 @@ class StepContext:
         self.query_start, self.context_len, self.state_slots, self.logit_rows = view(3), view(4), view(5), view(6)
         ng = len(batch.block_tables)
         self._tables = [view(7 + g, batch.block_tables[g].shape) for g in range(ng)]
-        self._tiles = {tq: (view(7 + ng + i, (-1, 4)), int(self._tiles_host[tq].shape[0]))
-                       for i, tq in enumerate(self._tiles_host)}
+        self._tiles = {key: (view(7 + ng + i, (-1, 4)) if self._tiles_host[key].size else None,
+                             int(self._tiles_host[key].shape[0]))
+                       for i, key in enumerate(self._tiles_host)}
 
     def block_table(self, group: int) -> torch.Tensor:
         return self._tables[group]
 
-    def attention_tiles(self, tile_q: int):
-        """(device tensor [n, 4], n) for tiles of up to ``tile_q`` queries."""
-        got = self._tiles.get(tile_q)
+    def attention_tiles(self, tile_q: int, kind: str = "all"):
+        """(device tensor [n, 4] or None, n) for tiles of up to ``tile_q`` queries over the runs of
+        ``kind``.  Tile shapes a mixer announces through ``tile_requests`` travel with the step's one
+        upload; others cost a copy of their own."""
+        key = (tile_q, kind)
+        got = self._tiles.get(key)
         if got is None:
-            host = attention_tiles(self.batch, tile_q)
-            dev = self.workspace.dynamic(f"step.tiles.{tile_q}", max(host.size, 4), torch.int32)
-            dev[:host.size].copy_(torch.from_numpy(host.reshape(-1)), non_blocking=False)
-            got = (dev[:host.size].view(-1, 4), int(host.shape[0]))
-            self._tiles[tile_q] = got
-            self._tiles_host[tile_q] = host
+            host = attention_tiles(self.batch, tile_q, kind)
+            if host.size == 0:
+                got = (None, 0)
+            else:
+                dev = self.workspace.dynamic(f"step.tiles.{tile_q}.{kind}", max(host.size, 4), torch.int32)
+                dev[:host.size].copy_(torch.from_numpy(host.reshape(-1)), non_blocking=False)
+                got = (dev[:host.size].view(-1, 4), int(host.shape[0]))
+            self._tiles[key] = got
+            self._tiles_host[key] = host
         return got
 
     def buf(self, name: str, shape: Tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:

@@ -96,7 +96,8 @@ class ModelRunner:
     def run_batch(self, batch: StepBatch) -> Optional[torch.Tensor]:
         if batch.T > self.max_batch_tokens:
             raise BatchError(f"the step has {batch.T} tokens; the limit is {self.max_batch_tokens}")
-        ctx = StepContext(batch, self.workspace, self.device, self.max_batch_tokens, err=self.err)
+        ctx = StepContext(batch, self.workspace, self.device, self.max_batch_tokens, err=self.err,
+                          tile_sizes=self.model.tile_requests())
         logits = self.model.forward(ctx, self.storage)
         for s, req in enumerate(batch.requests):
             self.cache.advance(req, int(batch.context_len[s]))

@@ -64,6 +64,18 @@ class CausalLM:
         owners = {(e.cache_of if e.cache_of >= 0 else e.layer) for e in self.spec.schedule}
         return {l: self.blocks[l].mixer.cache_need() for l in sorted(owners)}
 
+    def tile_requests(self):
+        """Attention tile shapes the mixers will ask the step context for (sent with the step's upload)."""
+        if not hasattr(self, "_tile_requests"):
+            keys = []
+            for b in self.blocks:
+                fn = getattr(b.mixer, "tile_requests", None)
+                for k in (fn() if fn else ()):
+                    if k not in keys:
+                        keys.append(k)
+            self._tile_requests = tuple(keys)
+        return self._tile_requests
+
     # ------------------------------------------------------------------ forward
     def forward(self, ctx, storage) -> Optional[torch.Tensor]:
         s, rt = self.spec, self.rt

@@ -280,9 +280,44 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, M: int, epilogu
           c_void_p(stream if stream is not None else current_stream_ptr()))
 
 
-def attention_tc_usable(dtype: torch.dtype, head_dim: int, group: int, page_tokens: int) -> bool:
-    return False
+def num_sms(device) -> int:
+    return _sms(device)
 
 
-def attention_tc(*args, **kw) -> None:
-    raise KernelError("the tensor-core attention is not built")
+def attention_tc_supported(head_dim: int, group: int, page_tokens: int, mode: int) -> bool:
+    """Whether the tensor-core attention takes this geometry (mode 0: prompt portions, 1: single tokens)."""
+    if not TC_ENABLED:
+        return False
+    lib = _lib("attention_tc")
+    return bool(lib.ember_attention_tc_supported(c_int(head_dim), c_int(group), c_int(page_tokens), c_int(mode)))
+
+
+def attention_tc_tile_queries(group: int) -> int:
+    return int(_lib("attention_tc").ember_attention_tc_tile_queries(c_int(group)))
+
+
+def attention_tc(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: torch.Tensor, mode: int,
+                 n_heads: int, n_kv: int, head_dim: int, tiles: torch.Tensor, n_tiles: int, block_table: torch.Tensor,
+                 page: int, window: int, scale: float, n_splits: int = 1, split_keys: int = 0,
+                 part_o: Optional[torch.Tensor] = None, part_ml: Optional[torch.Tensor] = None,
+                 err: Optional[torch.Tensor] = None, stream: Optional[int] = None) -> None:
+    """bf16 attention over the paged cache on tensor cores (TMA-fed).  ``mode`` 0 takes tiles of
+    prompt portions, 1 takes single-token tiles and may split their key range."""
+    _check(q, "q", torch.bfloat16)
+    _check(out, "out", torch.bfloat16)
+    _check(k_pool, "k_pool", torch.bfloat16)
+    _check(v_pool, "v_pool", torch.bfloat16)
+    _check(tiles, "tiles", torch.int32)
+    _check(block_table, "block_table", torch.int32)
+    if k_pool.dim() != 4 or tuple(k_pool.shape[1:]) != (n_kv, page, head_dim) or v_pool.shape != k_pool.shape:
+        raise KernelError(f"attention: pools {tuple(k_pool.shape)} are not [pages, {n_kv}, {page}, {head_dim}]")
+    if n_splits > 1:
+        _check(part_o, "part_o", torch.float32)
+        _check(part_ml, "part_ml", torch.float32)
+        if part_o.numel() < n_tiles * n_heads * n_splits * head_dim or part_ml.numel() < n_tiles * n_heads * n_splits * 2:
+            raise KernelError("attention: split buffers too small")
+    lib = _lib("attention_tc")
+    _call(lib, lib.ember_attention_tc, _p(q), _p(k_pool), _p(v_pool), _p(out), c_int(mode), c_int(n_heads), c_int(n_kv),
+          c_int(head_dim), _p(tiles), c_int(n_tiles), _p(block_table), c_int(block_table.shape[-1]), c_int(page),
+          c_int(k_pool.shape[0]), c_int(window), c_float(scale), c_int(n_splits), c_int(split_keys), _p(part_o),
+          _p(part_ml), _p(err), c_void_p(stream if stream is not None else current_stream_ptr()))

@@ -95,14 +95,56 @@ class Attention(Mixer):
         self.attend(ctx, q, cache, table, att)
         self.o(ctx, att, residual, T, ops.EPI_ADD_F32)
 
+    def _tc_modes(self):
+        """(prompt portions, single tokens): whether the tensor-core kernels take this geometry."""
+        s, rt = self.spec, self.rt
+        if rt.dtype != torch.bfloat16:
+            return False, False
+        return (ops.attention_tc_supported(s.head_dim, s.group, rt.page_tokens, 0),
+                ops.attention_tc_supported(s.head_dim, s.group, rt.page_tokens, 1))
+
+    def tile_requests(self):
+        s = self.spec
+        multi, single = self._tc_modes()
+        if multi:
+            tq = ops.attention_tc_tile_queries(s.group)
+            return [(tq, "multi"), (1, "single")] if single else [(tq, "all")]
+        return [(ops.attention_tile_queries(s.group), "all")]
+
     def attend(self, ctx, q: torch.Tensor, cache, table: torch.Tensor, out: torch.Tensor) -> None:
         """out[t, h, :] = softmax over the visible keys of (q . k * scale) times v."""
         s = self.spec
-        if ops.attention_tc_usable(q.dtype, s.head_dim, s.group, cache.page_tokens):
-            ops.attention_tc(ctx, q, cache, table, out, s.num_heads, s.num_kv_heads, s.head_dim, s.window, self.scale)
+        multi, single = self._tc_modes()
+        if multi and ops.TC_ENABLED:
+            tq = ops.attention_tc_tile_queries(s.group)
+            args = (s.num_heads, s.num_kv_heads, s.head_dim)
+            if not single:
+                tiles, n = ctx.attention_tiles(tq, "all")
+                ops.attention_tc(q, cache.k, cache.v, out, 0, *args, tiles, n, table, cache.page_tokens, s.window,
+                                 self.scale, err=ctx.err, stream=ctx.stream)
+                return
+            tiles, n = ctx.attention_tiles(tq, "multi")
+            if n:
+                ops.attention_tc(q, cache.k, cache.v, out, 0, *args, tiles, n, table, cache.page_tokens, s.window,
+                                 self.scale, err=ctx.err, stream=ctx.stream)
+            tiles, n = ctx.attention_tiles(1, "single")
+            if n:
+                # cut long key ranges so that about two waves of blocks share the work; splits are
+                # anchored at key 0, so with a window the early ones are empty
+                live = ctx.max_context if s.window <= 0 else min(ctx.max_context, s.window + 64)
+                want = max(1, (2 * ops.num_sms(q.device)) // max(1, n * s.num_kv_heads))
+                live_splits = max(1, min(want, (live + 255) // 256))
+                split_keys = ((live + live_splits - 1) // live_splits + 63) // 64 * 64
+                n_splits = (ctx.max_context + split_keys - 1) // split_keys
+                part_o = part_ml = None
+                if n_splits > 1:
+                    part_o = ctx.buf_dyn("attention.part_o", n * s.num_heads * n_splits * s.head_dim, torch.float32)
+                    part_ml = ctx.buf_dyn("attention.part_ml", n * s.num_heads * n_splits * 2, torch.float32)
+                ops.attention_tc(q, cache.k, cache.v, out, 1, *args, tiles, n, table, cache.page_tokens, s.window,
+                                 self.scale, n_splits, split_keys, part_o, part_ml, err=ctx.err, stream=ctx.stream)
             return
         tile_q = ops.attention_tile_queries(s.group)
-        tiles, n_tiles = ctx.attention_tiles(tile_q)
+        tiles, n_tiles = ctx.attention_tiles(tile_q, "all")
         # long key ranges of a small step are cut into fixed splits so that more SMs share them
         span = ctx.max_context if s.window <= 0 else min(ctx.max_context, s.window + tile_q)
         n_splits, part_o, part_ml = 1, None, None

@@ -182,7 +182,7 @@ def attention_ref(q, k, v, scale, window):
 
 
 @pytest.mark.parametrize("heads,kv,D,page", [(4, 2, 16, 16), (6, 1, 32, 16), (8, 8, 64, 32), (16, 8, 128, 16), (2, 1, 256, 16),
-                                             (12, 4, 80, 16)])
+                                             (12, 4, 80, 16), (12, 2, 128, 64), (5, 1, 64, 16), (32, 2, 64, 16)])
 @pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("window", [0, 37])
 def test_attention_general(heads, kv, D, page, dt, window):
@@ -224,6 +224,27 @@ def test_attention_general(heads, kv, D, page, dt, window):
     scale = 1.0 / math.sqrt(D)
     want = torch.cat([attention_ref(qs[s].to(dev), ks[s].to(dev), vs[s].to(dev), scale, window) for s in range(S)])
     err = torch.zeros(1, dtype=torch.int32, device=dev)
+    if dt == torch.bfloat16 and ops.attention_tc_supported(D, heads // kv, page, 0):
+        # the tensor-core kernels on the same case: prompt portions in mode 0, single tokens in mode 1
+        out = torch.zeros(T, heads * D, device=dev, dtype=dt)
+        tq = ops.attention_tc_tile_queries(heads // kv)
+        multi = torch.from_numpy(attention_tiles(batch, tq, "multi")).to(dev)
+        single = torch.from_numpy(attention_tiles(batch, 1, "single")).to(dev)
+        ops.attention_tc(q_all.view(T, -1), kp.to(dev), vp.to(dev), out, 0, heads, kv, D, multi, multi.shape[0],
+                         perm.to(dev), page, window, scale, err=err)
+        for n_splits, split_keys in ((1, 0), (4, 192), (11, 64)):
+            po = torch.empty(single.shape[0] * heads * n_splits * D, device=dev)
+            pml = torch.empty(single.shape[0] * heads * n_splits * 2, device=dev)
+            out[-2:] = 0
+            ops.attention_tc(q_all.view(T, -1), kp.to(dev), vp.to(dev), out, 1, heads, kv, D, single, single.shape[0],
+                             perm.to(dev), page, window, scale, n_splits, split_keys, po, pml, err=err)
+            assert int(err.item()) == 0
+            assert rel(out.float().view(T, heads, D), want) < 6e-3
+        all_tiles = torch.from_numpy(attention_tiles(batch, tq, "all")).to(dev)     # single tokens through mode 0 too
+        out2 = torch.zeros_like(out)
+        ops.attention_tc(q_all.view(T, -1), kp.to(dev), vp.to(dev), out2, 0, heads, kv, D, all_tiles, all_tiles.shape[0],
+                         perm.to(dev), page, window, scale, err=err)
+        assert int(err.item()) == 0 and rel(out2.float().view(T, heads, D), want) < 6e-3
     for n_splits, split_keys in ((1, 0), (6, 128)):
         out = torch.zeros(T, heads * D, device=dev, dtype=dt)
         po = torch.empty(T * heads * n_splits * D, device=dev)
