@@ -52,7 +52,7 @@ class LLM:
 
 def load(model: str, dtype: str = "bfloat16", device: str = "cuda:0", kv_cache_tokens: int = 0,
          max_batch_tokens: int = 2048, max_seqs: int = 64, prefill_chunk: int = 512,
-         max_context: Optional[int] = None, page_tokens: int = 16) -> LLM:
+         max_context: Optional[int] = None, page_tokens: int = 16, cuda_graphs: bool = True) -> LLM:
     """Loads a model folder (config.json + safetensors).  ``kv_cache_tokens`` 0 sizes the cache
     for ``max_seqs`` requests of the model's position limit, capped at 262,144 tokens."""
     cfg = load_config(model)
@@ -61,13 +61,14 @@ def load(model: str, dtype: str = "bfloat16", device: str = "cuda:0", kv_cache_t
         kv_cache_tokens = min(max_seqs * spec.max_positions, 262144)
     runner = ModelRunner(spec, WeightStore.from_dir(model), dtype=dtype, device=device,
                          capacity_tokens=kv_cache_tokens, max_batch_tokens=max_batch_tokens,
-                         max_requests=max_seqs, page_tokens=page_tokens)
+                         max_requests=max_seqs, page_tokens=page_tokens, cuda_graphs=cuda_graphs)
     return LLM(runner, max_prefill_chunk=prefill_chunk, max_context=max_context)
 
 
 def load_random(config, seed: int = 0, dtype: str = "bfloat16", device: str = "cuda:0", kv_cache_tokens: int = 0,
                 max_batch_tokens: int = 2048, max_seqs: int = 64, prefill_chunk: int = 512,
-                max_context: Optional[int] = None, page_tokens: int = 16, weight_dtype=torch.bfloat16,
+                max_context: Optional[int] = None, page_tokens: int = 16, cuda_graphs: bool = True,
+                weight_dtype=torch.bfloat16,
                 std: Optional[float] = None, norm_std: Optional[float] = None) -> LLM:
     """Random-weights mode without a folder: the tensors are made from ``seed`` in memory
     (on the device when it is a CUDA device) and loaded as if they came from a file."""
@@ -78,5 +79,6 @@ def load_random(config, seed: int = 0, dtype: str = "bfloat16", device: str = "c
     if kv_cache_tokens <= 0:
         kv_cache_tokens = min(max_seqs * spec.max_positions, 262144)
     runner = ModelRunner(spec, store, dtype=dtype, device=device, capacity_tokens=kv_cache_tokens,
-                         max_batch_tokens=max_batch_tokens, max_requests=max_seqs, page_tokens=page_tokens)
+                         max_batch_tokens=max_batch_tokens, max_requests=max_seqs, page_tokens=page_tokens,
+                         cuda_graphs=cuda_graphs)
     return LLM(runner, max_prefill_chunk=prefill_chunk, max_context=max_context)

@@ -10,7 +10,7 @@ The engine starts at token ids (there is no tokenizer here): ``-p`` takes ids se
 spaces or commas, ``--ids-file`` a file of them.  Options keep the reference's names where it
 has them: ``-m/--model``, ``--max-batch-tokens`` (2048), ``--max-seqs`` (64), ``--prefill-chunk``
 (512), ``--kv-cache-tokens``, ``-n/--max-tokens`` (512), ``--temp`` (0.7), ``--top-p`` (0.8),
-``--top-k`` (20), ``--min-p`` (0), ``--seed``, ``--greedy``, ``-v``.  ``--dtype`` (bfloat16 or
+``--top-k`` (20), ``--min-p`` (0), ``--seed``, ``--greedy``, ``--no-cuda-graphs``, ``-v``.  ``--dtype`` (bfloat16 or
 float32) stands where the reference has ``--weights``.
 """
 from __future__ import annotations
@@ -48,6 +48,7 @@ def _parser() -> argparse.ArgumentParser:
     ap.add_argument("--config", default="", help="random: the config.json to make a model for")
     ap.add_argument("--out", default="", help="random / replay: output folder")
     ap.add_argument("--weights-dtype", default="bfloat16", choices=["bfloat16", "float32"])
+    ap.add_argument("--no-cuda-graphs", action="store_true", help="launch decode kernels one by one")
     ap.add_argument("-v", "--verbose", action="store_true")
     ap.add_argument("rest", nargs="*", help="bench: prompt=N gen=N batch=a,b,c")
     return ap
@@ -65,7 +66,7 @@ def _load(args):
         raise SystemExit("error: give a model folder with -m DIR")
     return ember_b200.load(args.model, dtype=args.dtype, kv_cache_tokens=args.kv_cache_tokens,
                            max_batch_tokens=args.max_batch_tokens, max_seqs=args.max_seqs,
-                           prefill_chunk=args.prefill_chunk)
+                           prefill_chunk=args.prefill_chunk, cuda_graphs=not args.no_cuda_graphs)
 
 
 def _sampling(args):

@@ -117,6 +117,17 @@ def build_batch(entries: Sequence[StepEntry], cache: CacheManager, vocab_size: i
         state_slots=np.asarray(slots, dtype=np.int32), logit_rows=np.asarray(rows, dtype=np.int32))
 
 
+def pad_tables(batch: StepBatch, widths: Sequence[int]) -> StepBatch:
+    """The same batch with every group's block table padded (with -1) to the given width."""
+    tables = []
+    for t, w in zip(batch.block_tables, widths):
+        if t.shape[1] < w:
+            t = np.concatenate([t, np.full((t.shape[0], w - t.shape[1]), -1, dtype=np.int32)], axis=1)
+        tables.append(t)
+    return StepBatch(batch.requests, batch.tokens, batch.positions, batch.seq_of, batch.query_start,
+                     batch.context_len, tables, batch.state_slots, batch.logit_rows)
+
+
 def attention_tiles(batch: StepBatch, tile_q: int, kind: str = "all") -> np.ndarray:
     """Cuts runs into tiles of at most ``tile_q`` consecutive queries:
     rows of (run, first token row, queries, position of the first query).
@@ -138,6 +149,7 @@ class Workspace:
         self.device = device
         self._fixed: Dict[Tuple, torch.Tensor] = {}
         self._dyn: Dict[Tuple, torch.Tensor] = {}
+        self.version = 0          # grows whenever a buffer is (re)allocated: captured graphs hold the old pointers
 
     def fixed(self, name: str, shape: Tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:
         key = (name, tuple(shape), dtype)
@@ -145,6 +157,7 @@ class Workspace:
         if t is None:
             t = torch.empty(shape, dtype=dtype, device=self.device)
             self._fixed[key] = t
+            self.version += 1
         return t
 
     def dynamic(self, name: str, numel: int, dtype: torch.dtype) -> torch.Tensor:
@@ -153,6 +166,7 @@ class Workspace:
         if t is None or t.numel() < numel:
             t = torch.empty(max(numel, 1), dtype=dtype, device=self.device)
             self._dyn[key] = t
+            self.version += 1
         return t
 
     def bytes(self) -> int:
@@ -178,7 +192,8 @@ class StepContext:
     """Device form of a step: index arrays (one host-to-device copy), scratch, stream."""
 
     def __init__(self, batch: StepBatch, workspace: Workspace, device: torch.device, max_tokens: int,
-                 err: Optional[torch.Tensor] = None, tile_sizes: Sequence[int] = ()):
+                 err: Optional[torch.Tensor] = None, tile_sizes: Sequence[int] = (),
+                 max_context: Optional[int] = None, upload: bool = True):
         self.batch = batch
         self.workspace = workspace
         self.device = device
@@ -186,7 +201,8 @@ class StepContext:
         self.T, self.S, self.R = batch.T, batch.S, batch.R
         if self.T > max_tokens:
             raise BatchError(f"the step has {self.T} tokens; the limit is {max_tokens}")
-        self.max_context = int(batch.context_len.max())
+        # an upper bound of the cached length may be given (graph replays are built for a bucket)
+        self.max_context = int(max_context) if max_context is not None else int(batch.context_len.max())
         self.err = err
         self.stream = torch.cuda.current_stream(device).cuda_stream
         # host views parts may read (toy mixers, planners)
@@ -204,13 +220,15 @@ class StepContext:
             offs.append(total)
             total += (p.size + 7) // 8 * 8          # keep every array 32-byte aligned
         total = max(total, 8)
-        host, event = workspace.pinned_ints(total)
-        hn = host.numpy()
-        for p, o in zip(parts, offs):
-            hn[o:o + p.size] = p
-        dev = workspace.dynamic("step.ints", total, torch.int32)
-        dev[:total].copy_(host[:total], non_blocking=True)
-        event.record()
+        dev = workspace.dynamic("step.ints", max(total, 1 << 16), torch.int32)
+        self.ints = dev
+        if upload:
+            host, event = workspace.pinned_ints(total)
+            hn = host.numpy()
+            for p, o in zip(parts, offs):
+                hn[o:o + p.size] = p
+            dev[:total].copy_(host[:total], non_blocking=True)
+            event.record()
 
         def view(i, shape=None):
             p = parts[i]

@@ -13,6 +13,7 @@ from typing import Hashable, List, Optional, Sequence
 
 import torch
 
+from .. import ops
 from ..cache.manager import CacheManager
 from ..cache.storage import CacheStorage
 from ..config.registry import load_config
@@ -20,7 +21,7 @@ from ..config.spec import ModelSpec
 from ..model.causal_lm import CausalLM
 from ..parts.base import Runtime
 from ..weights.loader import WeightStore
-from .batch import BatchError, StepBatch, StepContext, StepEntry, Workspace, build_batch
+from .batch import BatchError, StepBatch, StepContext, StepEntry, Workspace, build_batch, pad_tables
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
            "f32": torch.float32}
@@ -44,7 +45,7 @@ class DeviceError(RuntimeError):
 class ModelRunner:
     def __init__(self, spec: ModelSpec, store: WeightStore, dtype="bfloat16", device="cuda:0",
                  capacity_tokens: int = 4096, max_batch_tokens: int = 2048, max_requests: int = 64,
-                 page_tokens: int = 16):
+                 page_tokens: int = 16, cuda_graphs: bool = True):
         if not torch.cuda.is_available():
             raise DeviceError("no CUDA device: this engine runs its model on a B200 only (there is no CPU path)")
         self.device = torch.device(device)
@@ -60,6 +61,14 @@ class ModelRunner:
         self.workspace = Workspace(self.device)
         self.err = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.steps = 0
+        # decode steps (one token per run) are captured into CUDA graphs, one per (runs, wanted rows,
+        # context bucket); the reference does the same for its decode steps (src/backend/cuda/cuda_backend.cu:376-454)
+        self.cuda_graphs = bool(cuda_graphs)
+        self.graph_context_bucket = 512
+        self.graph_max_runs = 256
+        self._graphs = {}
+        self._graph_seen = set()
+        self.graph_replays = 0
 
     # -------------------------------------------------------------- constructors
     @classmethod
@@ -96,12 +105,56 @@ class ModelRunner:
     def run_batch(self, batch: StepBatch) -> Optional[torch.Tensor]:
         if batch.T > self.max_batch_tokens:
             raise BatchError(f"the step has {batch.T} tokens; the limit is {self.max_batch_tokens}")
-        ctx = StepContext(batch, self.workspace, self.device, self.max_batch_tokens, err=self.err,
-                          tile_sizes=self.model.tile_requests())
-        logits = self.model.forward(ctx, self.storage)
+        if self.cuda_graphs and batch.T == batch.S and batch.S <= self.graph_max_runs:
+            logits = self._run_decode_graph(batch)
+        else:
+            ctx = StepContext(batch, self.workspace, self.device, self.max_batch_tokens, err=self.err,
+                              tile_sizes=self.model.tile_requests())
+            logits = self.model.forward(ctx, self.storage)
         for s, req in enumerate(batch.requests):
             self.cache.advance(req, int(batch.context_len[s]))
         self.steps += 1
+        return logits
+
+    def _run_decode_graph(self, batch: StepBatch) -> Optional[torch.Tensor]:
+        """A decode step through a captured graph.  The first step of a shape runs eagerly (it also
+        allocates every buffer), the second is captured, later ones only upload the step's integers
+        and replay.  A graph is built for a bucket of context lengths: block tables are padded to
+        the bucket's width and the attention splits cover the bucket, so any shorter context fits."""
+        bucket = self.graph_context_bucket
+        ctx_bucket = (int(batch.context_len.max()) + bucket - 1) // bucket * bucket
+        widths = [max(1, ctx_bucket // self.cache.page_tokens) if g.paged else 1 for g in self.cache.groups]
+        widths = [max(w, t.shape[1]) for w, t in zip(widths, batch.block_tables)]
+        key = (batch.S, batch.R, ctx_bucket, tuple(widths))
+        padded = pad_tables(batch, widths)
+        tiles = self.model.tile_requests()
+        ctx = StepContext(padded, self.workspace, self.device, self.max_batch_tokens, err=self.err, tile_sizes=tiles,
+                          max_context=ctx_bucket)          # uploads this step's integers
+        entry = self._graphs.get(key)
+        if entry is not None and entry[1] == self.workspace.version and entry[3] == ctx.ints.data_ptr():
+            entry[0].replay()
+            self.graph_replays += 1
+            ops.add_launches(entry[4])
+            return entry[2]
+        if key not in self._graph_seen:
+            self._graph_seen.add(key)
+            return self.model.forward(ctx, self.storage)
+        version = self.workspace.version
+        n0 = ops.launch_count()
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            cap = StepContext(padded, self.workspace, self.device, self.max_batch_tokens, err=self.err,
+                              tile_sizes=tiles, max_context=ctx_bucket, upload=False)
+            logits = self.model.forward(cap, self.storage)
+        if self.workspace.version != version or cap.ints.data_ptr() != ctx.ints.data_ptr():
+            # a buffer was (re)allocated while capturing: the graph holds stale pointers; run eagerly
+            self._graph_seen.discard(key)
+            return self.model.forward(ctx, self.storage)
+        if len(self._graphs) > 64:
+            self._graphs.clear()
+        self._graphs[key] = (graph, version, logits, ctx.ints.data_ptr(), ops.launch_count() - n0)
+        graph.replay()
+        self.graph_replays += 1
         return logits
 
     def check_device(self) -> None:

@@ -69,6 +69,12 @@ def launch_count() -> int:
     return _launches
 
 
+def add_launches(n: int) -> None:
+    """A replayed CUDA graph launches the kernels that were captured into it."""
+    global _launches
+    _launches += n
+
+
 def _call(lib, fn, *args):
     global _launches
     _launches += 1

@@ -105,3 +105,36 @@ def test_preemption_on_the_device_keeps_the_tokens(tiny_model_dirs):
     assert llm.stats.preemptions > 0
     for p, o in zip(prompts, outs):
         assert o == plain.greedy(p, 30)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_graph_replay_equals_eager_decoding(dtype, tiny_model_dirs):
+    """Decode steps through captured graphs give the logits that eager steps give, while the batch
+    changes size and contexts grow across a graph's context bucket."""
+    from ember_b200 import StepEntry
+    name = "b"
+    rng = np.random.default_rng(12)
+    seqs = {i: rng.integers(0, 1000, size=n).tolist() for i, n in enumerate((90, 140, 200))}
+
+    def run(graphs):
+        llm = load(tiny_model_dirs, name, dtype, cuda_graphs=graphs, kv_cache_tokens=1024)
+        r = llm.runner
+        r.graph_context_bucket = 64
+        out = []
+        for i, toks in seqs.items():
+            r.admit(i), r.reserve(i, 40)
+            r.step([StepEntry(i, toks[:40], ())])
+        for t in range(40, 90):                       # three runs decode together, then two, then one
+            live = [i for i, toks in seqs.items() if t < len(toks)]
+            for i in live:
+                assert r.reserve(i, 1)
+            lg = r.step([StepEntry(i, [seqs[i][t]], (0,)) for i in live])
+            out.append(lg.float().cpu().numpy().copy())
+        r.check_device()
+        return out, r.graph_replays
+
+    eager, n0 = run(False)
+    graphed, n1 = run(True)
+    assert n0 == 0 and n1 > 30
+    for a, b in zip(eager, graphed):
+        assert np.array_equal(a, b) if dtype == "float32" else np.allclose(a, b, rtol=0, atol=1e-2 * np.abs(a).max())
