@@ -80,12 +80,9 @@ def _build_dir_locked() -> str:
 
 def _digest(name: str) -> str:
     h = hashlib.sha256()
-    for fn in (name + ".cu", "common.cuh"):
+    headers = sorted(f for f in os.listdir(_HERE) if f.endswith((".cuh", ".h")))
+    for fn in [name + ".cu"] + headers:
         with open(os.path.join(_HERE, fn), "rb") as f:
-            h.update(f.read())
-    extra = os.path.join(_HERE, name + ".cuh")
-    if os.path.isfile(extra):
-        with open(extra, "rb") as f:
             h.update(f.read())
     h.update(" ".join(ARCH_FLAGS + NVCC_FLAGS + _EXTRA_LIBS.get(name, [])).encode())
     return h.hexdigest()[:16]

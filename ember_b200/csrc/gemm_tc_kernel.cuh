@@ -1,0 +1,320 @@
+// Device code and host helpers of the tcgen05/TMA bf16 matrix product, shared by the files that
+// export entry points for it (gemm_tc.cu, no_alloc.cu).  See gemm_tc.cu for the design.
+#pragma once
+
+#include <cuda.h>
+
+#include <mutex>
+
+#include "common.cuh"
+
+namespace ember {
+
+constexpr int TILE_ROWS = 128;     // UMMA M
+constexpr int TILE_K = 64;         // bf16 elements per stage along K = one 128-byte swizzle row
+constexpr int UMMA_K = 16;
+constexpr int GEMM_THREADS = 192;
+constexpr int MAX_STAGES = 8;
+constexpr unsigned WAIT_LIMIT = 1u << 24;
+
+struct GemmTcParams {
+    int M, N, K;
+    int swapped;          // 0: accumulator rows are tokens; 1: accumulator rows are weight rows
+    int block_cols;       // accumulator columns per tile (multiple of 16, <= 256)
+    int stages;
+    int num_k_blocks;     // ceil(K / TILE_K)
+    int k_blocks_per_split;
+    int epilogue;         // 0 store bf16, 1 store fp32, 2 add fp32, 3 silu(gate)*up -> bf16
+    void* out;
+    int ldc;
+    float* accum;         // split-K target: fp32 [M, accum_ld] (the residual itself for epilogue 2)
+    int accum_ld;
+    int tmem_cols;
+    int* err;
+};
+
+// ------------------------------------------------------------------------------ PTX helpers
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n}"
+        : "=r"(ok)
+        : "r"(smem_u32(bar)), "r"(parity)
+        : "memory");
+    return ok != 0;
+}
+// Bounded wait; returns false (and raises the abort flag) if the limit is reached.
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+    for (unsigned i = 0; i < WAIT_LIMIT; i++) {
+        if (mbar_try_wait(bar, parity)) return true;
+        if ((i & 1023u) == 1023u && *abort_flag) return false;
+    }
+    *abort_flag = 1;
+    return false;
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(smem_u32(dst)), "l"((uint64_t)map), "r"(smem_u32(bar)), "r"(x), "r"(y)
+        : "memory");
+}
+__device__ __forceinline__ void tcgen05_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tcgen05_mma_bf16(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "setp.ne.b32 p, %4, 0;\n"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
+    uint32_t r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; i++) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory matrix descriptor of a K-major bf16 tile whose rows are 128 bytes, written by TMA
+// with the 128-byte swizzle: 8-row groups are 1024 bytes apart (stride byte offset), descriptor
+// version 1, layout type 2 (128-byte swizzle).  The leading byte offset is not used by this layout.
+__device__ __forceinline__ uint64_t umma_desc_sw128(const void* tile) {
+    const uint64_t addr = (uint64_t)(smem_u32(tile) >> 4) & 0x3FFFull;
+    return addr | (1ull << 16) | ((uint64_t)(1024 >> 4) << 32) | (1ull << 46) | (2ull << 61);
+}
+
+// Instruction descriptor: fp32 accumulate, bf16 A and B, both K-major, M = 128, N = block_cols.
+__host__ __device__ __forceinline__ uint32_t umma_idesc(int n) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(TILE_ROWS >> 4) << 24);
+}
+
+__device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + __expf(-g)) * u; }
+
+// ------------------------------------------------------------------------------------ kernel
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant__ CUtensorMap map_cols,
+               const GemmTcParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    // tiles need 1024-byte alignment for the 128-byte swizzle
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    const int rows_bytes = TILE_ROWS * TILE_K * 2;               // 16 KiB
+    const int cols_bytes = p.block_cols * TILE_K * 2;
+    const int stage_bytes = rows_bytes + ((cols_bytes + 1023) & ~1023);
+    uint64_t* full_bar = (uint64_t*)(smem + (size_t)p.stages * stage_bytes);
+    uint64_t* empty_bar = full_bar + MAX_STAGES;
+    uint64_t* tmem_full_bar = empty_bar + MAX_STAGES;
+    uint32_t* tmem_base_slot = (uint32_t*)(tmem_full_bar + 1);
+    volatile int* abort_flag = (volatile int*)(tmem_base_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int row_tile = blockIdx.x, col_tile = blockIdx.y, split = blockIdx.z;
+    const int kb0 = split * p.k_blocks_per_split;
+    const int kb1 = min(p.num_k_blocks, kb0 + p.k_blocks_per_split);
+    const int n_kb = kb1 - kb0;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < p.stages; s++) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        mbar_init(tmem_full_bar, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_base_slot)), "r"(p.tmem_cols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_d = *tmem_base_slot;
+
+    if (warp == 0) {
+        // ---------------------------------------------------------------- TMA producer
+        if (lane == 0 && n_kb > 0) {
+            for (int i = 0; i < n_kb; i++) {
+                const int s = i % p.stages;
+                const uint32_t phase = (uint32_t)(i / p.stages) & 1u;
+                if (!mbar_wait(&empty_bar[s], phase ^ 1u, abort_flag)) break;
+                uint8_t* a = smem + (size_t)s * stage_bytes;
+                uint8_t* b = a + rows_bytes;
+                mbar_expect_tx(&full_bar[s], (uint32_t)(rows_bytes + cols_bytes));
+                tma_load_2d(a, &map_rows, &full_bar[s], (kb0 + i) * TILE_K, row_tile * TILE_ROWS);
+                tma_load_2d(b, &map_cols, &full_bar[s], (kb0 + i) * TILE_K, col_tile * p.block_cols);
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA issuer
+        if (lane == 0 && n_kb > 0) {
+            const uint32_t idesc = umma_idesc(p.block_cols);
+            bool ok = true;
+            for (int i = 0; i < n_kb && ok; i++) {
+                const int s = i % p.stages;
+                const uint32_t phase = (uint32_t)(i / p.stages) & 1u;
+                ok = mbar_wait(&full_bar[s], phase, abort_flag);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                uint8_t* a = smem + (size_t)s * stage_bytes;
+                const uint64_t da = umma_desc_sw128(a), db = umma_desc_sw128(a + rows_bytes);
+#pragma unroll
+                for (int k = 0; k < TILE_K / UMMA_K; k++) {
+                    // advancing 16 bf16 = 32 bytes inside the swizzled row: +2 in the 16-byte address field
+                    tcgen05_mma_bf16(tmem_d, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, (i > 0 || k > 0) ? 1u : 0u);
+                }
+                tcgen05_commit(&empty_bar[s]);      // the stage is free once these MMAs have read it
+            }
+            tcgen05_commit(tmem_full_bar);          // the accumulator is complete once all MMAs have finished
+        }
+    } else if (n_kb > 0) {
+        // -------------------------------------------------------------------- epilogue
+        const int quad = warp & 3;                  // TMEM lane quadrant this warp may read
+        const bool ok = mbar_wait(tmem_full_bar, 0, abort_flag);
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        if (ok) {
+            const int r = quad * 32 + lane;         // accumulator row of this thread
+            const uint32_t taddr_row = tmem_d + ((uint32_t)(quad * 32) << 16);
+            const bool splitk = gridDim.z > 1;
+            for (int c0 = 0; c0 < p.block_cols; c0 += 16) {
+                float v[16];
+                tmem_ld16(taddr_row + (uint32_t)c0, v);
+                if (!p.swapped) {
+                    const int m = row_tile * TILE_ROWS + r;
+                    const int n0 = col_tile * p.block_cols + c0;
+                    if (m >= p.M || n0 >= p.N) continue;
+                    const int nv = min(16, p.N - n0);
+                    if (splitk) {
+                        float* dst = p.accum + (size_t)m * p.accum_ld + n0;
+                        for (int j = 0; j < nv; j++) atomicAdd(dst + j, v[j]);
+                    } else if (p.epilogue == 0) {
+                        __nv_bfloat16* dst = (__nv_bfloat16*)p.out + (size_t)m * p.ldc + n0;
+                        if (nv == 16 && (((uintptr_t)dst) & 15) == 0) {
+                            uint4 q[2];
+                            __nv_bfloat162* h = (__nv_bfloat162*)q;
+#pragma unroll
+                            for (int j = 0; j < 8; j++) h[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+                            ((uint4*)dst)[0] = q[0];
+                            ((uint4*)dst)[1] = q[1];
+                        } else {
+                            for (int j = 0; j < nv; j++) dst[j] = __float2bfloat16_rn(v[j]);
+                        }
+                    } else if (p.epilogue == 1 || p.epilogue == 2) {
+                        float* dst = (float*)p.out + (size_t)m * p.ldc + n0;
+                        if (nv == 16 && (((uintptr_t)dst) & 15) == 0) {
+#pragma unroll
+                            for (int j = 0; j < 4; j++) {
+                                float4 o = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                                if (p.epilogue == 2) {
+                                    const float4 c = ((float4*)dst)[j];
+                                    o.x += c.x; o.y += c.y; o.z += c.z; o.w += c.w;
+                                }
+                                ((float4*)dst)[j] = o;
+                            }
+                        } else {
+                            for (int j = 0; j < nv; j++) dst[j] = p.epilogue == 2 ? dst[j] + v[j] : v[j];
+                        }
+                    } else {
+                        __nv_bfloat16* dst = (__nv_bfloat16*)p.out + (size_t)m * p.ldc + (n0 >> 1);
+                        for (int j = 0; j + 1 < nv; j += 2) dst[j >> 1] = __float2bfloat16_rn(silu_mul(v[j], v[j + 1]));
+                    }
+                } else {
+                    const int n = row_tile * TILE_ROWS + r;
+                    const int m0 = col_tile * p.block_cols + c0;
+                    if (p.epilogue == 3 && !splitk) {
+                        // gate rows are even, up rows odd: neighbours in the warp
+#pragma unroll
+                        for (int j = 0; j < 16; j++) {
+                            const float other = __shfl_xor_sync(0xffffffffu, v[j], 1);
+                            const int m = m0 + j;
+                            if ((lane & 1) == 0 && n + 1 < p.N && m < p.M)
+                                ((__nv_bfloat16*)p.out)[(size_t)m * p.ldc + (n >> 1)] = __float2bfloat16_rn(silu_mul(v[j], other));
+                        }
+                        continue;
+                    }
+                    if (n >= p.N) continue;
+#pragma unroll
+                    for (int j = 0; j < 16; j++) {
+                        const int m = m0 + j;
+                        if (m >= p.M) break;
+                        if (splitk) {
+                            atomicAdd(p.accum + (size_t)m * p.accum_ld + n, v[j]);
+                        } else if (p.epilogue == 0) {
+                            ((__nv_bfloat16*)p.out)[(size_t)m * p.ldc + n] = __float2bfloat16_rn(v[j]);
+                        } else if (p.epilogue == 1) {
+                            ((float*)p.out)[(size_t)m * p.ldc + n] = v[j];
+                        } else {
+                            float* dst = (float*)p.out + (size_t)m * p.ldc + n;
+                            *dst = *dst + v[j];
+                        }
+                    }
+                }
+            }
+        }
+        asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    }
+
+    __syncthreads();
+    if (threadIdx.x == 0 && *abort_flag && p.err) atomicOr(p.err, EMBER_ERR_WAIT_LIMIT);
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(p.tmem_cols) : "memory");
+    }
+}
+
+// Split-K finalize for the store epilogues: out = epilogue(accum), accum = 0.
+__global__ void gemm_tc_finalize_kernel(float* __restrict__ accum, int accum_ld, void* __restrict__ out, int ldc, int M,
+                                        int N, int epilogue) {
+    const int n_out = epilogue == 3 ? N / 2 : N;
+    const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (size_t)M * n_out) return;
+    const int m = (int)(idx / n_out), j = (int)(idx % n_out);
+    float* a = accum + (size_t)m * accum_ld;
+    if (epilogue == 3) {
+        const float g = a[2 * j], u = a[2 * j + 1];
+        a[2 * j] = 0.0f;
+        a[2 * j + 1] = 0.0f;
+        ((__nv_bfloat16*)out)[(size_t)m * ldc + j] = __float2bfloat16_rn(silu_mul(g, u));
+    } else {
+        const float c = a[j];
+        a[j] = 0.0f;
+        if (epilogue == 0) ((__nv_bfloat16*)out)[(size_t)m * ldc + j] = __float2bfloat16_rn(c);
+        else ((float*)out)[(size_t)m * ldc + j] = c;
+    }
+}
+
+// ------------------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    static std::once_flag once;
+    std::call_once(once, [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+            q == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)p;
+    });
+    return fn;
+}
+
+}  // namespace ember
