@@ -43,6 +43,8 @@ template <typename T, int NC>
 __global__ void __launch_bounds__(ATT_WARPS * 32)
 attention_tile_kernel(AttnParams p) {
     extern __shared__ float smem[];
+    pdl_launch_dependents();
+    pdl_wait();
     const int D = p.D, DP = D + 1;
     float* Ks = smem;                       // [KT][D+1]
     float* Vs = Ks + ATT_KT * DP;           // [KT][D]
@@ -170,6 +172,8 @@ attention_tile_kernel(AttnParams p) {
 template <typename T>
 __global__ void attention_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                          T* __restrict__ out, int n_splits, int D) {
+    pdl_launch_dependents();
+    pdl_wait();
     const size_t th = blockIdx.x;
     const float* ml = part_ml + th * n_splits * 2;
     float M = -INFINITY;
@@ -202,7 +206,7 @@ int launch_attention(const AttnParams& p, int n_tiles, int T_tokens, cudaStream_
             cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
             if (e != cudaSuccess) return fail("attention: shared memory %zu: %s", smem, cudaGetErrorString(e));
         }
-        kernel<<<grid, ATT_WARPS * 32, smem, st>>>(p);
+        launch_kernel(kernel, grid, ATT_WARPS * 32, smem, st, p);
         return check_launch("attention");
     };
     int rc;
@@ -213,8 +217,8 @@ int launch_attention(const AttnParams& p, int n_tiles, int T_tokens, cudaStream_
     if (rc) return rc;
     (void)G;
     if (p.n_splits > 1) {
-        attention_combine_kernel<T><<<(unsigned)((size_t)T_tokens * p.n_heads), D >= 128 ? 128 : 64, 0, st>>>(
-            p.part_o, p.part_ml, (T*)p.out, p.n_splits, D);
+        launch_kernel(attention_combine_kernel<T>, (unsigned)((size_t)T_tokens * p.n_heads), D >= 128 ? 128 : 64, 0, st,
+                      (const float*)p.part_o, (const float*)p.part_ml, (T*)p.out, p.n_splits, D);
         return check_launch("attention_combine");
     }
     return 0;

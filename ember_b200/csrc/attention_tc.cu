@@ -33,7 +33,8 @@ EMBER_DEFINE_LAST_ERROR
 namespace ember {
 
 constexpr int KT = 64;                 // keys per shared-memory tile
-constexpr int ATC_THREADS = 128;
+constexpr int ATC_CONSUMERS = 128;     // four warps multiply
+constexpr int ATC_THREADS = 160;       // + one warp that only fetches pages
 constexpr unsigned ATC_WAIT_LIMIT = 1u << 24;
 constexpr float LOG2E = 1.4426950408889634f;
 
@@ -79,6 +80,9 @@ __device__ __forceinline__ void atc_mbar_init(uint64_t* bar, int count) {
 __device__ __forceinline__ void atc_expect_tx(uint64_t* bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(s32(bar)), "r"(bytes) : "memory");
 }
+__device__ __forceinline__ void atc_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(s32(bar)) : "memory");
+}
 __device__ __forceinline__ bool atc_try_wait(uint64_t* bar, uint32_t parity) {
     uint32_t ok;
     asm volatile(
@@ -115,14 +119,18 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
     constexpr int TILE_BYTES = HALVES * HALF_BYTES; // Q, K or V tile
     constexpr int NKG = DECODE ? 2 : 8;             // groups of 8 keys a warp scores per tile
     constexpr int ND = D / 8;                       // output column groups of 8
+    constexpr int NSTAGE = DECODE ? 3 : 2;          // key/value tiles in flight or in use
+    constexpr int QROWS = DECODE ? 16 : 64;         // query rows kept in shared memory
+    constexpr int Q_HALF_BYTES = QROWS * 128;
 
     extern __shared__ uint8_t atc_smem_raw[];
     uint8_t* smem = (uint8_t*)(((uintptr_t)atc_smem_raw + 1023) & ~(uintptr_t)1023);
-    uint8_t* q_s = smem;
-    uint8_t* k_s = q_s + TILE_BYTES;                // two buffers
-    uint8_t* v_s = k_s + 2 * TILE_BYTES;            // two buffers
-    uint64_t* full_bar = (uint64_t*)(v_s + 2 * TILE_BYTES);
-    volatile int* abort_flag = (volatile int*)(full_bar + 2);
+    uint8_t* q_s = smem;                            // HALVES x [QROWS][64]
+    uint8_t* k_s = q_s + ((HALVES * Q_HALF_BYTES + 1023) & ~1023);   // NSTAGE buffers
+    uint8_t* v_s = k_s + NSTAGE * TILE_BYTES;       // NSTAGE buffers
+    uint64_t* full_bar = (uint64_t*)(v_s + NSTAGE * TILE_BYTES);
+    uint64_t* empty_bar = full_bar + NSTAGE;
+    volatile int* abort_flag = (volatile int*)(empty_bar + NSTAGE);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g8 = lane >> 2, t4 = lane & 3;
@@ -143,47 +151,69 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
     const int n_kt = hi > k_begin ? (hi - k_begin + KT - 1) / KT : 0;
 
     if (threadIdx.x == 0) {
-        atc_mbar_init(&full_bar[0], 1);
-        atc_mbar_init(&full_bar[1], 1);
+        for (int i = 0; i < NSTAGE; i++) {
+            atc_mbar_init(&full_bar[i], 1);
+            atc_mbar_init(&empty_bar[i], 4);        // one arrival per multiplying warp
+        }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
 
+    pdl_launch_dependents();
+    pdl_wait();       // queries and the newest keys are written by the kernel before this one
+
     // ---- query rows -> shared memory (row r = token r / G, head kvh * G + r % G), zero beyond `rows`
-    for (int idx = threadIdx.x; idx < KT * (D / 8); idx += ATC_THREADS) {
+    for (int idx = threadIdx.x; idx < QROWS * (D / 8); idx += ATC_THREADS) {
         const int r = idx / (D / 8), c = idx % (D / 8);
         uint4 val = make_uint4(0, 0, 0, 0);
         if (r < rows) {
             const int qi = r / G, g = r - qi * G;
             val = *reinterpret_cast<const uint4*>(p.q + ((size_t)(row0 + qi) * p.n_heads + kvh * G + g) * D + c * 8);
         }
-        *reinterpret_cast<uint4*>(q_s + (c >> 3) * HALF_BYTES + swz(r, c & 7)) = val;
+        *reinterpret_cast<uint4*>(q_s + (c >> 3) * Q_HALF_BYTES + swz(r, c & 7)) = val;
     }
     __syncthreads();
 
     const int* bt = p.block_table + (size_t)seq * p.max_blocks;
     const int boxes = KT / p.page;
-    auto issue = [&](int it) {
-        const int b = it & 1;
-        atc_expect_tx(&full_bar[b], (uint32_t)(2 * TILE_BYTES));
-        const int k0 = k_begin + it * KT;
-        for (int bx = 0; bx < boxes; bx++) {
-            int blk = bt[min((k0 + bx * p.page) / p.page, p.max_blocks - 1)];
-            if (blk < 0 || blk >= p.num_pages) blk = 0;     // beyond the context or given back: masked below
-            const int y = (blk * p.n_kv + kvh) * p.page;
-#pragma unroll
-            for (int h = 0; h < HALVES; h++) {
-                const int off = h * HALF_BYTES + bx * p.page * 128;
-                atc_tma_2d(k_s + b * TILE_BYTES + off, &map_k, &full_bar[b], h * 64, y);
-                atc_tma_2d(v_s + b * TILE_BYTES + off, &map_v, &full_bar[b], h * 64, y);
+
+    if (warp == 4) {
+        // ---------------------------------------------------------------- page fetcher
+        // Lane i fetches box i of every tile (its page id is looked up one tile ahead); the warp
+        // runs up to NSTAGE tiles ahead of the multiplying warps and never waits for them otherwise.
+        auto page_row = [&](int it) {
+            int blk = 0;
+            if (lane < boxes && it < n_kt) {
+                blk = bt[min((k_begin + it * KT + lane * p.page) / p.page, p.max_blocks - 1)];
+                if (blk < 0 || blk >= p.num_pages) blk = 0;     // beyond the context or given back: masked below
             }
+            return (blk * p.n_kv + kvh) * p.page;
+        };
+        int y = page_row(0);
+        bool ok = true;
+        for (int it = 0; it < n_kt && ok; it++) {
+            const int b = it % NSTAGE;
+            const int y_next = page_row(it + 1);
+            if (it >= NSTAGE) ok = atc_wait(&empty_bar[b], (uint32_t)(it / NSTAGE - 1) & 1u, abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            if (lane == 0) atc_expect_tx(&full_bar[b], (uint32_t)(2 * TILE_BYTES));
+            __syncwarp();
+            if (lane < boxes) {
+#pragma unroll
+                for (int h = 0; h < HALVES; h++) {
+                    const int off = h * HALF_BYTES + lane * p.page * 128;
+                    atc_tma_2d(k_s + b * TILE_BYTES + off, &map_k, &full_bar[b], h * 64, y);
+                    atc_tma_2d(v_s + b * TILE_BYTES + off, &map_v, &full_bar[b], h * 64, y);
+                }
+            }
+            y = y_next;
         }
-    };
-    if (threadIdx.x == 0 && n_kt > 0) issue(0);
+    }
 
     // ---- this warp's query fragments (16 rows x D)
-    const int wrow = DECODE ? 0 : warp * 16;
+    const int wrow = DECODE ? 0 : (warp & 3) * 16;
     uint32_t qf[D / 16][4];
     {
         const int mat = lane >> 3, rin = lane & 7;
@@ -191,7 +221,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
 #pragma unroll
         for (int kc = 0; kc < D / 16; kc++) {
             const int chunk = kc * 2 + (mat >> 1);
-            ldsm_x4(s32(q_s + (chunk >> 3) * HALF_BYTES + swz(r, chunk & 7)), qf[kc][0], qf[kc][1], qf[kc][2], qf[kc][3]);
+            ldsm_x4(s32(q_s + (chunk >> 3) * Q_HALF_BYTES + swz(r, chunk & 7)), qf[kc][0], qf[kc][1], qf[kc][2], qf[kc][3]);
         }
     }
     const int r_a = wrow + g8, r_b = wrow + g8 + 8;          // the two rows this thread holds
@@ -203,10 +233,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
     for (int j = 0; j < ND; j++) o[j][0] = o[j][1] = o[j][2] = o[j][3] = 0.0f;
 
     bool alive = true;
-    for (int it = 0; it < n_kt; it++) {
-        const int b = it & 1;
-        if (threadIdx.x == 0 && it + 1 < n_kt) issue(it + 1);
-        if (alive) alive = atc_wait(&full_bar[b], (uint32_t)(it >> 1) & 1u, abort_flag);
+    for (int it = 0; it < n_kt && warp < 4; it++) {
+        const int b = it % NSTAGE;
+        if (alive) alive = atc_wait(&full_bar[b], (uint32_t)(it / NSTAGE) & 1u, abort_flag);
         if (alive) {
             const uint8_t* kb = k_s + b * TILE_BYTES;
             const uint8_t* vb = v_s + b * TILE_BYTES;
@@ -299,9 +328,12 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
                 }
             }
         }
-        __syncthreads();   // everyone is done with buffer b before the load after next overwrites it
+        __syncwarp();
+        if (lane == 0) atc_arrive(&empty_bar[b]);   // this warp is done with buffer b
     }
+    __syncthreads();       // every tile has landed and has been read: the buffers are free
     if (threadIdx.x == 0 && *abort_flag && p.err) atomicOr(p.err, EMBER_ERR_WAIT_LIMIT);
+    if (warp == 4 && !DECODE) return;
 
     if (!DECODE) {
         // ---- rows are private to a warp: normalise and store
@@ -326,14 +358,14 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
     // ---- decode: merge the four warps (each saw a quarter of the keys) through shared memory
     float* mo = reinterpret_cast<float*>(k_s);                 // [4 warps][16 rows][D]   (K/V buffers are free now)
     float* mm = reinterpret_cast<float*>(v_s);                 // [4][16] maxima, then [4][16] denominators
-    if (t4 == 0) {
+    if (warp < 4 && t4 == 0) {
         mm[warp * 16 + g8] = m_a;
         mm[warp * 16 + g8 + 8] = m_b;
         mm[64 + warp * 16 + g8] = l_a;
         mm[64 + warp * 16 + g8 + 8] = l_b;
     }
 #pragma unroll
-    for (int j = 0; j < ND; j++) {
+    for (int j = 0; j < ND && warp < 4; j++) {
         float* ra = mo + ((size_t)warp * 16 + g8) * D + j * 8 + 2 * t4;
         float* rb = mo + ((size_t)warp * 16 + g8 + 8) * D + j * 8 + 2 * t4;
         ra[0] = o[j][0]; ra[1] = o[j][1];
@@ -372,6 +404,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
 __global__ void attention_tc_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                             __nv_bfloat16* __restrict__ out, const int* __restrict__ tiles,
                                             int n_heads, int n_splits, int D) {
+    pdl_launch_dependents();
+    pdl_wait();
     const size_t th = blockIdx.x;                                          // tile * n_heads + head
     const int tile = (int)(th / n_heads), head = (int)(th % n_heads);
     const size_t oh = (size_t)tiles[tile * 4 + 1] * n_heads + head;        // the tile's single token row
@@ -479,12 +513,14 @@ EMBER_API int ember_attention_tc(const void* q, const void* k_pool, const void* 
     p.n_heads = n_heads; p.n_kv = n_kv; p.window = window; p.scale_log2 = scale * LOG2E;
     p.n_splits = n_splits; p.split_keys = split_keys; p.n_tiles = n_tiles; p.err = err;
     cudaStream_t st = (cudaStream_t)stream;
-    const size_t smem = (size_t)5 * (D / 64) * KT * 128 + 1024 + 64;
+    const size_t tile_bytes = (size_t)(D / 64) * KT * 128;
+    const size_t q_bytes = ((size_t)(D / 64) * (mode == 1 ? 16 : 64) * 128 + 1023) & ~(size_t)1023;
+    const size_t smem = q_bytes + (size_t)(mode == 1 ? 3 : 2) * 2 * tile_bytes + 1024 + 128;
     dim3 grid(n_tiles, n_kv, n_splits);
     auto run = [&](auto kernel) -> int {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return fail("attention_tc: shared memory %zu: %s", smem, cudaGetErrorString(e));
-        kernel<<<grid, ATC_THREADS, smem, st>>>(mk, mv, p);
+        launch_kernel(kernel, grid, ATC_THREADS, smem, st, mk, mv, p);
         return check_launch("attention_tc");
     };
     int rc;
@@ -492,8 +528,8 @@ EMBER_API int ember_attention_tc(const void* q, const void* k_pool, const void* 
     else rc = mode == 1 ? run(attention_tc_kernel<1, true>) : run(attention_tc_kernel<1, false>);
     if (rc) return rc;
     if (n_splits > 1) {
-        attention_tc_combine_kernel<<<(unsigned)((size_t)n_tiles * n_heads), D, 0, st>>>(part_o, part_ml, (__nv_bfloat16*)out,
-                                                                                     tiles, n_heads, n_splits, D);
+        launch_kernel(attention_tc_combine_kernel, (unsigned)((size_t)n_tiles * n_heads), D, 0, st, (const float*)part_o,
+                      (const float*)part_ml, (__nv_bfloat16*)out, tiles, n_heads, n_splits, D);
         return check_launch("attention_tc_combine");
     }
     return 0;

@@ -16,6 +16,8 @@ namespace ember {
 template <typename TW>
 __global__ void embed_kernel(const int* __restrict__ tokens, const TW* __restrict__ table,
                              float* __restrict__ out, int H, int V, int* __restrict__ err) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.x;
     const int tok = tokens[t];
     float* o = out + (size_t)t * H;
@@ -36,6 +38,8 @@ template <typename TO>
 __global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restrict__ rows,
                                const float* __restrict__ w, float eps, TO* __restrict__ out, int H) {
     __shared__ float scratch[32];
+    pdl_launch_dependents();
+    pdl_wait();
     const int r = blockIdx.x;
     const float* in = x + (size_t)(rows ? rows[r] : r) * H;
     float ss = 0.0f;
@@ -66,6 +70,8 @@ __global__ void qk_norm_rope_store_kernel(
     T* __restrict__ q_out, T* __restrict__ k_pool, T* __restrict__ v_pool, int write_kv,
     int* __restrict__ err) {
     extern __shared__ float smem[];
+    pdl_launch_dependents();
+    pdl_wait();
     const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x;
     const int slot = blockIdx.y * warps + warp;
@@ -121,6 +127,8 @@ __global__ void qk_norm_rope_store_kernel(
 // out[m, j] = silu(x[m, 2j]) * x[m, 2j+1] for an unfused gate/up product (interleaved rows).
 template <typename T>
 __global__ void silu_mul_interleaved_kernel(const T* __restrict__ x, T* __restrict__ out, size_t n_out) {
+    pdl_launch_dependents();
+    pdl_wait();
     size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (i >= n_out) return;
     const float g = to_float(x[2 * i]), u = to_float(x[2 * i + 1]);
@@ -138,9 +146,9 @@ EMBER_API int ember_embed(const int* tokens, const void* table, int table_dtype,
     cudaStream_t st = (cudaStream_t)stream;
     const int threads = H >= 1024 ? 256 : 128;
     if (table_dtype == EMBER_F32)
-        embed_kernel<float><<<T, threads, 0, st>>>(tokens, (const float*)table, out, H, V, err);
+        launch_kernel(embed_kernel<float>, T, threads, 0, st, tokens, (const float*)table, out, H, V, err);
     else if (table_dtype == EMBER_BF16)
-        embed_kernel<__nv_bfloat16><<<T, threads, 0, st>>>(tokens, (const __nv_bfloat16*)table, out, H, V, err);
+        launch_kernel(embed_kernel<__nv_bfloat16>, T, threads, 0, st, tokens, (const __nv_bfloat16*)table, out, H, V, err);
     else
         return fail("embed: unsupported table dtype %d", table_dtype);
     return check_launch("embed");
@@ -153,9 +161,9 @@ EMBER_API int ember_rmsnorm(const float* x, const int* rows, const float* w, flo
     cudaStream_t st = (cudaStream_t)stream;
     const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
     if (out_dtype == EMBER_F32)
-        rmsnorm_kernel<float><<<n_rows, threads, 0, st>>>(x, rows, w, eps, (float*)out, H);
+        launch_kernel(rmsnorm_kernel<float>, n_rows, threads, 0, st, x, rows, w, eps, (float*)out, H);
     else if (out_dtype == EMBER_BF16)
-        rmsnorm_kernel<__nv_bfloat16><<<n_rows, threads, 0, st>>>(x, rows, w, eps, (__nv_bfloat16*)out, H);
+        launch_kernel(rmsnorm_kernel<__nv_bfloat16>, n_rows, threads, 0, st, x, rows, w, eps, (__nv_bfloat16*)out, H);
     else
         return fail("rmsnorm: unsupported output dtype %d", out_dtype);
     return check_launch("rmsnorm");
@@ -179,11 +187,11 @@ EMBER_API int ember_qk_norm_rope_store(const void* qkv, int dtype, int T, int ld
     dim3 grid(T, (slots + warps - 1) / warps);
     const size_t smem = (size_t)warps * D * sizeof(float);
     if (dtype == EMBER_F32)
-        qk_norm_rope_store_kernel<float><<<grid, warps * 32, smem, st>>>(
+        launch_kernel(qk_norm_rope_store_kernel<float>, grid, warps * 32, smem, st,
             (const float*)qkv, ld, n_heads, n_kv, D, q_norm_w, k_norm_w, eps, inv_freq, rotary, positions, seq_of,
             block_table, max_blocks, page, num_pages, (float*)q_out, (float*)k_pool, (float*)v_pool, write_kv, err);
     else if (dtype == EMBER_BF16)
-        qk_norm_rope_store_kernel<__nv_bfloat16><<<grid, warps * 32, smem, st>>>(
+        launch_kernel(qk_norm_rope_store_kernel<__nv_bfloat16>, grid, warps * 32, smem, st,
             (const __nv_bfloat16*)qkv, ld, n_heads, n_kv, D, q_norm_w, k_norm_w, eps, inv_freq, rotary, positions,
             seq_of, block_table, max_blocks, page, num_pages, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool,
             (__nv_bfloat16*)v_pool, write_kv, err);
@@ -197,9 +205,9 @@ EMBER_API int ember_silu_mul_interleaved(const void* x, void* out, int dtype, lo
     cudaStream_t st = (cudaStream_t)stream;
     const unsigned blocks = (unsigned)((n_out + 255) / 256);
     if (dtype == EMBER_F32)
-        silu_mul_interleaved_kernel<float><<<blocks, 256, 0, st>>>((const float*)x, (float*)out, (size_t)n_out);
+        launch_kernel(silu_mul_interleaved_kernel<float>, blocks, 256, 0, st, (const float*)x, (float*)out, (size_t)n_out);
     else if (dtype == EMBER_BF16)
-        silu_mul_interleaved_kernel<__nv_bfloat16><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)out, (size_t)n_out);
+        launch_kernel(silu_mul_interleaved_kernel<__nv_bfloat16>, blocks, 256, 0, st, (const __nv_bfloat16*)x, (__nv_bfloat16*)out, (size_t)n_out);
     else
         return fail("silu_mul: unsupported dtype %d", dtype);
     return check_launch("silu_mul");

@@ -24,6 +24,8 @@ gemm_simt_kernel(const TA* __restrict__ A, int lda, const TW* __restrict__ W, in
                  const float* __restrict__ bias, void* __restrict__ Cv, int ldc, int M, int N, int K) {
     __shared__ float As[BK][BM + 4];
     __shared__ float Ws[BK][BN + 4];
+    pdl_launch_dependents();
+    pdl_wait();
     const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;  // tx -> columns, ty -> rows
     const int m0 = blockIdx.y * BM, n0 = blockIdx.x * BN;
     float acc[4][4];
@@ -91,10 +93,10 @@ int launch(const void* A, int lda, const void* W, int ldw, const float* bias, vo
     const TA* a = (const TA*)A;
     const TW* w = (const TW*)W;
     switch (epi) {
-        case 0: gemm_simt_kernel<TA, TW, 0><<<grid, 256, 0, st>>>(a, lda, w, ldw, bias, C, ldc, M, N, K); break;
-        case 1: gemm_simt_kernel<TA, TW, 1><<<grid, 256, 0, st>>>(a, lda, w, ldw, bias, C, ldc, M, N, K); break;
-        case 2: gemm_simt_kernel<TA, TW, 2><<<grid, 256, 0, st>>>(a, lda, w, ldw, bias, C, ldc, M, N, K); break;
-        case 3: gemm_simt_kernel<TA, TW, 3><<<grid, 256, 0, st>>>(a, lda, w, ldw, bias, C, ldc, M, N, K); break;
+        case 0: launch_kernel(gemm_simt_kernel<TA, TW, 0>, grid, 256, 0, st, a, lda, w, ldw, bias, C, ldc, M, N, K); break;
+        case 1: launch_kernel(gemm_simt_kernel<TA, TW, 1>, grid, 256, 0, st, a, lda, w, ldw, bias, C, ldc, M, N, K); break;
+        case 2: launch_kernel(gemm_simt_kernel<TA, TW, 2>, grid, 256, 0, st, a, lda, w, ldw, bias, C, ldc, M, N, K); break;
+        case 3: launch_kernel(gemm_simt_kernel<TA, TW, 3>, grid, 256, 0, st, a, lda, w, ldw, bias, C, ldc, M, N, K); break;
         default: return fail("gemm: unknown epilogue %d", epi);
     }
     return check_launch("gemm_simt");

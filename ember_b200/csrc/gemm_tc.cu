@@ -79,7 +79,7 @@ EMBER_API long long ember_gemm_tc_scratch_floats(int max_tokens_swapped, int N) 
 // C = A . W^T with the fused epilogue.  `scratch` is a zero-filled fp32 buffer of at least
 // min(M, 128) * N floats (used only when the K range is split; it is left zeroed).
 EMBER_API int ember_gemm_tc(const void* A, const void* W, void* out, int ldc, int M, int N, int K, int epilogue,
-                            float* scratch, long long scratch_floats, int num_sms, int* err, void* stream) {
+                            float* scratch, long long scratch_floats, int num_sms, int split_mode, int* err, void* stream) {
     if (M <= 0 || N <= 0) return 0;
     if (!ember_gemm_tc_supported(M, N, K, epilogue))
         return fail("gemm_tc: sizes M=%d N=%d K=%d (epilogue %d) are not taken; K must be a multiple of 8", M, N, K, epilogue);
@@ -101,20 +101,40 @@ EMBER_API int ember_gemm_tc(const void* A, const void* W, void* out, int ldc, in
         row_tiles = (M + TILE_ROWS - 1) / TILE_ROWS;
         col_tiles = (N + p.block_cols - 1) / p.block_cols;
     }
-    // split K when there are too few tiles to keep the memory system busy
+    // With few output tiles the K range is split so that every SM streams weights.  Two ways to
+    // sum the partial results (split_mode 0 picks one):
+    //   cluster: the splits of a tile form a thread-block cluster and are summed in shared memory,
+    //            in block order (no scratch, no second kernel) -- best for up to 16 tokens;
+    //   atomic:  fp32 atomic adds into the residual (add epilogue) or into zeroed scratch that a
+    //            small kernel converts and clears -- best for wider token tiles.
+    // The split count depends on N and K only.
+    const int tiles = row_tiles * col_tiles;
+    const bool store_epilogue = epilogue != 2;
+    const bool use_cluster = split_mode == 2 || (split_mode == 0 && p.block_cols <= 16 && store_epilogue);
     int splits = 1;
-    if (p.swapped && row_tiles * col_tiles < num_sms) {
-        const int by_sms = (num_sms + row_tiles * col_tiles - 1) / (row_tiles * col_tiles);
-        const int by_k = p.num_k_blocks / 4 > 0 ? p.num_k_blocks / 4 : 1;    // at least 4 k-blocks per split
-        splits = by_sms < by_k ? by_sms : by_k;
-        if (splits > 16) splits = 16;
-        if (splits < 1) splits = 1;
+    if (p.swapped && use_cluster) {
+        // fill the SMs once: clusters of up to 8 blocks, at least 2 k-blocks each
+        if (tiles < num_sms) {
+            splits = (num_sms + tiles - 1) / tiles;
+            if (splits > 8) splits = 8;
+            while (splits > 1 && p.num_k_blocks / splits < 2) splits--;
+        }
+    } else if (p.swapped) {
+        // minimise the number of waves over the SMs; a larger split must pay for itself
+        double best = 1e30;
+        for (int sct = 1; sct <= 16; sct++) {
+            if (sct > 1 && p.num_k_blocks / sct < 2) break;
+            const double waves = (double)((tiles * sct + num_sms - 1) / num_sms) / sct;
+            if (waves < best * 0.9) { best = waves; splits = sct; }
+        }
     }
     p.k_blocks_per_split = (p.num_k_blocks + splits - 1) / splits;
     splits = (p.num_k_blocks + p.k_blocks_per_split - 1) / p.k_blocks_per_split;
     p.epilogue = epilogue; p.out = out; p.ldc = ldc; p.err = err;
     p.accum = nullptr; p.accum_ld = 0;
-    if (splits > 1) {
+    p.cluster_splits = use_cluster ? splits : 1;
+    p.rows_per = (use_cluster && splits > 1) ? 2 * ((TILE_ROWS / 2 + splits - 1) / splits) : TILE_ROWS;
+    if (!use_cluster && splits > 1) {
         if (epilogue == 2) {
             p.accum = (float*)out;
             p.accum_ld = ldc;
@@ -131,11 +151,17 @@ EMBER_API int ember_gemm_tc(const void* A, const void* W, void* out, int ldc, in
     const int rows_bytes = TILE_ROWS * TILE_K * 2;
     const int cols_bytes = p.block_cols * TILE_K * 2;
     const int stage_bytes = rows_bytes + ((cols_bytes + 1023) & ~1023);
-    int stages = (200 * 1024) / stage_bytes;
+    const size_t recv_bytes = p.cluster_splits > 1 ? (size_t)splits * p.rows_per * p.block_cols * sizeof(float) : 0;
+    // Decode-sized tiles keep their blocks small (about 96 KiB of stages) so that two or three fit on
+    // an SM: the next kernel's blocks become resident and prefetch their weights while this kernel
+    // drains, and the memory system sees more independent streams.  Prefill tiles take all they can.
+    const size_t budget = p.swapped ? (size_t)96 * 1024 : (size_t)200 * 1024 - recv_bytes;
+    int stages = (int)(budget / stage_bytes);
     if (stages > MAX_STAGES) stages = MAX_STAGES;
+    if (stages < 2) stages = 2;
     if (stages > p.k_blocks_per_split) stages = p.k_blocks_per_split < 2 ? 2 : p.k_blocks_per_split;
     p.stages = stages;
-    const size_t smem = (size_t)stages * stage_bytes + 1024 /* alignment slack */ + 256 /* barriers */;
+    const size_t smem = (size_t)stages * stage_bytes + 1024 /* alignment slack */ + 256 /* barriers */ + recv_bytes;
 
     CUtensorMap map_rows, map_cols;
     const void* rows_ptr = p.swapped ? W : A;
@@ -152,12 +178,29 @@ EMBER_API int ember_gemm_tc(const void* A, const void* W, void* out, int ldc, in
         attr_set = true;
     }
     dim3 grid(row_tiles, col_tiles, splits);
-    gemm_tc_kernel<<<grid, GEMM_THREADS, smem, st>>>(map_rows, map_cols, p);
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = dim3(GEMM_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attrs[2];
+    attrs[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+    cfg.numAttrs = 1;
+    if (p.cluster_splits > 1) {
+        attrs[1].id = cudaLaunchAttributeClusterDimension;
+        attrs[1].val.clusterDim.x = 1;
+        attrs[1].val.clusterDim.y = 1;
+        attrs[1].val.clusterDim.z = (unsigned)splits;
+        cfg.numAttrs = 2;
+    }
+    cfg.attrs = attrs;
+    cudaLaunchKernelEx(&cfg, gemm_tc_kernel, map_rows, map_cols, p);
     int rc = check_launch("gemm_tc");
     if (rc) return rc;
-    if (splits > 1 && epilogue != 2) {
+    if (splits > 1 && p.cluster_splits <= 1 && epilogue != 2) {
         const size_t total = (size_t)M * (epilogue == 3 ? N / 2 : N);
-        gemm_tc_finalize_kernel<<<(unsigned)((total + 255) / 256), 256, 0, st>>>(p.accum, p.accum_ld, out, ldc, M, N, epilogue);
+        launch_kernel(gemm_tc_finalize_kernel, (unsigned)((total + 255) / 256), 256, 0, st, p.accum, p.accum_ld, out, ldc, M, N, epilogue);
         return check_launch("gemm_tc_finalize");
     }
     return 0;

@@ -27,8 +27,10 @@ struct GemmTcParams {
     int epilogue;         // 0 store bf16, 1 store fp32, 2 add fp32, 3 silu(gate)*up -> bf16
     void* out;
     int ldc;
-    float* accum;         // split-K target: fp32 [M, accum_ld] (the residual itself for epilogue 2)
+    float* accum;         // atomic split-K target: fp32 [M, accum_ld] (the residual itself for epilogue 2)
     int accum_ld;
+    int cluster_splits;   // > 1: the K splits of a tile form a thread-block cluster and are summed in shared memory
+    int rows_per;         // accumulator rows each block of the cluster finishes (even)
     int tmem_cols;
     int* err;
 };
@@ -91,6 +93,17 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
     for (int i = 0; i < 16; i++) v[i] = __uint_as_float(r[i]);
 }
 
+__device__ __forceinline__ uint32_t map_to_rank(uint32_t smem_addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void st_cluster_f32x4(uint32_t addr, float a, float b, float c, float d) {
+    asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+__device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+
 // Shared-memory matrix descriptor of a K-major bf16 tile whose rows are 128 bytes, written by TMA
 // with the 128-byte swizzle: 8-row groups are 1024 bytes apart (stride byte offset), descriptor
 // version 1, layout type 2 (128-byte swizzle).  The leading byte offset is not used by this layout.
@@ -121,6 +134,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_consta
     uint64_t* tmem_full_bar = empty_bar + MAX_STAGES;
     uint32_t* tmem_base_slot = (uint32_t*)(tmem_full_bar + 1);
     volatile int* abort_flag = (volatile int*)(tmem_base_slot + 1);
+    // cluster split-K: partial sums of the rows this block finishes, one slab per block of the cluster
+    float* recv = (float*)((uint8_t*)full_bar + 256);            // [cluster_splits][rows_per][block_cols]
+    const bool clustered = p.cluster_splits > 1;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int row_tile = blockIdx.x, col_tile = blockIdx.y, split = blockIdx.z;
@@ -146,19 +162,37 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_consta
     __syncthreads();
     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
     const uint32_t tmem_d = *tmem_base_slot;
+    if (clustered) cluster_arrive();        // phase 1: every block of the cluster is up before anyone writes to it
 
+    pdl_launch_dependents();
     if (warp == 0) {
         // ---------------------------------------------------------------- TMA producer
+        // The weight operand does not depend on earlier kernels: its first tiles are requested
+        // before the grid dependency is awaited, so they stream in while the kernel before this
+        // one is still finishing.  The activation operand is requested only after the wait.
         if (lane == 0 && n_kb > 0) {
-            for (int i = 0; i < n_kb; i++) {
+            const CUtensorMap* map_w = p.swapped ? &map_rows : &map_cols;
+            const CUtensorMap* map_x = p.swapped ? &map_cols : &map_rows;
+            const int w_y = p.swapped ? row_tile * TILE_ROWS : col_tile * p.block_cols;
+            const int x_y = p.swapped ? col_tile * p.block_cols : row_tile * TILE_ROWS;
+            const int w_off = p.swapped ? 0 : rows_bytes, x_off = p.swapped ? rows_bytes : 0;
+            const int ahead = min(n_kb, p.stages);
+            for (int i = 0; i < ahead; i++) {
+                uint8_t* st = smem + (size_t)i * stage_bytes;
+                mbar_expect_tx(&full_bar[i], (uint32_t)(rows_bytes + cols_bytes));
+                tma_load_2d(st + w_off, map_w, &full_bar[i], (kb0 + i) * TILE_K, w_y);
+            }
+            pdl_wait();
+            for (int i = 0; i < ahead; i++)
+                tma_load_2d(smem + (size_t)i * stage_bytes + x_off, map_x, &full_bar[i], (kb0 + i) * TILE_K, x_y);
+            for (int i = ahead; i < n_kb; i++) {
                 const int s = i % p.stages;
                 const uint32_t phase = (uint32_t)(i / p.stages) & 1u;
                 if (!mbar_wait(&empty_bar[s], phase ^ 1u, abort_flag)) break;
-                uint8_t* a = smem + (size_t)s * stage_bytes;
-                uint8_t* b = a + rows_bytes;
+                uint8_t* st = smem + (size_t)s * stage_bytes;
                 mbar_expect_tx(&full_bar[s], (uint32_t)(rows_bytes + cols_bytes));
-                tma_load_2d(a, &map_rows, &full_bar[s], (kb0 + i) * TILE_K, row_tile * TILE_ROWS);
-                tma_load_2d(b, &map_cols, &full_bar[s], (kb0 + i) * TILE_K, col_tile * p.block_cols);
+                tma_load_2d(st + w_off, map_w, &full_bar[s], (kb0 + i) * TILE_K, w_y);
+                tma_load_2d(st + x_off, map_x, &full_bar[s], (kb0 + i) * TILE_K, x_y);
             }
         }
     } else if (warp == 1) {
@@ -186,9 +220,27 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_consta
     } else if (n_kb > 0) {
         // -------------------------------------------------------------------- epilogue
         const int quad = warp & 3;                  // TMEM lane quadrant this warp may read
+        pdl_wait();                                 // the output may still be read by earlier kernels until here
         const bool ok = mbar_wait(tmem_full_bar, 0, abort_flag);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        if (ok) {
+        if (clustered) {
+            // hand this block's partial sums to the blocks that finish them: row r goes to block r / rows_per
+            __syncwarp();
+            cluster_wait();                         // phase 1 complete: all blocks of the cluster run
+            const int r = quad * 32 + lane;
+            const uint32_t taddr_row = tmem_d + ((uint32_t)(quad * 32) << 16);
+            const int owner = r / p.rows_per, rl = r - owner * p.rows_per;
+            const uint32_t dst_row = map_to_rank(smem_u32(recv + ((size_t)split * p.rows_per + rl) * p.block_cols), (uint32_t)owner);
+            for (int c0 = 0; c0 < p.block_cols; c0 += 16) {
+                float v[16];
+                tmem_ld16(taddr_row + (uint32_t)c0, v);
+                if (ok) {
+#pragma unroll
+                    for (int j = 0; j < 4; j++)
+                        st_cluster_f32x4(dst_row + (uint32_t)(c0 + 4 * j) * 4u, v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                }
+            }
+        } else if (ok) {
             const int r = quad * 32 + lane;         // accumulator row of this thread
             const uint32_t taddr_row = tmem_d + ((uint32_t)(quad * 32) << 16);
             const bool splitk = gridDim.z > 1;
@@ -232,7 +284,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_consta
                         }
                     } else {
                         __nv_bfloat16* dst = (__nv_bfloat16*)p.out + (size_t)m * p.ldc + (n0 >> 1);
-                        for (int j = 0; j + 1 < nv; j += 2) dst[j >> 1] = __float2bfloat16_rn(silu_mul(v[j], v[j + 1]));
+                        if (nv == 16 && (((uintptr_t)dst) & 15) == 0) {
+                            uint4 q;
+                            __nv_bfloat162* h = (__nv_bfloat162*)&q;
+#pragma unroll
+                            for (int j = 0; j < 4; j++)
+                                h[j] = __floats2bfloat162_rn(silu_mul(v[4 * j], v[4 * j + 1]), silu_mul(v[4 * j + 2], v[4 * j + 3]));
+                            *(uint4*)dst = q;
+                        } else {
+                            for (int j = 0; j + 1 < nv; j += 2) dst[j >> 1] = __float2bfloat16_rn(silu_mul(v[j], v[j + 1]));
+                        }
                     }
                 } else {
                     const int n = row_tile * TILE_ROWS + r;
@@ -270,6 +331,45 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_consta
         asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     }
 
+    if (clustered) {
+        // ---- sum the cluster's partial results for the rows this block finishes, in block order
+        __syncwarp();
+        if (warp < 2 || n_kb <= 0) cluster_wait();          // the epilogue warps already passed phase 1
+        cluster_arrive();                                   // phase 2: all partial sums are written ...
+        cluster_wait();                                     // ... and visible
+        pdl_wait();
+        const int S = p.cluster_splits, RP = p.rows_per, C = p.block_cols;
+        const int row_base = row_tile * TILE_ROWS + split * RP;       // first weight row this block finishes
+        const int rows_here = max(0, min(RP, TILE_ROWS - split * RP));
+        if (p.epilogue == 3) {
+            const int pairs = rows_here >> 1;
+            for (int idx = threadIdx.x; idx < pairs * C; idx += GEMM_THREADS) {
+                const int c = idx / pairs, pr = idx - c * pairs;
+                const int n = row_base + 2 * pr, m = col_tile * C + c;
+                if (n + 1 >= p.N || m >= p.M) continue;
+                float g = 0.0f, u = 0.0f;
+                for (int s = 0; s < S; s++) {
+                    g += recv[((size_t)s * RP + 2 * pr) * C + c];
+                    u += recv[((size_t)s * RP + 2 * pr + 1) * C + c];
+                }
+                ((__nv_bfloat16*)p.out)[(size_t)m * p.ldc + (n >> 1)] = __float2bfloat16_rn(silu_mul(g, u));
+            }
+        } else {
+            for (int idx = threadIdx.x; idx < rows_here * C; idx += GEMM_THREADS) {
+                const int c = idx / rows_here, rl = idx - c * rows_here;
+                const int n = row_base + rl, m = col_tile * C + c;
+                if (n >= p.N || m >= p.M) continue;
+                float v = 0.0f;
+                for (int s = 0; s < S; s++) v += recv[((size_t)s * RP + rl) * C + c];
+                if (p.epilogue == 0) ((__nv_bfloat16*)p.out)[(size_t)m * p.ldc + n] = __float2bfloat16_rn(v);
+                else if (p.epilogue == 1) ((float*)p.out)[(size_t)m * p.ldc + n] = v;
+                else {
+                    float* dst = (float*)p.out + (size_t)m * p.ldc + n;
+                    *dst = *dst + v;
+                }
+            }
+        }
+    }
     __syncthreads();
     if (threadIdx.x == 0 && *abort_flag && p.err) atomicOr(p.err, EMBER_ERR_WAIT_LIMIT);
     if (warp == 1) {
@@ -281,6 +381,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_consta
 // Split-K finalize for the store epilogues: out = epilogue(accum), accum = 0.
 __global__ void gemm_tc_finalize_kernel(float* __restrict__ accum, int accum_ld, void* __restrict__ out, int ldc, int M,
                                         int N, int epilogue) {
+    pdl_launch_dependents();
+    pdl_wait();
     const int n_out = epilogue == 3 ? N / 2 : N;
     const size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= (size_t)M * n_out) return;

@@ -265,8 +265,9 @@ def gemm_tc_usable(x: torch.Tensor, w: torch.Tensor, bias, epilogue: int) -> boo
 
 
 def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, M: int, epilogue: int = EPI_STORE,
-            err: Optional[torch.Tensor] = None, stream: Optional[int] = None) -> None:
-    """out (+)= a[:M] @ w.T on the tcgen05 tensor cores (bf16 in, fp32 accumulate)."""
+            err: Optional[torch.Tensor] = None, stream: Optional[int] = None, split_mode: int = 0) -> None:
+    """out (+)= a[:M] @ w.T on the tcgen05 tensor cores (bf16 in, fp32 accumulate).
+    ``split_mode``: how split-K partial sums are combined (0 automatic, 1 atomics, 2 cluster)."""
     _check(a, "a", torch.bfloat16)
     _check(w, "w", torch.bfloat16)
     _check(out, "out")
@@ -282,7 +283,8 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, M: int, epilogu
     scratch = _scratch(a.device, min(M, 128) * N) if M <= 128 else None
     lib = _lib("gemm_tc")
     _call(lib, lib.ember_gemm_tc, _p(a), _p(w), _p(out), c_int(n_out), c_int(M), c_int(N), c_int(K), c_int(epilogue),
-          _p(scratch), c_longlong(scratch.numel() if scratch is not None else 0), c_int(_sms(a.device)), _p(err),
+          _p(scratch), c_longlong(scratch.numel() if scratch is not None else 0), c_int(_sms(a.device)), c_int(split_mode),
+          _p(err),
           c_void_p(stream if stream is not None else current_stream_ptr()))
 
 
@@ -292,14 +294,15 @@ def num_sms(device) -> int:
 
 def attention_tc_supported(head_dim: int, group: int, page_tokens: int, mode: int) -> bool:
     """Whether the tensor-core attention takes this geometry (mode 0: prompt portions, 1: single tokens)."""
-    if not TC_ENABLED:
+    # the same rule as ember_attention_tc_supported, stated here so that a model that cannot use the
+    # kernels never loads (or compiles) their library
+    if not TC_ENABLED or head_dim not in (64, 128) or page_tokens not in (16, 32, 64) or group < 1:
         return False
-    lib = _lib("attention_tc")
-    return bool(lib.ember_attention_tc_supported(c_int(head_dim), c_int(group), c_int(page_tokens), c_int(mode)))
+    return group <= 16 if mode == 1 else group <= 64
 
 
 def attention_tc_tile_queries(group: int) -> int:
-    return int(_lib("attention_tc").ember_attention_tc_tile_queries(c_int(group)))
+    return 64 // group if 1 <= group <= 64 else 0
 
 
 def attention_tc(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: torch.Tensor, mode: int,

@@ -132,8 +132,13 @@ class Attention(Mixer):
                 # cut long key ranges so that about two waves of blocks share the work; splits are
                 # anchored at key 0, so with a window the early ones are empty
                 live = ctx.max_context if s.window <= 0 else min(ctx.max_context, s.window + 64)
-                want = max(1, (2 * ops.num_sms(q.device)) // max(1, n * s.num_kv_heads))
-                live_splits = max(1, min(want, (live + 255) // 256))
+                slots = 2 * ops.num_sms(q.device)                 # two blocks fit on an SM
+                blocks = n * s.num_kv_heads
+                live_splits, best = 1, None
+                for cand in range(1, max(1, min(16, (live + 255) // 256)) + 1):
+                    cost = -(-blocks * cand // slots) / cand * (1.0 + 0.03 * cand)    # waves per split, splits cost a little
+                    if best is None or cost < best:
+                        live_splits, best = cand, cost
                 split_keys = ((live + live_splits - 1) // live_splits + 63) // 64 * 64
                 n_splits = (ctx.max_context + split_keys - 1) // split_keys
                 part_o = part_ml = None

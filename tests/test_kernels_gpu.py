@@ -24,9 +24,11 @@ def ref_epilogue(c, epilogue, prev=None):
 
 
 @pytest.mark.parametrize("M,N,K", [(1, 512, 64), (3, 1000, 96), (17, 192, 200), (64, 2048, 2048), (65, 130, 72),
-                                   (128, 256, 512), (129, 1000, 264), (300, 1536, 1024), (1000, 520, 136)])
+                                   (128, 256, 512), (129, 1000, 264), (300, 1536, 1024), (1000, 520, 136),
+                                   (8, 4096, 2048), (5, 2048, 6144), (16, 12288, 1024), (100, 640, 4096)])
 @pytest.mark.parametrize("epilogue", [0, 1, 2, 3])
-def test_gemm_tc(M, N, K, epilogue):
+@pytest.mark.parametrize("split_mode", [0, 1, 2])
+def test_gemm_tc(M, N, K, epilogue, split_mode):
     from ember_b200 import ops
     torch.manual_seed(M * 7 + N + K + epilogue)
     a = (torch.randn(M, K, device="cuda") * 0.5).bfloat16()
@@ -36,7 +38,7 @@ def test_gemm_tc(M, N, K, epilogue):
     out = prev.clone() if epilogue in (1, 2) else torch.zeros(M, n_out, device="cuda", dtype=torch.bfloat16)
     err = torch.zeros(1, dtype=torch.int32, device="cuda")
     assert ops.gemm_tc_usable(a, w, None, epilogue)
-    ops.gemm_tc(a, w, out, M, epilogue, err=err)
+    ops.gemm_tc(a, w, out, M, epilogue, err=err, split_mode=split_mode)
     want = ref_epilogue(a.float() @ w.float().t(), epilogue, prev)
     assert int(err.item()) == 0
     tol = 5e-3 if epilogue in (0, 3) else 1e-5          # bf16 rounding of the output, else fp32 accumulation only
