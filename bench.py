@@ -246,6 +246,7 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration has (named in config)")
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
+    ap.add_argument("--only-prefill", action="store_true", help="profiling aid: run just the 2,048-token prefill")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -265,6 +266,14 @@ def main() -> int:
     n_layers = args.layers or cfg.num_hidden_layers
     pk = peaks()
     wbytes, kv_per_token, prefill_flops = model_bytes_and_flops(cfg, n_layers)
+
+    if args.only_prefill:
+        llm = build_llm(cfg, n_layers, 1)
+        pms = time_prefill(llm, PREFILL_TOKENS, reps=max(1, min(5, args.steps)), warmup=min(3, warmup))
+        fl = prefill_flops(PREFILL_TOKENS)
+        print(json.dumps({"prefill": {"value": round(PREFILL_TOKENS / (pms * 1e-3), 1), "tokens": PREFILL_TOKENS,
+                                      "ms": round(pms, 3), "tflops": round(fl / (pms * 1e-3) / 1e12, 1), "layers": n_layers}}))
+        return 0
 
     llm = build_llm(cfg, n_layers, max(args.batch, 1))
     with ClockSampler() as clocks:

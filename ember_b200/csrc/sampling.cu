@@ -275,9 +275,68 @@ sample_kernel(const float* __restrict__ logits_all, int V, const SampleParams* _
     if (tid == 0) out[row] = tok == 0x7fffffff ? arg : tok;
 }
 
+// ---- greedy rows only: argmax in two steps so that many blocks share a row
+constexpr int ARGMAX_CHUNKS = 32;
+
+__global__ void __launch_bounds__(256)
+argmax_partial_kernel(const float* __restrict__ logits_all, int V, float* __restrict__ part_v, int* __restrict__ part_i) {
+    __shared__ float sv[8];
+    __shared__ int si[8];
+    const int row = blockIdx.x, chunk = blockIdx.y;
+    const float* logits = logits_all + (size_t)row * V;
+    const int per = (V + ARGMAX_CHUNKS - 1) / ARGMAX_CHUNKS;
+    const int lo = chunk * per, hi = min(V, lo + per);
+    float best = -INFINITY;
+    int best_i = 0x7fffffff;
+    for (int i = lo + threadIdx.x; i < hi; i += 256) {
+        const float x = logits[i];
+        if (x > best) { best = x; best_i = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+        if (ov > best || (ov == best && oi < best_i)) { best = ov; best_i = oi; }
+    }
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    if (lane == 0) { sv[warp] = best; si[warp] = best_i; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < 8; w++)
+            if (sv[w] > best || (sv[w] == best && si[w] < best_i)) { best = sv[w]; best_i = si[w]; }
+        part_v[row * ARGMAX_CHUNKS + chunk] = best;
+        part_i[row * ARGMAX_CHUNKS + chunk] = best_i;
+    }
+}
+
+__global__ void argmax_final_kernel(const float* __restrict__ part_v, const int* __restrict__ part_i, int* __restrict__ out) {
+    const int row = blockIdx.x, lane = threadIdx.x;      // 32 threads, one per chunk
+    float best = part_v[row * ARGMAX_CHUNKS + lane];
+    int best_i = part_i[row * ARGMAX_CHUNKS + lane];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, best_i, o);
+        if (ov > best || (ov == best && oi < best_i)) { best = ov; best_i = oi; }
+    }
+    if (lane == 0) out[row] = best_i == 0x7fffffff ? 0 : best_i;
+}
+
 }  // namespace ember
 
 using namespace ember;
+
+// Argmax of every row (lowest index on ties): the greedy case, spread over many blocks.
+// part_v / part_i: scratch of rows * 32 floats / ints.
+EMBER_API int ember_argmax(const float* logits, int rows, int V, float* part_v, int* part_i, int* out, void* stream) {
+    if (rows <= 0) return 0;
+    if (V <= 0) return fail("argmax: vocabulary %d", V);
+    static_assert(ARGMAX_CHUNKS == 32, "the final step uses one warp");
+    cudaStream_t st = (cudaStream_t)stream;
+    argmax_partial_kernel<<<dim3(rows, ARGMAX_CHUNKS), 256, 0, st>>>(logits, V, part_v, part_i);
+    argmax_final_kernel<<<rows, 32, 0, st>>>(part_v, part_i, out);
+    return check_launch("argmax");
+}
 
 EMBER_API int ember_sample(const float* logits, int rows, int V, const void* params, int* out, void* stream) {
     if (rows <= 0) return 0;

@@ -232,6 +232,20 @@ def sample(logits: torch.Tensor, params: torch.Tensor, out: torch.Tensor, rows: 
           c_void_p(stream if stream is not None else current_stream_ptr()))
 
 
+def argmax(logits: torch.Tensor, out: torch.Tensor, rows: int, part_v: torch.Tensor, part_i: torch.Tensor,
+           stream: Optional[int] = None) -> None:
+    """out[r] = index of the largest logit of row r, lowest index on ties (greedy sampling)."""
+    _check(logits, "logits", torch.float32)
+    _check(out, "out", torch.int32)
+    _check(part_v, "part_v", torch.float32)
+    _check(part_i, "part_i", torch.int32)
+    if logits.dim() != 2 or logits.shape[0] < rows or out.numel() < rows or part_v.numel() < rows * 32 or part_i.numel() < rows * 32:
+        raise KernelError("argmax: buffers do not fit the rows")
+    lib = _lib("sampling")
+    _call(lib, lib.ember_argmax, _p(logits), c_int(rows), c_int(logits.shape[1]), _p(part_v), _p(part_i), _p(out),
+          c_void_p(stream if stream is not None else current_stream_ptr()))
+
+
 # ------------------------------------------------------------- tensor-core kernels (bf16)
 _tc_scratch = {}
 _num_sms = {}

@@ -27,9 +27,15 @@ def sample(logits: torch.Tensor, params: Sequence[SamplingParams], counters: Seq
     rows, vocab = logits.shape
     if len(params) != rows or len(counters) != rows:
         raise ops.KernelError(f"sample: {len(params)} parameter sets for {rows} rows")
-    host = torch.from_numpy(pack_params(params, counters).copy())
-    dev = host.to(logits.device, non_blocking=False)
     if out is None:
         out = torch.empty(rows, dtype=torch.int32, device=logits.device)
+    if all(p.greedy for p in params):
+        # argmax needs no parameters on the device and is spread over many blocks per row
+        part_v = torch.empty(rows * 32, dtype=torch.float32, device=logits.device)
+        part_i = torch.empty(rows * 32, dtype=torch.int32, device=logits.device)
+        ops.argmax(logits, out, rows, part_v, part_i)
+        return out
+    host = torch.from_numpy(pack_params(params, counters).copy()).pin_memory()
+    dev = host.to(logits.device, non_blocking=True)
     ops.sample(logits, dev, out, rows)
     return out

@@ -51,6 +51,19 @@ def test_device_equals_host(vocab):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("vocab", [17, 1000, 151936])
+def test_device_greedy_rows_take_the_lowest_index_on_ties(vocab):
+    from ember_b200.sampling import device
+    rng = np.random.default_rng(vocab)
+    logits = rng.normal(size=(9, vocab)).astype(np.float32)
+    logits[2, [3, vocab - 1]] = 50.0                   # a tie far apart
+    logits[4, :] = 1.0                                 # everything ties: index 0
+    logits[6, vocab - 1] = 99.0                        # the very last entry
+    got = device.sample(torch.from_numpy(logits).cuda(), [SamplingParams(temperature=0.0)] * 9, [0] * 9).cpu().tolist()
+    assert got == [int(np.argmax(r)) for r in logits]
+
+
+@pytest.mark.gpu
 def test_device_draws_stay_in_the_kept_set_and_follow_the_distribution():
     from ember_b200.sampling import device
     rng = np.random.default_rng(5)
