@@ -520,6 +520,8 @@ EMBER_API int ember_attention_tc(const void* q, const void* k_pool, const void* 
     auto run = [&](auto kernel) -> int {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return fail("attention_tc: shared memory %zu: %s", smem, cudaGetErrorString(e));
+        // ask for the largest shared-memory carve-out so that two blocks fit on an SM
+        cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared);
         launch_kernel(kernel, grid, ATC_THREADS, smem, st, mk, mv, p);
         return check_launch("attention_tc");
     };

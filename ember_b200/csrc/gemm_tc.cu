@@ -145,8 +145,12 @@ EMBER_API int ember_gemm_tc(const void* A, const void* W, void* out, int ldc, in
             p.accum_ld = N;
         }
     }
+    // Prefill-sized products run as persistent blocks with two accumulators in tensor memory.
+    const bool persistent = !p.swapped && split_mode != 3;
+    p.row_tiles = row_tiles;
+    p.total_tiles = row_tiles * col_tiles;
     int tc = 32;
-    while (tc < p.block_cols) tc <<= 1;
+    while (tc < p.block_cols * (persistent ? 2 : 1)) tc <<= 1;
     p.tmem_cols = tc;
     const int rows_bytes = TILE_ROWS * TILE_K * 2;
     const int cols_bytes = p.block_cols * TILE_K * 2;
@@ -175,7 +179,19 @@ EMBER_API int ember_gemm_tc(const void* A, const void* W, void* out, int ldc, in
     if (!attr_set) {
         cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
         if (e != cudaSuccess) return fail("gemm_tc: cannot raise the shared-memory limit: %s", cudaGetErrorString(e));
+        cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared);
         attr_set = true;
+    }
+    if (persistent) {
+        static bool pattr = false;
+        if (!pattr) {
+            cudaError_t e = cudaFuncSetAttribute(gemm_tc_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+            if (e != cudaSuccess) return fail("gemm_tc: cannot raise the shared-memory limit: %s", cudaGetErrorString(e));
+            pattr = true;
+        }
+        const int blocks = p.total_tiles < num_sms ? p.total_tiles : num_sms;
+        launch_kernel(gemm_tc_persistent_kernel, dim3(blocks), dim3(GEMM_THREADS), smem, st, map_rows, map_cols, p);
+        return check_launch("gemm_tc_persistent");
     }
     dim3 grid(row_tiles, col_tiles, splits);
     cudaLaunchConfig_t cfg = {};

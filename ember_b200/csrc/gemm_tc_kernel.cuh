@@ -31,6 +31,8 @@ struct GemmTcParams {
     int accum_ld;
     int cluster_splits;   // > 1: the K splits of a tile form a thread-block cluster and are summed in shared memory
     int rows_per;         // accumulator rows each block of the cluster finishes (even)
+    int row_tiles;        // persistent kernel: tiles along M, and their total number
+    int total_tiles;
     int tmem_cols;
     int* err;
 };
@@ -40,6 +42,9 @@ __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)_
 
 __device__ __forceinline__ void mbar_init(uint64_t* bar, int count) {
     asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(smem_u32(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
@@ -118,6 +123,51 @@ __host__ __device__ __forceinline__ uint32_t umma_idesc(int n) {
 }
 
 __device__ __forceinline__ float silu_mul(float g, float u) { return g / (1.0f + __expf(-g)) * u; }
+
+// Fused epilogue of 16 consecutive output columns of one token row (normal orientation):
+// store bf16 / store fp32 / add into the fp32 residual / silu(gate) * up.
+__device__ __forceinline__ void store_chunk_normal(const GemmTcParams& p, int m, int n0, int nv, const float* v) {
+    if (p.epilogue == 0) {
+        __nv_bfloat16* dst = (__nv_bfloat16*)p.out + (size_t)m * p.ldc + n0;
+        if (nv == 16 && (((uintptr_t)dst) & 15) == 0) {
+            uint4 q[2];
+            __nv_bfloat162* h = (__nv_bfloat162*)q;
+#pragma unroll
+            for (int j = 0; j < 8; j++) h[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+            ((uint4*)dst)[0] = q[0];
+            ((uint4*)dst)[1] = q[1];
+        } else {
+            for (int j = 0; j < nv; j++) dst[j] = __float2bfloat16_rn(v[j]);
+        }
+    } else if (p.epilogue == 1 || p.epilogue == 2) {
+        float* dst = (float*)p.out + (size_t)m * p.ldc + n0;
+        if (nv == 16 && (((uintptr_t)dst) & 15) == 0) {
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                float4 o = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                if (p.epilogue == 2) {
+                    const float4 c = ((float4*)dst)[j];
+                    o.x += c.x; o.y += c.y; o.z += c.z; o.w += c.w;
+                }
+                ((float4*)dst)[j] = o;
+            }
+        } else {
+            for (int j = 0; j < nv; j++) dst[j] = p.epilogue == 2 ? dst[j] + v[j] : v[j];
+        }
+    } else {
+        __nv_bfloat16* dst = (__nv_bfloat16*)p.out + (size_t)m * p.ldc + (n0 >> 1);
+        if (nv == 16 && (((uintptr_t)dst) & 15) == 0) {
+            uint4 q;
+            __nv_bfloat162* h = (__nv_bfloat162*)&q;
+#pragma unroll
+            for (int j = 0; j < 4; j++)
+                h[j] = __floats2bfloat162_rn(silu_mul(v[4 * j], v[4 * j + 1]), silu_mul(v[4 * j + 2], v[4 * j + 3]));
+            *(uint4*)dst = q;
+        } else {
+            for (int j = 0; j + 1 < nv; j += 2) dst[j >> 1] = __float2bfloat16_rn(silu_mul(v[j], v[j + 1]));
+        }
+    }
+}
 
 // ------------------------------------------------------------------------------------ kernel
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
@@ -255,45 +305,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_consta
                     if (splitk) {
                         float* dst = p.accum + (size_t)m * p.accum_ld + n0;
                         for (int j = 0; j < nv; j++) atomicAdd(dst + j, v[j]);
-                    } else if (p.epilogue == 0) {
-                        __nv_bfloat16* dst = (__nv_bfloat16*)p.out + (size_t)m * p.ldc + n0;
-                        if (nv == 16 && (((uintptr_t)dst) & 15) == 0) {
-                            uint4 q[2];
-                            __nv_bfloat162* h = (__nv_bfloat162*)q;
-#pragma unroll
-                            for (int j = 0; j < 8; j++) h[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
-                            ((uint4*)dst)[0] = q[0];
-                            ((uint4*)dst)[1] = q[1];
-                        } else {
-                            for (int j = 0; j < nv; j++) dst[j] = __float2bfloat16_rn(v[j]);
-                        }
-                    } else if (p.epilogue == 1 || p.epilogue == 2) {
-                        float* dst = (float*)p.out + (size_t)m * p.ldc + n0;
-                        if (nv == 16 && (((uintptr_t)dst) & 15) == 0) {
-#pragma unroll
-                            for (int j = 0; j < 4; j++) {
-                                float4 o = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
-                                if (p.epilogue == 2) {
-                                    const float4 c = ((float4*)dst)[j];
-                                    o.x += c.x; o.y += c.y; o.z += c.z; o.w += c.w;
-                                }
-                                ((float4*)dst)[j] = o;
-                            }
-                        } else {
-                            for (int j = 0; j < nv; j++) dst[j] = p.epilogue == 2 ? dst[j] + v[j] : v[j];
-                        }
                     } else {
-                        __nv_bfloat16* dst = (__nv_bfloat16*)p.out + (size_t)m * p.ldc + (n0 >> 1);
-                        if (nv == 16 && (((uintptr_t)dst) & 15) == 0) {
-                            uint4 q;
-                            __nv_bfloat162* h = (__nv_bfloat162*)&q;
-#pragma unroll
-                            for (int j = 0; j < 4; j++)
-                                h[j] = __floats2bfloat162_rn(silu_mul(v[4 * j], v[4 * j + 1]), silu_mul(v[4 * j + 2], v[4 * j + 3]));
-                            *(uint4*)dst = q;
-                        } else {
-                            for (int j = 0; j + 1 < nv; j += 2) dst[j >> 1] = __float2bfloat16_rn(silu_mul(v[j], v[j + 1]));
-                        }
+                        store_chunk_normal(p, m, n0, nv, v);
                     }
                 } else {
                     const int n = row_tile * TILE_ROWS + r;
@@ -370,6 +383,131 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_consta
             }
         }
     }
+    __syncthreads();
+    if (threadIdx.x == 0 && *abort_flag && p.err) atomicOr(p.err, EMBER_ERR_WAIT_LIMIT);
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_d), "r"(p.tmem_cols) : "memory");
+    }
+}
+
+// ------------------------------------------------------------------ persistent kernel (prefill)
+// Normal orientation only (accumulator rows are tokens).  One block per SM walks over output tiles
+// (tile t -> weight column tile t / row_tiles, token row tile t % row_tiles, so that blocks running at
+// the same time share weight tiles in L2).  Two accumulators live in tensor memory: while the four
+// epilogue warps drain and store tile i, the MMA warp already fills the other accumulator with tile
+// i + 1, and the TMA warp runs ahead through the ring of stages across tile borders.
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant__ CUtensorMap map_cols,
+                          const GemmTcParams p) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = (uint8_t*)(((uintptr_t)smem_raw + 1023) & ~(uintptr_t)1023);
+    const int rows_bytes = TILE_ROWS * TILE_K * 2;
+    const int cols_bytes = p.block_cols * TILE_K * 2;
+    const int stage_bytes = rows_bytes + ((cols_bytes + 1023) & ~1023);
+    uint64_t* full_bar = (uint64_t*)(smem + (size_t)p.stages * stage_bytes);
+    uint64_t* empty_bar = full_bar + MAX_STAGES;
+    uint64_t* tmem_full_bar = empty_bar + MAX_STAGES;      // [2]
+    uint64_t* tmem_empty_bar = tmem_full_bar + 2;           // [2]
+    uint32_t* tmem_base_slot = (uint32_t*)(tmem_empty_bar + 2);
+    volatile int* abort_flag = (volatile int*)(tmem_base_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n_kb = p.num_k_blocks;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < p.stages; s++) {
+            mbar_init(&full_bar[s], 1);
+            mbar_init(&empty_bar[s], 1);
+        }
+        for (int a = 0; a < 2; a++) {
+            mbar_init(&tmem_full_bar[a], 1);
+            mbar_init(&tmem_empty_bar[a], 4);               // one arrival per epilogue warp
+        }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_base_slot)), "r"(p.tmem_cols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_d = *tmem_base_slot;
+
+    pdl_launch_dependents();
+    pdl_wait();
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int it = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
+                const int col_tile = t / p.row_tiles, row_tile = t - col_tile * p.row_tiles;
+                for (int i = 0; i < n_kb; i++, it++) {
+                    const int s = it % p.stages;
+                    if (it >= p.stages) ok = mbar_wait(&empty_bar[s], ((uint32_t)(it / p.stages) & 1u) ^ 1u, abort_flag);
+                    if (!ok) break;
+                    uint8_t* st = smem + (size_t)s * stage_bytes;
+                    mbar_expect_tx(&full_bar[s], (uint32_t)(rows_bytes + cols_bytes));
+                    tma_load_2d(st, &map_rows, &full_bar[s], i * TILE_K, row_tile * TILE_ROWS);
+                    tma_load_2d(st + rows_bytes, &map_cols, &full_bar[s], i * TILE_K, col_tile * p.block_cols);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            const uint32_t idesc = umma_idesc(p.block_cols);
+            int it = 0, li = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x, li++) {
+                const int acc = li & 1;
+                if (li >= 2) ok = mbar_wait(&tmem_empty_bar[acc], ((uint32_t)(li >> 1) & 1u) ^ 1u, abort_flag);
+                if (!ok) break;
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t d = tmem_d + (uint32_t)(acc * p.block_cols);
+                for (int i = 0; i < n_kb; i++, it++) {
+                    const int s = it % p.stages;
+                    ok = mbar_wait(&full_bar[s], (uint32_t)(it / p.stages) & 1u, abort_flag);
+                    if (!ok) break;
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    uint8_t* a = smem + (size_t)s * stage_bytes;
+                    const uint64_t da = umma_desc_sw128(a), db = umma_desc_sw128(a + rows_bytes);
+#pragma unroll
+                    for (int k = 0; k < TILE_K / UMMA_K; k++)
+                        tcgen05_mma_bf16(d, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, (i > 0 || k > 0) ? 1u : 0u);
+                    tcgen05_commit(&empty_bar[s]);
+                }
+                if (ok) tcgen05_commit(&tmem_full_bar[acc]);
+            }
+        }
+    } else {
+        const int quad = warp & 3;
+        const int r = quad * 32 + lane;
+        bool ok = true;
+        int li = 0;
+        for (int t = blockIdx.x; t < p.total_tiles; t += gridDim.x, li++) {
+            const int col_tile = t / p.row_tiles, row_tile = t - col_tile * p.row_tiles;
+            const int acc = li & 1;
+            if (ok) ok = mbar_wait(&tmem_full_bar[acc], (uint32_t)(li >> 1) & 1u, abort_flag);
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const uint32_t taddr_row = tmem_d + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * p.block_cols);
+            const int m = row_tile * TILE_ROWS + r;
+            for (int c0 = 0; c0 < p.block_cols; c0 += 16) {
+                float v[16];
+                tmem_ld16(taddr_row + (uint32_t)c0, v);
+                const int n0 = col_tile * p.block_cols + c0;
+                if (!ok || m >= p.M || n0 >= p.N) continue;
+                store_chunk_normal(p, m, n0, min(16, p.N - n0), v);
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tmem_empty_bar[acc]);      // this warp has drained the accumulator
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
     __syncthreads();
     if (threadIdx.x == 0 && *abort_flag && p.err) atomicOr(p.err, EMBER_ERR_WAIT_LIMIT);
     if (warp == 1) {

@@ -94,6 +94,7 @@ EMBER_API int ember_gemm_tc_noalloc(const void* A, const void* W, void* out, int
     splits = (p.num_k_blocks + p.k_blocks_per_split - 1) / p.k_blocks_per_split;
     p.epilogue = epilogue; p.out = out; p.ldc = ldc; p.err = err;
     p.accum = nullptr; p.accum_ld = 0;
+    p.row_tiles = 0; p.total_tiles = 0;
     p.cluster_splits = 1; p.rows_per = TILE_ROWS;      // this variant sums its K splits with atomics into the scratch
     if (splits > 1) {
         if (epilogue == 2) {

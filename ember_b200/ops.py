@@ -281,7 +281,8 @@ def gemm_tc_usable(x: torch.Tensor, w: torch.Tensor, bias, epilogue: int) -> boo
 def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, M: int, epilogue: int = EPI_STORE,
             err: Optional[torch.Tensor] = None, stream: Optional[int] = None, split_mode: int = 0) -> None:
     """out (+)= a[:M] @ w.T on the tcgen05 tensor cores (bf16 in, fp32 accumulate).
-    ``split_mode``: how split-K partial sums are combined (0 automatic, 1 atomics, 2 cluster)."""
+    ``split_mode``: how split-K partial sums are combined (0 automatic, 1 atomics, 2 cluster); 3 runs
+    prefill-sized products one tile per block instead of persistently (for tests)."""
     _check(a, "a", torch.bfloat16)
     _check(w, "w", torch.bfloat16)
     _check(out, "out")
