@@ -190,7 +190,7 @@ def time_e2e(llm, batch, steps, warmup, context):
     import random
     rng = random.Random(1234)
     seqs = [eng.submit(Request(prompt=[rng.randrange(1000, min(100000, vocab)) for _ in range(context)],
-                               sampling=SamplingParams(temperature=0.0), max_tokens=warmup + steps + 4, ignore_eos=True))
+                               sampling=SamplingParams(temperature=0.0), max_tokens=CONTEXT - context - 8, ignore_eos=True))
             for _ in range(batch)]
     while not all(s.generated >= 1 for s in seqs):
         eng.step()

@@ -262,20 +262,35 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
                         }
                     }
                 }
-                // scale, mask, running maximum
+                // scale, mask, running maximum.  A tile that every row of this warp sees completely
+                // (all keys at or before the warp's first query, inside the window and the split) needs
+                // no mask: only tiles at the causal diagonal and at range edges pay for the compares.
                 float tmax_a = -INFINITY, tmax_b = -INFINITY;
+                const int first_q = pos0 + min(wrow, rows - 1) / G;          // earliest query position of this warp
+                const bool interior = k0 + koff >= lo && k0 + koff + NKG * 8 <= hi && k0 + koff + NKG * 8 - 1 <= first_q &&
+                                      (p.window <= 0 || k0 + koff > warp_last_q - p.window);
+                if (interior) {
 #pragma unroll
-                for (int j = 0; j < NKG; j++) {
+                    for (int j = 0; j < NKG; j++) {
 #pragma unroll
-                    for (int e = 0; e < 2; e++) {
-                        const int key = k0 + koff + j * 8 + 2 * t4 + e;
-                        const bool in = key >= lo && key < hi;
-                        const bool va = in && key <= qpos_a && (p.window <= 0 || key > qpos_a - p.window);
-                        const bool vb2 = in && key <= qpos_b && (p.window <= 0 || key > qpos_b - p.window);
-                        s[j][e] = va ? s[j][e] * p.scale_log2 : -INFINITY;
-                        s[j][2 + e] = vb2 ? s[j][2 + e] * p.scale_log2 : -INFINITY;
-                        tmax_a = fmaxf(tmax_a, s[j][e]);
-                        tmax_b = fmaxf(tmax_b, s[j][2 + e]);
+                        for (int e = 0; e < 4; e++) s[j][e] *= p.scale_log2;
+                        tmax_a = fmaxf(tmax_a, fmaxf(s[j][0], s[j][1]));
+                        tmax_b = fmaxf(tmax_b, fmaxf(s[j][2], s[j][3]));
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < NKG; j++) {
+#pragma unroll
+                        for (int e = 0; e < 2; e++) {
+                            const int key = k0 + koff + j * 8 + 2 * t4 + e;
+                            const bool in = key >= lo && key < hi;
+                            const bool va = in && key <= qpos_a && (p.window <= 0 || key > qpos_a - p.window);
+                            const bool vb2 = in && key <= qpos_b && (p.window <= 0 || key > qpos_b - p.window);
+                            s[j][e] = va ? s[j][e] * p.scale_log2 : -INFINITY;
+                            s[j][2 + e] = vb2 ? s[j][2 + e] * p.scale_log2 : -INFINITY;
+                            tmax_a = fmaxf(tmax_a, s[j][e]);
+                            tmax_b = fmaxf(tmax_b, s[j][2 + e]);
+                        }
                     }
                 }
                 tmax_a = fmaxf(tmax_a, __shfl_xor_sync(0xffffffffu, tmax_a, 1));

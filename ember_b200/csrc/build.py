@@ -23,7 +23,7 @@ _HERE = os.path.dirname(os.path.abspath(__file__))
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--shared", "-Xcompiler", "-fPIC", "-Xcompiler", "-fvisibility=hidden",
               "--expt-relaxed-constexpr"]
-SOURCES = ("elementwise", "gemm_simt", "attention", "sampling", "gemm_tc", "attention_tc", "no_alloc")
+SOURCES = ("elementwise", "gemm_simt", "attention", "sampling", "gemm_tc", "attention_tc", "attention_fa", "no_alloc")
 _EXTRA_LIBS = {}
 
 _lock = threading.Lock()

@@ -320,6 +320,37 @@ def attention_tc_tile_queries(group: int) -> int:
     return 64 // group if 1 <= group <= 64 else 0
 
 
+FA_ENABLED = True
+
+
+def attention_fa_supported(head_dim: int, group: int, page_tokens: int) -> bool:
+    """Whether the tcgen05 prefill attention takes this geometry (the rule of ember_attention_fa_supported)."""
+    return (TC_ENABLED and FA_ENABLED and head_dim == 128 and page_tokens in (16, 32, 64)
+            and 1 <= group <= 128 and 128 % group == 0)
+
+
+def attention_fa_tile_queries(group: int) -> int:
+    return 128 // group
+
+
+def attention_fa(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: torch.Tensor, n_heads: int,
+                 n_kv: int, head_dim: int, tiles: torch.Tensor, n_tiles: int, block_table: torch.Tensor, page: int,
+                 window: int, scale: float, err: Optional[torch.Tensor] = None, stream: Optional[int] = None) -> None:
+    """bf16 causal attention of prompt portions on tcgen05 tensor cores (S and O in tensor memory)."""
+    _check(q, "q", torch.bfloat16)
+    _check(out, "out", torch.bfloat16)
+    _check(k_pool, "k_pool", torch.bfloat16)
+    _check(v_pool, "v_pool", torch.bfloat16)
+    _check(tiles, "tiles", torch.int32)
+    _check(block_table, "block_table", torch.int32)
+    if k_pool.dim() != 4 or tuple(k_pool.shape[1:]) != (n_kv, page, head_dim) or v_pool.shape != k_pool.shape:
+        raise KernelError(f"attention: pools {tuple(k_pool.shape)} are not [pages, {n_kv}, {page}, {head_dim}]")
+    lib = _lib("attention_fa")
+    _call(lib, lib.ember_attention_fa, _p(q), _p(k_pool), _p(v_pool), _p(out), c_int(n_heads), c_int(n_kv), c_int(head_dim),
+          _p(tiles), c_int(n_tiles), _p(block_table), c_int(block_table.shape[-1]), c_int(page), c_int(k_pool.shape[0]),
+          c_int(window), c_float(scale), _p(err), c_void_p(stream if stream is not None else current_stream_ptr()))
+
+
 def attention_tc(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: torch.Tensor, mode: int,
                  n_heads: int, n_kv: int, head_dim: int, tiles: torch.Tensor, n_tiles: int, block_table: torch.Tensor,
                  page: int, window: int, scale: float, n_splits: int = 1, split_keys: int = 0,

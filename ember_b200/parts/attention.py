@@ -103,9 +103,17 @@ class Attention(Mixer):
         return (ops.attention_tc_supported(s.head_dim, s.group, rt.page_tokens, 0),
                 ops.attention_tc_supported(s.head_dim, s.group, rt.page_tokens, 1))
 
+    def _fa(self) -> bool:
+        """Whether prompt portions go to the tcgen05 kernel (needs the single-token kernel beside it)."""
+        s, rt = self.spec, self.rt
+        return (rt.dtype == torch.bfloat16 and ops.attention_fa_supported(s.head_dim, s.group, rt.page_tokens)
+                and self._tc_modes()[1])
+
     def tile_requests(self):
         s = self.spec
         multi, single = self._tc_modes()
+        if self._fa():
+            return [(ops.attention_fa_tile_queries(s.group), "multi"), (1, "single")]
         if multi:
             tq = ops.attention_tc_tile_queries(s.group)
             return [(tq, "multi"), (1, "single")] if single else [(tq, "all")]
@@ -123,10 +131,16 @@ class Attention(Mixer):
                 ops.attention_tc(q, cache.k, cache.v, out, 0, *args, tiles, n, table, cache.page_tokens, s.window,
                                  self.scale, err=ctx.err, stream=ctx.stream)
                 return
-            tiles, n = ctx.attention_tiles(tq, "multi")
-            if n:
-                ops.attention_tc(q, cache.k, cache.v, out, 0, *args, tiles, n, table, cache.page_tokens, s.window,
-                                 self.scale, err=ctx.err, stream=ctx.stream)
+            if self._fa():
+                tiles, n = ctx.attention_tiles(ops.attention_fa_tile_queries(s.group), "multi")
+                if n:
+                    ops.attention_fa(q, cache.k, cache.v, out, *args, tiles, n, table, cache.page_tokens, s.window,
+                                     self.scale, err=ctx.err, stream=ctx.stream)
+            else:
+                tiles, n = ctx.attention_tiles(tq, "multi")
+                if n:
+                    ops.attention_tc(q, cache.k, cache.v, out, 0, *args, tiles, n, table, cache.page_tokens, s.window,
+                                     self.scale, err=ctx.err, stream=ctx.stream)
             tiles, n = ctx.attention_tiles(1, "single")
             if n:
                 # cut long key ranges so that about two waves of blocks share the work; splits are

@@ -185,7 +185,8 @@ def attention_ref(q, k, v, scale, window):
 
 
 @pytest.mark.parametrize("heads,kv,D,page", [(4, 2, 16, 16), (6, 1, 32, 16), (8, 8, 64, 32), (16, 8, 128, 16), (2, 1, 256, 16),
-                                             (12, 4, 80, 16), (12, 2, 128, 64), (5, 1, 64, 16), (32, 2, 64, 16)])
+                                             (12, 4, 80, 16), (12, 2, 128, 64), (5, 1, 64, 16), (32, 2, 64, 16),
+                                             (8, 8, 128, 32), (8, 2, 128, 16), (16, 1, 128, 16)])
 @pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("window", [0, 37])
 def test_attention_general(heads, kv, D, page, dt, window):
@@ -248,6 +249,16 @@ def test_attention_general(heads, kv, D, page, dt, window):
         ops.attention_tc(q_all.view(T, -1), kp.to(dev), vp.to(dev), out2, 0, heads, kv, D, all_tiles, all_tiles.shape[0],
                          perm.to(dev), page, window, scale, err=err)
         assert int(err.item()) == 0 and rel(out2.float().view(T, heads, D), want) < 6e-3
+    if dt == torch.bfloat16 and ops.attention_fa_supported(D, heads // kv, page):
+        # the tcgen05 kernel on the prompt portions of the same case
+        out = torch.zeros(T, heads * D, device=dev, dtype=dt)
+        tq = ops.attention_fa_tile_queries(heads // kv)
+        multi = torch.from_numpy(attention_tiles(batch, tq, "multi")).to(dev)
+        ops.attention_fa(q_all.view(T, -1), kp.to(dev), vp.to(dev), out, heads, kv, D, multi, multi.shape[0],
+                         perm.to(dev), page, window, scale, err=err)
+        assert int(err.item()) == 0
+        n_multi = sum(n for n in new if n > 1)
+        assert rel(out.float().view(T, heads, D)[:n_multi], want[:n_multi]) < 6e-3
     for n_splits, split_keys in ((1, 0), (6, 128)):
         out = torch.zeros(T, heads * D, device=dev, dtype=dt)
         po = torch.empty(T * heads * n_splits * D, device=dev)
