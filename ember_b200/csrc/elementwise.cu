@@ -35,13 +35,59 @@ __global__ void embed_kernel(const int* __restrict__ tokens, const TW* __restric
 // `rows` (nullable) gathers input rows: the final norm runs only on the rows whose logits
 // are wanted.
 template <typename TO>
-__global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restrict__ rows,
-                               const float* __restrict__ w, float eps, TO* __restrict__ out, int H) {
+__device__ __forceinline__ void store4(TO* dst, float a, float b, float c, float d);
+template <>
+__device__ __forceinline__ void store4<float>(float* dst, float a, float b, float c, float d) {
+    *reinterpret_cast<float4*>(dst) = make_float4(a, b, c, d);
+}
+template <>
+__device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16* dst, float a, float b, float c, float d) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+    uint2 u;
+    u.x = *reinterpret_cast<uint32_t*>(&lo);
+    u.y = *reinterpret_cast<uint32_t*>(&hi);
+    *reinterpret_cast<uint2*>(dst) = u;
+}
+
+constexpr int NORM_THREADS = 256;
+constexpr int NORM_VEC = 8;      // float4 per thread kept in registers: rows up to 256 * 8 * 4 = 8192 wide
+
+// Rows whose width is a multiple of 4 and at most 8192 are read once, 16 bytes at a time, and kept in
+// registers between the reduction and the scaling; other widths take the two-pass scalar path.
+template <typename TO>
+__global__ void __launch_bounds__(NORM_THREADS)
+rmsnorm_kernel(const float* __restrict__ x, const int* __restrict__ rows,
+               const float* __restrict__ w, float eps, TO* __restrict__ out, int H) {
     __shared__ float scratch[32];
     pdl_launch_dependents();
     pdl_wait();
     const int r = blockIdx.x;
     const float* in = x + (size_t)(rows ? rows[r] : r) * H;
+    TO* o = out + (size_t)r * H;
+    const int nvec = H >> 2;
+    if ((H & 3) == 0 && nvec <= NORM_THREADS * NORM_VEC) {
+        float4 v[NORM_VEC];
+        float ss = 0.0f;
+#pragma unroll
+        for (int i = 0; i < NORM_VEC; i++) {
+            const int idx = threadIdx.x + i * NORM_THREADS;
+            if (idx < nvec) {
+                v[i] = reinterpret_cast<const float4*>(in)[idx];
+                ss = fmaf(v[i].x, v[i].x, fmaf(v[i].y, v[i].y, fmaf(v[i].z, v[i].z, fmaf(v[i].w, v[i].w, ss))));
+            }
+        }
+        ss = block_sum(ss, scratch);
+        const float scale = 1.0f / sqrtf(ss / (float)H + eps);
+#pragma unroll
+        for (int i = 0; i < NORM_VEC; i++) {
+            const int idx = threadIdx.x + i * NORM_THREADS;
+            if (idx < nvec) {
+                const float4 g = reinterpret_cast<const float4*>(w)[idx];
+                store4<TO>(o + 4 * idx, g.x * (v[i].x * scale), g.y * (v[i].y * scale), g.z * (v[i].z * scale), g.w * (v[i].w * scale));
+            }
+        }
+        return;
+    }
     float ss = 0.0f;
     for (int i = threadIdx.x; i < H; i += blockDim.x) {
         float v = in[i];
@@ -49,7 +95,6 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restric
     }
     ss = block_sum(ss, scratch);
     const float scale = 1.0f / sqrtf(ss / (float)H + eps);
-    TO* o = out + (size_t)r * H;
     for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = from_float<TO>(w[i] * (in[i] * scale));
 }
 
@@ -60,6 +105,25 @@ __global__ void rmsnorm_kernel(const float* __restrict__ x, const int* __restric
 //         the first `rotary` elements with angle = float(pos) * inv_freq[i] in fp32.
 //   q -> q_out[t, head, :];  k, v -> page bt[seq][pos / page], slot pos % page of the pools,
 //   layout [page][kv_head][slot][D].
+template <typename T>
+__device__ __forceinline__ float2 load2(const T* p);
+template <>
+__device__ __forceinline__ float2 load2<float>(const float* p) { return *reinterpret_cast<const float2*>(p); }
+template <>
+__device__ __forceinline__ float2 load2<__nv_bfloat16>(const __nv_bfloat16* p) {
+    return __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(p));
+}
+template <typename T>
+__device__ __forceinline__ void store2(T* p, float a, float b);
+template <>
+__device__ __forceinline__ void store2<float>(float* p, float a, float b) { *reinterpret_cast<float2*>(p) = make_float2(a, b); }
+template <>
+__device__ __forceinline__ void store2<__nv_bfloat16>(__nv_bfloat16* p, float a, float b) {
+    *reinterpret_cast<__nv_bfloat162*>(p) = __floats2bfloat162_rn(a, b);
+}
+
+// One block per token.  The sines and cosines of the token's position are computed once and shared
+// by all heads; then each warp takes head slots in turn (element pairs are loaded and stored together).
 template <typename T>
 __global__ void qk_norm_rope_store_kernel(
     const T* __restrict__ qkv, int ld, int n_heads, int n_kv, int D,
@@ -74,54 +138,64 @@ __global__ void qk_norm_rope_store_kernel(
     pdl_wait();
     const int warps = blockDim.x >> 5, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int t = blockIdx.x;
-    const int slot = blockIdx.y * warps + warp;
     const int slots = n_heads + 2 * n_kv;
-    if (slot >= slots) return;
-    float* s = smem + (size_t)warp * D;
-
-    const int kind = slot < n_heads ? 0 : (slot < n_heads + n_kv ? 1 : 2);  // q, k, v
-    if (kind != 0 && !write_kv) return;
-    const T* src = qkv + (size_t)t * ld + (size_t)slot * D;
-
-    float ss = 0.0f;
-    for (int i = lane; i < D; i += 32) {
-        float v = to_float(src[i]);
-        s[i] = v;
-        ss = fmaf(v, v, ss);
-    }
-    const float* nw = kind == 0 ? q_norm_w : (kind == 1 ? k_norm_w : nullptr);
-    if (nw) {
-        ss = warp_sum(ss);
-        const float scale = 1.0f / sqrtf(ss / (float)D + eps);
-        for (int i = lane; i < D; i += 32) s[i] = nw[i] * (s[i] * scale);
-    }
-    __syncwarp();
+    const int half = (inv_freq && rotary > 0) ? rotary >> 1 : 0;
+    float* cs = smem;                 // [half]
+    float* sn = cs + half;            // [half]
+    float* bufs = sn + half;          // [warps][D]
     const int pos = positions[t];
-    if (kind != 2 && inv_freq && rotary > 0) {
-        const int half = rotary >> 1;
-        for (int i = lane; i < half; i += 32) {
-            float sn, cs;
-            sincosf((float)pos * inv_freq[i], &sn, &cs);
-            const float a = s[i], b = s[i + half];
-            s[i] = a * cs - b * sn;
-            s[i + half] = b * cs + a * sn;
+    for (int i = threadIdx.x; i < half; i += blockDim.x) sincosf((float)pos * inv_freq[i], &sn[i], &cs[i]);
+    __syncthreads();
+
+    int blk = -1;
+    if (write_kv) {
+        blk = block_table[(size_t)seq_of[t] * max_blocks + pos / page];
+        if (blk < 0 || blk >= num_pages) {
+            if (threadIdx.x == 0 && err) atomicOr(err, EMBER_ERR_PAGE_RANGE);
+            blk = -1;
+        }
+    }
+    float* s = bufs + (size_t)warp * D;
+    // blockIdx.y splits the head slots between blocks when a step has few tokens
+    for (int slot = blockIdx.y * warps + warp; slot < slots; slot += warps * gridDim.y) {
+        const int kind = slot < n_heads ? 0 : (slot < n_heads + n_kv ? 1 : 2);  // q, k, v
+        if (kind != 0 && (!write_kv || blk < 0)) continue;
+        const T* src = qkv + (size_t)t * ld + (size_t)slot * D;
+        float ss = 0.0f;
+        for (int i = 2 * lane; i < D; i += 64) {
+            const float2 v = load2<T>(src + i);
+            s[i] = v.x;
+            s[i + 1] = v.y;
+            ss = fmaf(v.x, v.x, fmaf(v.y, v.y, ss));
+        }
+        const float* nw = kind == 0 ? q_norm_w : (kind == 1 ? k_norm_w : nullptr);
+        if (nw) {
+            ss = warp_sum(ss);
+            const float scale = 1.0f / sqrtf(ss / (float)D + eps);
+            for (int i = 2 * lane; i < D; i += 64) {
+                s[i] = nw[i] * (s[i] * scale);
+                s[i + 1] = nw[i + 1] * (s[i + 1] * scale);
+            }
         }
         __syncwarp();
+        if (kind != 2 && half > 0) {
+            for (int i = lane; i < half; i += 32) {
+                const float a = s[i], b = s[i + half];
+                s[i] = a * cs[i] - b * sn[i];
+                s[i + half] = b * cs[i] + a * sn[i];
+            }
+            __syncwarp();
+        }
+        T* dst;
+        if (kind == 0) {
+            dst = q_out + ((size_t)t * n_heads + slot) * D;
+        } else {
+            const int kvh = kind == 1 ? slot - n_heads : slot - n_heads - n_kv;
+            dst = (kind == 1 ? k_pool : v_pool) + (((size_t)blk * n_kv + kvh) * page + (pos % page)) * D;
+        }
+        for (int i = 2 * lane; i < D; i += 64) store2<T>(dst + i, s[i], s[i + 1]);
+        __syncwarp();
     }
-    if (kind == 0) {
-        T* dst = q_out + ((size_t)t * n_heads + slot) * D;
-        for (int i = lane; i < D; i += 32) dst[i] = from_float<T>(s[i]);
-        return;
-    }
-    const int kvh = kind == 1 ? slot - n_heads : slot - n_heads - n_kv;
-    const int blk = block_table[(size_t)seq_of[t] * max_blocks + pos / page];
-    if (blk < 0 || blk >= num_pages) {
-        if (lane == 0 && err) atomicOr(err, EMBER_ERR_PAGE_RANGE);
-        return;
-    }
-    T* pool = kind == 1 ? k_pool : v_pool;
-    T* dst = pool + (((size_t)blk * n_kv + kvh) * page + (pos % page)) * D;
-    for (int i = lane; i < D; i += 32) dst[i] = from_float<T>(s[i]);
 }
 
 // out[m, j] = silu(x[m, 2j]) * x[m, 2j+1] for an unfused gate/up product (interleaved rows).
@@ -159,7 +233,8 @@ EMBER_API int ember_rmsnorm(const float* x, const int* rows, const float* w, flo
     if (n_rows <= 0) return 0;
     if (H <= 0) return fail("rmsnorm: bad width %d", H);
     cudaStream_t st = (cudaStream_t)stream;
-    const int threads = H >= 2048 ? 512 : (H >= 512 ? 256 : 128);
+    if ((((uintptr_t)x) | ((uintptr_t)w) | ((uintptr_t)out)) & 15) return fail("rmsnorm: buffers must be 16-byte aligned");
+    const int threads = NORM_THREADS;
     if (out_dtype == EMBER_F32)
         launch_kernel(rmsnorm_kernel<float>, n_rows, threads, 0, st, x, rows, w, eps, (float*)out, H);
     else if (out_dtype == EMBER_BF16)
@@ -184,8 +259,13 @@ EMBER_API int ember_qk_norm_rope_store(const void* qkv, int dtype, int T, int ld
     cudaStream_t st = (cudaStream_t)stream;
     const int slots = n_heads + 2 * n_kv;
     const int warps = slots < 8 ? slots : 8;
-    dim3 grid(T, (slots + warps - 1) / warps);
-    const size_t smem = (size_t)warps * D * sizeof(float);
+    int ny = (296 + T - 1) / T;                       // enough blocks for a decode step of a few tokens
+    const int ny_max = (slots + warps - 1) / warps;
+    if (ny > ny_max) ny = ny_max;
+    if (ny < 1) ny = 1;
+    dim3 grid(T, ny);
+    const size_t smem = ((size_t)warps * D + (size_t)(inv_freq ? rotary : 0)) * sizeof(float);
+    if (ld & 1) return fail("qk_norm_rope_store: the row stride %d must be even", ld);
     if (dtype == EMBER_F32)
         launch_kernel(qk_norm_rope_store_kernel<float>, grid, warps * 32, smem, st,
             (const float*)qkv, ld, n_heads, n_kv, D, q_norm_w, k_norm_w, eps, inv_freq, rotary, positions, seq_of,
