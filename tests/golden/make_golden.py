@@ -25,7 +25,7 @@ import numpy as np
 import torch
 
 sys.path.insert(0, os.path.join(os.path.dirname(os.path.abspath(__file__)), "..", ".."))
-from tests.tiny_configs import TINY, tiny_config, tiny_prompts  # noqa: E402
+from tests.tiny_configs import GOLDEN_CONFIGS, TINY, tiny_config, tiny_prompts  # noqa: E402
 from ember_b200.weights import write_model_dir  # noqa: E402
 
 
@@ -51,7 +51,7 @@ def main() -> None:
                            "-I", os.path.join(args.reference, "tests"), os.path.join(here, "ref_driver.cpp"),
                            os.path.join(build, "libember_core.a"), "-lpthread", "-o", driver])
     out = {}
-    for name in TINY:
+    for name in GOLDEN_CONFIGS:
         cfg = tiny_config(name)
         mdir = os.path.join(work, f"model_{name}")
         write_model_dir(cfg, mdir, seed=TINY[name]["seed"], dtype=torch.bfloat16, std=TINY[name]["std"],

@@ -8,7 +8,7 @@ import pytest
 import torch
 
 from tests.plain.qwen3_plain import PlainQwen3
-from tests.tiny_configs import TINY, tiny_prompts
+from tests.tiny_configs import GOLDEN_CONFIGS, TINY, tiny_prompts
 
 GOLDEN = os.path.join(os.path.dirname(__file__), "golden", "qwen3_reference_logits.npz")
 
@@ -18,7 +18,7 @@ def _rel(a, b):
     return float(np.linalg.norm(a - b) / max(np.linalg.norm(b), 1e-30))
 
 
-@pytest.mark.parametrize("name", sorted(TINY))
+@pytest.mark.parametrize("name", GOLDEN_CONFIGS)
 def test_plain_matches_reference_cpu_backend(name, tiny_model_dirs):
     g = np.load(GOLDEN)
     mdir = tiny_model_dirs[name]

@@ -19,7 +19,20 @@ TINY = {
                         intermediate_size=256, num_hidden_layers=3, num_attention_heads=6, num_key_value_heads=1,
                         head_dim=32, rope_theta=1000000.0, rms_norm_eps=1e-5, tie_word_embeddings=False,
                         max_position_embeddings=256, attention_bias=False)),
+    # two more shapes that reach the tensor-core attention kernels in bfloat16: head size 128 with a
+    # group of 2 (tcgen05 prompt kernel + key-split decode kernel) and head size 64 with a group of 3
+    "c": dict(seed=31, std=0.04, norm_std=0.08,
+              json=dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=777, hidden_size=256,
+                        intermediate_size=328, num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2,
+                        head_dim=128, rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=True,
+                        max_position_embeddings=512, attention_bias=False)),
+    "d": dict(seed=37, std=0.04, norm_std=0.08,
+              json=dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=640, hidden_size=136,
+                        intermediate_size=200, num_hidden_layers=2, num_attention_heads=3, num_key_value_heads=1,
+                        head_dim=64, rope_theta=10000.0, rms_norm_eps=1e-5, tie_word_embeddings=False,
+                        max_position_embeddings=512, attention_bias=False)),
 }
+GOLDEN_CONFIGS = ("a", "b")          # the ones the reference's CPU backend was run on
 
 
 def tiny_config(name: str) -> Qwen3Config:
@@ -29,5 +42,5 @@ def tiny_config(name: str) -> Qwen3Config:
 def tiny_prompts(name: str):
     rng = np.random.default_rng(1234 + ord(name))
     vocab = TINY[name]["json"]["vocab_size"]
-    lengths = (5, 17, 33) if name == "a" else (1, 31, 64, 100)
+    lengths = (5, 17, 33) if name == "a" else (1, 31, 64, 100)          # "b", "c", "d": the longer set
     return [rng.integers(0, vocab, size=n).tolist() for n in lengths]
