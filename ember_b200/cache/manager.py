@@ -17,6 +17,8 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Dict, Hashable, List, Mapping, Optional, Sequence, Tuple
 
+import numpy as np
+
 from ..parts.base import CacheNeed
 
 
@@ -93,6 +95,21 @@ class RequestCache:
     tables: List[List[int]]        # per group: physical page of each logical page, -1 once given back
     first_live: List[int]          # per group: first logical page still held
     tokens: int = 0                # tokens whose keys are in the cache
+    arrays: List[np.ndarray] = field(default_factory=list)   # per group: int32 mirror of `tables` (grown by doubling)
+
+    def table_array(self, group: int) -> np.ndarray:
+        """The group's block table as an int32 array (a view: valid until the table changes)."""
+        n = len(self.tables[group])
+        return self.arrays[group][:n]
+
+    def _mirror_append(self, group: int, page: int) -> None:
+        n = len(self.tables[group])          # the list already holds the new page at n - 1
+        a = self.arrays[group]
+        if n > a.shape[0]:
+            b = np.full(max(16, 2 * a.shape[0]), -1, dtype=np.int32)
+            b[:a.shape[0]] = a
+            self.arrays[group] = a = b
+        a[n - 1] = page
 
 
 def group_needs(needs: Mapping[int, Optional[CacheNeed]]) -> List[Tuple[CacheNeed, List[int]]]:
@@ -148,7 +165,8 @@ class CacheManager:
         if not self._free_slots:
             return None
         rc = RequestCache(slot=self._free_slots.pop(), tables=[[] for _ in self.groups],
-                          first_live=[0 for _ in self.groups])
+                          first_live=[0 for _ in self.groups],
+                          arrays=[np.full(16, -1, dtype=np.int32) for _ in self.groups])
         self._requests[request] = rc
         return rc
 
@@ -166,7 +184,9 @@ class CacheManager:
                 return False
         for g, n in zip(self.groups, need):
             for _ in range(n):
-                rc.tables[g.index].append(g.pool.allocate())
+                page = g.pool.allocate()
+                rc.tables[g.index].append(page)
+                rc._mirror_append(g.index, page)
         return True
 
     def advance(self, request: Hashable, tokens: int) -> int:
@@ -186,6 +206,7 @@ class CacheManager:
                 if table[i] >= 0:
                     g.pool.release(table[i])
                     table[i] = -1
+                    rc.arrays[g.index][i] = -1
                     freed += 1
             rc.first_live[g.index] = max(rc.first_live[g.index], min(dead, len(table)))
         return freed

@@ -62,15 +62,15 @@ def build_batch(entries: Sequence[StepEntry], cache: CacheManager, vocab_size: i
     if not entries:
         raise BatchError("a step needs at least one entry")
     seen = set()
-    tokens: List[int] = []
-    positions: List[int] = []
-    seq_of: List[int] = []
-    query_start = [0]
-    context_len: List[int] = []
+    tok_parts, pos_parts = [], []
+    counts: List[int] = []
+    starts: List[int] = []
     slots: List[int] = []
     rows: List[int] = []
-    tables: List[List[List[int]]] = [[] for _ in cache.groups]
-    for s, e in enumerate(entries):
+    tables: List[List[np.ndarray]] = [[] for _ in cache.groups]
+    at = 0
+    page = cache.page_tokens
+    for e in entries:
         if e.request in seen:
             raise BatchError(f"request {e.request!r} appears twice in one step")
         seen.add(e.request)
@@ -82,38 +82,41 @@ def build_batch(entries: Sequence[StepEntry], cache: CacheManager, vocab_size: i
         if max_positions is not None and start + n > max_positions:
             raise BatchError(f"request {e.request!r} would reach position {start + n}; the model's limit is {max_positions}")
         for g in cache.groups:
-            if g.paged and len(rc.tables[g.index]) * cache.page_tokens < start + n:
+            if g.paged and len(rc.tables[g.index]) * page < start + n:
                 raise BatchError(f"request {e.request!r} has no pages for tokens up to {start + n}")
-        for i, t in enumerate(e.tokens):
-            t = int(t)
-            if not (0 <= t < vocab_size):
-                raise BatchError(f"token id {t} is out of range (vocabulary {vocab_size})")
-            tokens.append(t)
-            positions.append(start + i)
-            seq_of.append(s)
+        tok_parts.append(np.asarray(e.tokens, dtype=np.int64))
+        pos_parts.append(np.arange(start, start + n, dtype=np.int32))
         for w in e.want:
             w = int(w)
             if not (0 <= w < n):
                 raise BatchError(f"request {e.request!r} wants row {w} of {n} tokens")
-            rows.append(query_start[-1] + w)
-        query_start.append(query_start[-1] + n)
-        context_len.append(start + n)
+            rows.append(at + w)
+        counts.append(n)
+        starts.append(start)
+        at += n
         slots.append(rc.slot)
         for g in cache.groups:
-            tables[g.index].append(rc.tables[g.index])
+            tables[g.index].append(rc.table_array(g.index))
+    tokens = np.concatenate(tok_parts) if len(tok_parts) > 1 else tok_parts[0]
+    if tokens.size and (int(tokens.min()) < 0 or int(tokens.max()) >= vocab_size):
+        bad = int(tokens[(tokens < 0) | (tokens >= vocab_size)][0])
+        raise BatchError(f"token id {bad} is out of range (vocabulary {vocab_size})")
+    counts_a = np.asarray(counts, dtype=np.int32)
+    query_start = np.zeros(len(entries) + 1, dtype=np.int32)
+    np.cumsum(counts_a, out=query_start[1:])
     bt = []
     for g in cache.groups:
         width = max(1, max(len(t) for t in tables[g.index]))
         arr = np.full((len(entries), width), -1, dtype=np.int32)
         for s, t in enumerate(tables[g.index]):
-            if t:
-                arr[s, :len(t)] = t
+            if t.shape[0]:
+                arr[s, :t.shape[0]] = t
         bt.append(arr)
     return StepBatch(
         requests=[e.request for e in entries],
-        tokens=np.asarray(tokens, dtype=np.int32), positions=np.asarray(positions, dtype=np.int32),
-        seq_of=np.asarray(seq_of, dtype=np.int32), query_start=np.asarray(query_start, dtype=np.int32),
-        context_len=np.asarray(context_len, dtype=np.int32), block_tables=bt,
+        tokens=tokens.astype(np.int32), positions=np.concatenate(pos_parts) if len(pos_parts) > 1 else pos_parts[0],
+        seq_of=np.repeat(np.arange(len(entries), dtype=np.int32), counts_a), query_start=query_start,
+        context_len=np.asarray(starts, dtype=np.int32) + counts_a, block_tables=bt,
         state_slots=np.asarray(slots, dtype=np.int32), logit_rows=np.asarray(rows, dtype=np.int32))
 
 
@@ -132,11 +135,22 @@ def attention_tiles(batch: StepBatch, tile_q: int, kind: str = "all") -> np.ndar
     """Cuts runs into tiles of at most ``tile_q`` consecutive queries:
     rows of (run, first token row, queries, position of the first query).
     ``kind`` selects the runs: "all", "multi" (two or more new tokens) or "single" (one)."""
+    qs = batch.query_start
+    lens = qs[1:] - qs[:-1]
+    if kind == "multi":
+        runs = np.nonzero(lens >= 2)[0]
+    elif kind == "single":
+        runs = np.nonzero(lens == 1)[0]
+    else:
+        runs = np.arange(batch.S)
+    if runs.size == 0:
+        return np.zeros((0, 4), dtype=np.int32)
+    if int(lens[runs].max()) <= tile_q:                 # every selected run is one tile (all decode steps)
+        first = qs[:-1][runs]
+        return np.stack([runs.astype(np.int32), first, lens[runs], batch.positions[first]], axis=1).astype(np.int32)
     out = []
-    for s in range(batch.S):
-        a, b = int(batch.query_start[s]), int(batch.query_start[s + 1])
-        if (kind == "multi" and b - a < 2) or (kind == "single" and b - a != 1):
-            continue
+    for s in runs:
+        a, b = int(qs[s]), int(qs[s + 1])
         for r in range(a, b, tile_q):
             out.append((s, r, min(tile_q, b - r), int(batch.positions[r])))
     return np.asarray(out, dtype=np.int32).reshape(-1, 4)
@@ -211,7 +225,8 @@ class StepContext:
         self.state_slots_host = batch.state_slots
         # tile_sizes: (tile_q, kind) pairs the model's mixers asked for ahead of time
         self._tiles_host = {key: attention_tiles(batch, key[0], key[1]) for key in tile_sizes}
-        # one packed upload
+        # one packed upload; device views of its pieces are made only when a part asks for them
+        # (a replayed graph needs the upload alone)
         parts = [batch.tokens, batch.positions, batch.seq_of, batch.query_start, batch.context_len,
                  batch.state_slots, batch.logit_rows] + [t.reshape(-1) for t in batch.block_tables] + \
                 [t.reshape(-1) for t in self._tiles_host.values()]
@@ -220,31 +235,39 @@ class StepContext:
             offs.append(total)
             total += (p.size + 7) // 8 * 8          # keep every array 32-byte aligned
         total = max(total, 8)
-        dev = workspace.dynamic("step.ints", max(total, 1 << 16), torch.int32)
-        self.ints = dev
+        self._parts, self._offs, self._total = parts, offs, total
+        self.ints = workspace.dynamic("step.ints", max(total, 1 << 16), torch.int32)
+        self._ng = len(batch.block_tables)
+        self._tiles = {}
         if upload:
-            host, event = workspace.pinned_ints(total)
-            hn = host.numpy()
-            for p, o in zip(parts, offs):
-                hn[o:o + p.size] = p
-            dev[:total].copy_(host[:total], non_blocking=True)
-            event.record()
+            self.upload()
 
-        def view(i, shape=None):
-            p = parts[i]
-            v = dev[offs[i]:offs[i] + p.size]
-            return v.view(shape) if shape is not None else v
+    _NAMES = {"tokens": 0, "positions": 1, "seq_of": 2, "query_start": 3, "context_len": 4, "state_slots": 5,
+              "logit_rows": 6}
 
-        self.tokens, self.positions, self.seq_of = view(0), view(1), view(2)
-        self.query_start, self.context_len, self.state_slots, self.logit_rows = view(3), view(4), view(5), view(6)
-        ng = len(batch.block_tables)
-        self._tables = [view(7 + g, batch.block_tables[g].shape) for g in range(ng)]
-        self._tiles = {key: (view(7 + ng + i, (-1, 4)) if self._tiles_host[key].size else None,
-                             int(self._tiles_host[key].shape[0]))
-                       for i, key in enumerate(self._tiles_host)}
+    def upload(self) -> None:
+        host, event = self.workspace.pinned_ints(self._total)
+        hn = host.numpy()
+        for p, o in zip(self._parts, self._offs):
+            hn[o:o + p.size] = p
+        self.ints[:self._total].copy_(host[:self._total], non_blocking=True)
+        event.record()
+
+    def _view(self, i: int, shape=None) -> torch.Tensor:
+        v = self.ints[self._offs[i]:self._offs[i] + self._parts[i].size]
+        return v.view(shape) if shape is not None else v
+
+    def __getattr__(self, name: str):
+        # device views of the packed arrays, made on first use
+        idx = StepContext._NAMES.get(name)
+        if idx is None:
+            raise AttributeError(name)
+        v = self._view(idx)
+        setattr(self, name, v)
+        return v
 
     def block_table(self, group: int) -> torch.Tensor:
-        return self._tables[group]
+        return self._view(7 + group, self.batch.block_tables[group].shape)
 
     def attention_tiles(self, tile_q: int, kind: str = "all"):
         """(device tensor [n, 4] or None, n) for tiles of up to ``tile_q`` queries over the runs of
@@ -252,6 +275,11 @@ class StepContext:
         upload; others cost a copy of their own."""
         key = (tile_q, kind)
         got = self._tiles.get(key)
+        if got is None and key in self._tiles_host:
+            i = 7 + self._ng + list(self._tiles_host).index(key)
+            host = self._tiles_host[key]
+            got = (self._view(i, (-1, 4)) if host.size else None, int(host.shape[0]))
+            self._tiles[key] = got
         if got is None:
             host = attention_tiles(self.batch, tile_q, kind)
             if host.size == 0:
@@ -261,7 +289,6 @@ class StepContext:
                 dev[:host.size].copy_(torch.from_numpy(host.reshape(-1)), non_blocking=False)
                 got = (dev[:host.size].view(-1, 4), int(host.shape[0]))
             self._tiles[key] = got
-            self._tiles_host[key] = host
         return got
 
     def buf(self, name: str, shape: Tuple[int, ...], dtype: torch.dtype) -> torch.Tensor:

@@ -21,6 +21,18 @@ def pack_params(params: Sequence[SamplingParams], counters: Sequence[int]) -> np
     return np.frombuffer(bytes(buf), dtype=np.uint8)
 
 
+_scratch = {}
+
+
+def _argmax_scratch(device, rows: int):
+    got = _scratch.get(device)
+    if got is None or got[0].numel() < rows * 32:
+        n = max(rows, 64) * 32
+        got = (torch.empty(n, dtype=torch.float32, device=device), torch.empty(n, dtype=torch.int32, device=device))
+        _scratch[device] = got
+    return got
+
+
 def sample(logits: torch.Tensor, params: Sequence[SamplingParams], counters: Sequence[int],
            out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """One token id per row of ``logits`` [rows, vocab] (fp32, device); returns int32 [rows] on the device."""
@@ -31,8 +43,7 @@ def sample(logits: torch.Tensor, params: Sequence[SamplingParams], counters: Seq
         out = torch.empty(rows, dtype=torch.int32, device=logits.device)
     if all(p.greedy for p in params):
         # argmax needs no parameters on the device and is spread over many blocks per row
-        part_v = torch.empty(rows * 32, dtype=torch.float32, device=logits.device)
-        part_i = torch.empty(rows * 32, dtype=torch.int32, device=logits.device)
+        part_v, part_i = _argmax_scratch(logits.device, rows)
         ops.argmax(logits, out, rows, part_v, part_i)
         return out
     host = torch.from_numpy(pack_params(params, counters).copy()).pin_memory()
