@@ -96,6 +96,7 @@ class RequestCache:
     first_live: List[int]          # per group: first logical page still held
     tokens: int = 0                # tokens whose keys are in the cache
     arrays: List[np.ndarray] = field(default_factory=list)   # per group: int32 mirror of `tables` (grown by doubling)
+    addrs: List[int] = field(default_factory=list)           # per group: address of the mirror (for the native packer)
 
     def table_array(self, group: int) -> np.ndarray:
         """The group's block table as an int32 array (a view: valid until the table changes)."""
@@ -109,6 +110,7 @@ class RequestCache:
             b = np.full(max(16, 2 * a.shape[0]), -1, dtype=np.int32)
             b[:a.shape[0]] = a
             self.arrays[group] = a = b
+            self.addrs[group] = a.ctypes.data
         a[n - 1] = page
 
 
@@ -164,9 +166,10 @@ class CacheManager:
             raise CacheError(f"request {request!r} is admitted twice")
         if not self._free_slots:
             return None
+        arrays = [np.full(16, -1, dtype=np.int32) for _ in self.groups]
         rc = RequestCache(slot=self._free_slots.pop(), tables=[[] for _ in self.groups],
-                          first_live=[0 for _ in self.groups],
-                          arrays=[np.full(16, -1, dtype=np.int32) for _ in self.groups])
+                          first_live=[0 for _ in self.groups], arrays=arrays,
+                          addrs=[a.ctypes.data for a in arrays])
         self._requests[request] = rc
         return rc
 

@@ -205,9 +205,11 @@ class Workspace:
 class StepContext:
     """Device form of a step: index arrays (one host-to-device copy), scratch, stream."""
 
-    def __init__(self, batch: StepBatch, workspace: Workspace, device: torch.device, max_tokens: int,
-                 err: Optional[torch.Tensor] = None, tile_sizes: Sequence[int] = (),
+    def __init__(self, batch, workspace: Workspace, device: torch.device, max_tokens: int,
+                 err: Optional[torch.Tensor] = None, tile_sizes: Sequence[Tuple[int, str]] = (),
                  max_context: Optional[int] = None, upload: bool = True):
+        """``batch`` is a ``StepBatch`` (packed here, with numpy) or a ``runtime.PackedStep`` (packed
+        already, by the native packer, with the tile lists it was asked for)."""
         self.batch = batch
         self.workspace = workspace
         self.device = device
@@ -215,29 +217,45 @@ class StepContext:
         self.T, self.S, self.R = batch.T, batch.S, batch.R
         if self.T > max_tokens:
             raise BatchError(f"the step has {self.T} tokens; the limit is {max_tokens}")
-        # an upper bound of the cached length may be given (graph replays are built for a bucket)
-        self.max_context = int(max_context) if max_context is not None else int(batch.context_len.max())
         self.err = err
         self.stream = torch.cuda.current_stream(device).cuda_stream
         # host views parts may read (toy mixers, planners)
         self.query_start_host = batch.query_start
         self.positions_host = batch.positions
         self.state_slots_host = batch.state_slots
-        # tile_sizes: (tile_q, kind) pairs the model's mixers asked for ahead of time
-        self._tiles_host = {key: attention_tiles(batch, key[0], key[1]) for key in tile_sizes}
+        self._packed = batch if hasattr(batch, "layout") else None
+        if self._packed is not None:
+            lay, S = batch.layout, batch.S
+            longest = batch.max_context
+            self._table_shapes = [(S, w) for w in batch.widths]
+            self._tile_rows = {key: int(lay.n_tiles[i]) for i, key in enumerate(batch.tile_keys)}
+            self._offs = [lay.tokens, lay.positions, lay.seq_of, lay.query_start, lay.context_len, lay.state_slots,
+                          lay.logit_rows] + [lay.tables[g] for g in range(len(batch.widths))] + \
+                         [lay.tiles[i] for i in range(len(batch.tile_keys))]
+            self._sizes = [self.T, self.T, self.T, S + 1, S, S, self.R] + [S * w for w in batch.widths] + \
+                          [4 * n for n in self._tile_rows.values()]
+            self._parts, self._total = None, int(lay.total)
+        else:
+            longest = int(batch.context_len.max())
+            # tile_sizes: (tile_q, kind) pairs the model's mixers asked for ahead of time
+            tiles_host = {key: attention_tiles(batch, key[0], key[1]) for key in tile_sizes}
+            self._table_shapes = [t.shape for t in batch.block_tables]
+            self._tile_rows = {key: int(t.shape[0]) for key, t in tiles_host.items()}
+            parts = [batch.tokens, batch.positions, batch.seq_of, batch.query_start, batch.context_len,
+                     batch.state_slots, batch.logit_rows] + [t.reshape(-1) for t in batch.block_tables] + \
+                    [t.reshape(-1) for t in tiles_host.values()]
+            offs, total = [], 0
+            for p in parts:
+                offs.append(total)
+                total += (p.size + 7) // 8 * 8          # keep every array 32-byte aligned
+            self._parts, self._offs, self._total = parts, offs, max(total, 8)
+            self._sizes = [p.size for p in parts]
+        # an upper bound of the cached length may be given (graph replays are built for a bucket)
+        self.max_context = int(max_context) if max_context is not None else longest
         # one packed upload; device views of its pieces are made only when a part asks for them
         # (a replayed graph needs the upload alone)
-        parts = [batch.tokens, batch.positions, batch.seq_of, batch.query_start, batch.context_len,
-                 batch.state_slots, batch.logit_rows] + [t.reshape(-1) for t in batch.block_tables] + \
-                [t.reshape(-1) for t in self._tiles_host.values()]
-        offs, total = [], 0
-        for p in parts:
-            offs.append(total)
-            total += (p.size + 7) // 8 * 8          # keep every array 32-byte aligned
-        total = max(total, 8)
-        self._parts, self._offs, self._total = parts, offs, total
-        self.ints = workspace.dynamic("step.ints", max(total, 1 << 16), torch.int32)
-        self._ng = len(batch.block_tables)
+        self.ints = workspace.dynamic("step.ints", max(self._total, 1 << 16), torch.int32)
+        self._ng = len(self._table_shapes)
         self._tiles = {}
         if upload:
             self.upload()
@@ -246,15 +264,22 @@ class StepContext:
               "logit_rows": 6}
 
     def upload(self) -> None:
-        host, event = self.workspace.pinned_ints(self._total)
-        hn = host.numpy()
-        for p, o in zip(self._parts, self._offs):
-            hn[o:o + p.size] = p
+        staging = self._packed.staging if self._packed is not None else None
+        if staging is not None:
+            host, event = staging
+        else:
+            host, event = self.workspace.pinned_ints(self._total)
+            hn = host.numpy()
+            if self._packed is not None:
+                hn[:self._total] = self._packed.buf[:self._total]
+            else:
+                for p, o in zip(self._parts, self._offs):
+                    hn[o:o + p.size] = p
         self.ints[:self._total].copy_(host[:self._total], non_blocking=True)
         event.record()
 
     def _view(self, i: int, shape=None) -> torch.Tensor:
-        v = self.ints[self._offs[i]:self._offs[i] + self._parts[i].size]
+        v = self.ints[self._offs[i]:self._offs[i] + self._sizes[i]]
         return v.view(shape) if shape is not None else v
 
     def __getattr__(self, name: str):
@@ -267,7 +292,7 @@ class StepContext:
         return v
 
     def block_table(self, group: int) -> torch.Tensor:
-        return self._view(7 + group, self.batch.block_tables[group].shape)
+        return self._view(7 + group, self._table_shapes[group])
 
     def attention_tiles(self, tile_q: int, kind: str = "all"):
         """(device tensor [n, 4] or None, n) for tiles of up to ``tile_q`` queries over the runs of
@@ -275,10 +300,10 @@ class StepContext:
         upload; others cost a copy of their own."""
         key = (tile_q, kind)
         got = self._tiles.get(key)
-        if got is None and key in self._tiles_host:
-            i = 7 + self._ng + list(self._tiles_host).index(key)
-            host = self._tiles_host[key]
-            got = (self._view(i, (-1, 4)) if host.size else None, int(host.shape[0]))
+        if got is None and key in self._tile_rows:
+            i = 7 + self._ng + list(self._tile_rows).index(key)
+            n = self._tile_rows[key]
+            got = (self._view(i, (-1, 4)) if n else None, n)
             self._tiles[key] = got
         if got is None:
             host = attention_tiles(self.batch, tile_q, kind)

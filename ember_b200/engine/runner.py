@@ -21,7 +21,8 @@ from ..config.spec import ModelSpec
 from ..model.causal_lm import CausalLM
 from ..parts.base import Runtime
 from ..weights.loader import WeightStore
-from .batch import BatchError, StepBatch, StepContext, StepEntry, Workspace, build_batch, pad_tables
+from .batch import BatchError, StepBatch, StepContext, StepEntry, Workspace
+from ..runtime import StepPacker
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32,
            "f32": torch.float32}
@@ -59,6 +60,7 @@ class ModelRunner:
         self.cache = CacheManager(self.model.cache_needs(), page_tokens, int(capacity_tokens), self.max_requests)
         self.storage = CacheStorage(self.cache, self.device, self.dtype)
         self.workspace = Workspace(self.device)
+        self._packer = StepPacker()
         self.err = torch.zeros(1, dtype=torch.int32, device=self.device)
         self.steps = 0
         # decode steps (one token per run) are captured into CUDA graphs, one per (runs, wanted rows,
@@ -99,36 +101,50 @@ class ModelRunner:
     def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
         """Runs the entries as one batch; returns logits [wanted rows, vocab] fp32 on the device
         (a view of a scratch buffer, valid until the next step), or None if nothing is wanted."""
-        batch = build_batch(entries, self.cache, self.spec.vocab_size, self.spec.max_positions)
-        return self.run_batch(batch)
+        graphable = self.cuda_graphs and 0 < len(entries) <= self.graph_max_runs and \
+            all(len(e.tokens) == 1 for e in entries)
+        min_widths, ctx_bucket = None, None
+        if graphable:
+            # a graph is built for a bucket of context lengths: block tables are padded to the bucket's
+            # width and the attention splits cover the bucket, so any shorter context fits
+            bucket = self.graph_context_bucket
+            longest = 1 + max(self.cache.get(e.request).tokens for e in entries)
+            ctx_bucket = (longest + bucket - 1) // bucket * bucket
+            min_widths = [max(1, ctx_bucket // self.cache.page_tokens) if g.paged else 1 for g in self.cache.groups]
+        staging = []
 
-    def run_batch(self, batch: StepBatch) -> Optional[torch.Tensor]:
+        def alloc(n: int):
+            host, event = self.workspace.pinned_ints(n)
+            staging.append((host, event))
+            return host.numpy(), host.data_ptr()
+
+        packed = self._packer.pack(entries, self.cache, self.spec.vocab_size, self.spec.max_positions,
+                           tile_keys=self.model.tile_requests(), min_widths=min_widths, alloc=alloc)
+        packed.staging = staging[0]
+        return self.run_batch(packed, ctx_bucket)
+
+    def run_batch(self, batch, graph_bucket: Optional[int] = None) -> Optional[torch.Tensor]:
+        """Runs a laid-out step (a ``PackedStep``, or a ``StepBatch`` which is packed here)."""
         if batch.T > self.max_batch_tokens:
             raise BatchError(f"the step has {batch.T} tokens; the limit is {self.max_batch_tokens}")
-        if self.cuda_graphs and batch.T == batch.S and batch.S <= self.graph_max_runs:
-            logits = self._run_decode_graph(batch)
+        if graph_bucket is not None:
+            logits = self._run_decode_graph(batch, graph_bucket)
         else:
             ctx = StepContext(batch, self.workspace, self.device, self.max_batch_tokens, err=self.err,
                               tile_sizes=self.model.tile_requests())
             logits = self.model.forward(ctx, self.storage)
+        lens = batch.context_len.tolist()
         for s, req in enumerate(batch.requests):
-            self.cache.advance(req, int(batch.context_len[s]))
+            self.cache.advance(req, lens[s])
         self.steps += 1
         return logits
 
-    def _run_decode_graph(self, batch: StepBatch) -> Optional[torch.Tensor]:
+    def _run_decode_graph(self, packed, ctx_bucket: int) -> Optional[torch.Tensor]:
         """A decode step through a captured graph.  The first step of a shape runs eagerly (it also
         allocates every buffer), the second is captured, later ones only upload the step's integers
-        and replay.  A graph is built for a bucket of context lengths: block tables are padded to
-        the bucket's width and the attention splits cover the bucket, so any shorter context fits."""
-        bucket = self.graph_context_bucket
-        ctx_bucket = (int(batch.context_len.max()) + bucket - 1) // bucket * bucket
-        widths = [max(1, ctx_bucket // self.cache.page_tokens) if g.paged else 1 for g in self.cache.groups]
-        widths = [max(w, t.shape[1]) for w, t in zip(widths, batch.block_tables)]
-        key = (batch.S, batch.R, ctx_bucket, tuple(widths))
-        padded = pad_tables(batch, widths)
-        tiles = self.model.tile_requests()
-        ctx = StepContext(padded, self.workspace, self.device, self.max_batch_tokens, err=self.err, tile_sizes=tiles,
+        and replay."""
+        key = (packed.S, packed.R, ctx_bucket, tuple(packed.widths))
+        ctx = StepContext(packed, self.workspace, self.device, self.max_batch_tokens, err=self.err,
                           max_context=ctx_bucket)          # uploads this step's integers
         entry = self._graphs.get(key)
         if entry is not None and entry[1] == self.workspace.version and entry[3] == ctx.ints.data_ptr():
@@ -143,8 +159,8 @@ class ModelRunner:
         n0 = ops.launch_count()
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
-            cap = StepContext(padded, self.workspace, self.device, self.max_batch_tokens, err=self.err,
-                              tile_sizes=tiles, max_context=ctx_bucket, upload=False)
+            cap = StepContext(packed, self.workspace, self.device, self.max_batch_tokens, err=self.err,
+                              max_context=ctx_bucket, upload=False)
             logits = self.model.forward(cap, self.storage)
         if self.workspace.version != version or cap.ints.data_ptr() != ctx.ints.data_ptr():
             # a buffer was (re)allocated while capturing: the graph holds stale pointers; run eagerly

@@ -1,0 +1,260 @@
+"""Native host runtime: the per-step packing of a batch's integer arrays (C++, C ABI, ctypes).
+
+``pack_step`` is what ``ModelRunner.step`` uses; ``engine.batch.build_batch`` states the same
+layout with numpy and is what tests compare it with.  The library is compiled with the host
+C++ compiler at first use (no CUDA needed) into the folder the kernels are built in.
+"""
+from __future__ import annotations
+
+import ctypes
+import hashlib
+import os
+import shutil
+import subprocess
+import sys
+import threading
+from ctypes import c_int, c_int32, c_uint64, c_void_p, POINTER
+from typing import Hashable, List, Optional, Sequence, Tuple
+
+import numpy as np
+
+from ..csrc import build as kernel_build
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_lock = threading.Lock()
+_lib = None
+
+TILE_KINDS = {"all": 0, "multi": 1, "single": 2}
+
+
+class StepLayout(ctypes.Structure):
+    _fields_ = [("tokens", c_int32), ("positions", c_int32), ("seq_of", c_int32), ("query_start", c_int32),
+                ("context_len", c_int32), ("state_slots", c_int32), ("logit_rows", c_int32),
+                ("tables", c_int32 * 8), ("tiles", c_int32 * 8), ("n_tiles", c_int32 * 8), ("total", c_int32),
+                ("T", c_int32), ("S", c_int32), ("R", c_int32), ("max_context", c_int32)]
+
+
+class RuntimeBuildError(RuntimeError):
+    pass
+
+
+def _compiler() -> str:
+    for cand in (os.environ.get("CXX"), shutil.which("g++"), shutil.which("c++"), shutil.which("clang++")):
+        if cand and shutil.which(cand):
+            return cand
+    raise RuntimeBuildError("no C++ compiler found (g++ / c++); the native host runtime cannot be built")
+
+
+def library() -> ctypes.CDLL:
+    global _lib
+    with _lock:
+        if _lib is not None:
+            return _lib
+        src = os.path.join(_HERE, "step_pack.cpp")
+        with open(src, "rb") as f:
+            digest = hashlib.sha256(f.read()).hexdigest()[:16]
+        so = os.path.join(kernel_build.build_dir(), "libember_runtime.so")
+        stamp = so + ".stamp"
+        current = os.path.isfile(so) and os.path.isfile(stamp) and open(stamp).read().strip() == digest
+        if not current:
+            print("[ember_b200] compiling the host runtime (step_pack.cpp) ...", file=sys.stderr, flush=True)
+            tmp = f"{so}.{os.getpid()}.tmp"
+            proc = subprocess.run([_compiler(), "-O2", "-std=c++17", "-shared", "-fPIC", "-o", tmp, src],
+                                  capture_output=True, text=True)
+            if proc.returncode != 0:
+                raise RuntimeBuildError(f"the C++ compiler failed on step_pack.cpp:\n{proc.stdout}{proc.stderr}")
+            os.replace(tmp, so)
+            with open(stamp, "w") as f:
+                f.write(digest)
+        lib = ctypes.CDLL(so)
+        vp = c_void_p                 # addresses are passed as plain integers
+        lib.ember_step_layout.restype = c_int
+        lib.ember_step_layout.argtypes = [c_int, vp, vp, vp, vp, vp, c_int, vp, c_int, vp, vp, c_int,
+                                          POINTER(StepLayout)]
+        lib.ember_step_pack.restype = None
+        lib.ember_step_pack.argtypes = [c_int, vp, vp, vp, vp, vp, vp, c_int, vp, vp, vp,
+                                        c_int, vp, vp, POINTER(StepLayout), vp]
+        _lib = lib
+        return lib
+
+
+_ERRORS = {-1: "a step needs at least one entry", -2: "a request brings no tokens",
+           -3: "a wanted row lies outside its request's tokens", -4: "a token id is out of range",
+           -5: "too many cache groups or tile lists for one step"}
+
+
+class PackedStep:
+    """A step's integer arrays in one buffer, with the offsets of its pieces."""
+
+    def __init__(self, requests, layout: StepLayout, buf: np.ndarray, widths: Sequence[int],
+                 tile_keys: Sequence[Tuple[int, str]]):
+        self.requests = requests
+        self.layout = layout
+        self.buf = buf
+        self.widths = list(widths)
+        self.tile_keys = list(tile_keys)
+        self.T, self.S, self.R = layout.T, layout.S, layout.R
+        self.max_context = layout.max_context
+        self.total = layout.total
+        self.staging = None          # (pinned tensor, event) when ``buf`` is a view of staging memory
+
+    @property
+    def block_tables(self):
+        return [self.block_table(g) for g in range(len(self.widths))]
+
+    def piece(self, offset: int, n: int) -> np.ndarray:
+        return self.buf[offset:offset + n]
+
+    @property
+    def tokens(self):
+        return self.piece(self.layout.tokens, self.T)
+
+    @property
+    def positions(self):
+        return self.piece(self.layout.positions, self.T)
+
+    @property
+    def seq_of(self):
+        return self.piece(self.layout.seq_of, self.T)
+
+    @property
+    def query_start(self):
+        return self.piece(self.layout.query_start, self.S + 1)
+
+    @property
+    def context_len(self):
+        return self.piece(self.layout.context_len, self.S)
+
+    @property
+    def state_slots(self):
+        return self.piece(self.layout.state_slots, self.S)
+
+    @property
+    def logit_rows(self):
+        return self.piece(self.layout.logit_rows, self.R)
+
+    def block_table(self, group: int) -> np.ndarray:
+        return self.piece(self.layout.tables[group], self.S * self.widths[group]).reshape(self.S, self.widths[group])
+
+    def tiles(self, index: int) -> np.ndarray:
+        return self.piece(self.layout.tiles[index], self.layout.n_tiles[index] * 4).reshape(-1, 4)
+
+
+class StepPacker:
+    """Packs steps through the native library.  Keeps its input arrays (and their addresses) across
+    steps, so a step costs one pass over the entries and two calls into the library."""
+
+    def __init__(self):
+        self._lib = library()
+        self._cap_runs = self._cap_tokens = self._cap_want = self._cap_tables = 0
+        self._small = {}
+        self._lay = None
+
+    def _array(self, name: str, n: int, dtype=np.int32):
+        got = self._small.get(name)
+        if got is None or got[0].shape[0] < n:
+            arr = np.zeros(max(16, 2 * n), dtype=dtype)
+            got = (arr, arr.ctypes.data)
+            self._small[name] = got
+        return got
+
+    def pack(self, entries, cache, vocab_size: int, max_positions: Optional[int] = None,
+             tile_keys: Sequence[Tuple[int, str]] = (), widths: Optional[Sequence[int]] = None,
+             min_widths: Optional[Sequence[int]] = None, alloc=None) -> PackedStep:
+        """Checks the entries, reads cached lengths, slots and block tables from ``cache`` (pages for the
+        new tokens must already be ensured) and packs the step.  ``widths`` sets the block tables' widths,
+        ``min_widths`` only pads them (graph buckets); ``alloc(n)`` returns (int32 array to fill, its
+        address) — pinned staging memory — else a new array is made."""
+        from ..engine.batch import BatchError
+        lib = self._lib
+        S = len(entries)
+        if S == 0:
+            raise BatchError("a step needs at least one entry")
+        groups = cache.groups
+        G = len(groups)
+        page = cache.page_tokens
+        requests, counts, starts, slots, want_counts = [], [], [], [], []
+        tok_flat, want_flat = [], []
+        table_addr = [0] * (G * S)
+        table_lens = [0] * (G * S)
+        get = cache.get
+        s = 0
+        for e in entries:
+            toks = e.tokens
+            n = len(toks)
+            rc = get(e.request)
+            start = rc.tokens
+            if max_positions is not None and start + n > max_positions:
+                raise BatchError(f"request {e.request!r} would reach position {start + n}; "
+                                 f"the model's limit is {max_positions}")
+            tables, addrs = rc.tables, rc.addrs
+            for g in groups:
+                gi = g.index
+                ln = len(tables[gi])
+                if ln * page < start + n and g.paged:
+                    raise BatchError(f"request {e.request!r} has no pages for tokens up to {start + n}")
+                table_addr[gi * S + s] = addrs[gi]
+                table_lens[gi * S + s] = ln
+            requests.append(e.request)
+            counts.append(n)
+            starts.append(start)
+            slots.append(rc.slot)
+            want_counts.append(len(e.want))
+            tok_flat += toks
+            if e.want:
+                want_flat += e.want
+            s += 1
+        if len(set(requests)) != S:
+            raise BatchError("a request appears twice in one step")
+        if widths is None:
+            widths = [max(1, max(table_lens[g * S:(g + 1) * S])) for g in range(G)]
+            if min_widths is not None:
+                widths = [max(w, m) for w, m in zip(widths, min_widths)]
+        L = len(tile_keys)
+        T, R = len(tok_flat), len(want_flat)
+        # one int32 scratch array holds every small input; the table addresses have their own
+        n_small = 4 * S + T + R + G + 2 * L
+        ints, ints_at = self._array("ints", n_small + 8)
+        try:
+            ints[:n_small] = counts + starts + slots + want_counts + tok_flat + want_flat + list(widths) + \
+                [k[0] for k in tile_keys] + [TILE_KINDS[k[1]] for k in tile_keys]
+        except (OverflowError, ValueError, TypeError):
+            raise BatchError("a token id or a wanted row is not a 32-bit integer") from None
+        o_counts, o_starts, o_slots, o_wc = ints_at, ints_at + 4 * S, ints_at + 8 * S, ints_at + 12 * S
+        o_tok = ints_at + 16 * S
+        o_want = o_tok + 4 * T
+        o_widths = o_want + 4 * R
+        o_tq = o_widths + 4 * G
+        o_tk = o_tq + 4 * L
+        lay = StepLayout()
+        lay_ref = ctypes.byref(lay)
+        code = lib.ember_step_layout(S, o_counts, o_starts, o_wc, o_tok, o_want, G, o_widths, L, o_tq, o_tk,
+                                     int(vocab_size), lay_ref)
+        if code != 0:
+            raise BatchError(_ERRORS.get(code, f"the step could not be laid out (code {code})") +
+                             f" (vocabulary {vocab_size})")
+        if alloc is not None:
+            buf, buf_at = alloc(lay.total)
+        else:
+            buf = np.empty(lay.total, dtype=np.int32)
+            buf_at = buf.ctypes.data
+        addr, addr_at = self._array("addr", G * S + 1, np.uint64)
+        lens, lens_at = self._array("lens", G * S + 1)
+        addr[:G * S] = table_addr
+        lens[:G * S] = table_lens
+        lib.ember_step_pack(S, o_counts, o_starts, o_slots, o_wc, o_tok, o_want, G, o_widths, addr_at, lens_at,
+                            L, o_tq, o_tk, lay_ref, buf_at)
+        return PackedStep(requests, lay, buf, widths, tile_keys)
+
+
+_default_packer = None
+
+
+def pack_step(entries, cache, vocab_size: int, max_positions: Optional[int] = None,
+              tile_keys: Sequence[Tuple[int, str]] = (), widths: Optional[Sequence[int]] = None,
+              min_widths: Optional[Sequence[int]] = None, alloc=None) -> PackedStep:
+    """``StepPacker.pack`` with a packer shared by the process (not for concurrent use)."""
+    global _default_packer
+    if _default_packer is None:
+        _default_packer = StepPacker()
+    return _default_packer.pack(entries, cache, vocab_size, max_positions, tile_keys, widths, min_widths, alloc)
