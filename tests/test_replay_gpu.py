@@ -60,7 +60,8 @@ def replay(model_dir, dtype, steps, capacity):
     return outputs
 
 
-LENGTHS = {"a": (5, 17, 33, 100), "b": (1, 31, 64, 100, 130), "c": (3, 70, 200, 333), "d": (2, 65, 129, 260)}
+LENGTHS = {"a": (5, 17, 33, 100), "b": (1, 31, 64, 100, 130), "c": (3, 70, 200, 333), "d": (2, 65, 129, 260),
+           "e": (4, 47, 97, 150)}
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

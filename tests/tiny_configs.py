@@ -31,6 +31,13 @@ TINY = {
                         intermediate_size=200, num_hidden_layers=2, num_attention_heads=3, num_key_value_heads=1,
                         head_dim=64, rope_theta=10000.0, rms_norm_eps=1e-5, tie_word_embeddings=False,
                         max_position_embeddings=512, attention_bias=False)),
+    # sizes the tensor-core kernels refuse (a width of 100 breaks the 16-byte row rule of TMA, head size 48
+    # is no multiple of 32), q/k/v biases, as many key heads as query heads: the general kernels in bfloat16
+    "e": dict(seed=41, std=0.05, norm_std=0.1,
+              json=dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=333, hidden_size=100,
+                        intermediate_size=150, num_hidden_layers=2, num_attention_heads=5, num_key_value_heads=5,
+                        head_dim=48, rope_theta=50000.0, rms_norm_eps=1e-6, tie_word_embeddings=True,
+                        max_position_embeddings=300, attention_bias=True)),
 }
 GOLDEN_CONFIGS = ("a", "b")          # the ones the reference's CPU backend was run on
 
