@@ -36,12 +36,27 @@ class TraceReplayer:
         os.makedirs(out_dir, exist_ok=True)
 
     def run_step(self, record: dict) -> Optional[np.ndarray]:
+        """Runs one record.  A step with more tokens than the runner takes at once is run as several
+        batches, cut at the limit (the logits at a position do not depend on where a step is cut)."""
         r = self.runner
         step = record["step"]
-        entries = []
+        todo = []                                  # [id, tokens, {offset in tokens: [output rows]}]
+        seen = set()
+        n_out = 0
         for e in record.get("entries", []):
             rid = e["id"]
             toks = list(e["tokens"])
+            if rid in seen:
+                raise ReplayError(f"step {step}: request {rid!r} appears twice")
+            seen.add(rid)
+            want = {}
+            for w in e.get("want", []):
+                if not (0 <= int(w) < len(toks)):
+                    raise ReplayError(f"step {step}: request {rid!r} wants row {w} of {len(toks)} tokens")
+                want.setdefault(int(w), []).append(n_out)
+                n_out += 1
+            if not toks:
+                continue
             if not r.cache.has(rid):
                 if not r.admit(rid):
                     raise ReplayError(f"step {step}: no free request slot for {rid!r} "
@@ -50,14 +65,33 @@ class TraceReplayer:
                 raise ReplayError(
                     f"step {step}: the cache pool ({r.cache.capacity_tokens()} tokens) has no pages for "
                     f"{len(toks)} more tokens of {rid!r}; live requests hold {r.cache.used_pages()} pages")
-            entries.append(StepEntry(rid, toks, list(e.get("want", []))))
+            todo.append((rid, toks, want))
         out = None
-        if entries:
+        limit = r.max_batch_tokens
+        at, offset = 0, 0                          # next entry and how much of it has run
+        while at < len(todo):
+            entries, rows, room = [], [], limit
+            while at < len(todo) and room > 0:
+                rid, toks, want = todo[at]
+                n = min(room, len(toks) - offset)
+                here = sorted(w for w in want if offset <= w < offset + n)
+                for w in here:
+                    rows.append(want[w])
+                entries.append(StepEntry(rid, toks[offset:offset + n], [w - offset for w in here]))
+                room -= n
+                offset += n
+                if offset == len(toks):
+                    at, offset = at + 1, 0
             logits = r.step(entries)
             if logits is not None:
-                out = logits.detach().to("cpu").numpy().astype("<f4", copy=False)
-                out.tofile(os.path.join(self.out_dir, f"{step}.f32"))
+                got = logits.detach().to("cpu").numpy()
+                if out is None:
+                    out = np.empty((n_out, got.shape[1]), dtype="<f4")
+                for i, dest in enumerate(rows):
+                    out[dest] = got[i]             # a place wanted twice is written twice
             r.check_device()
+        if out is not None:
+            out.tofile(os.path.join(self.out_dir, f"{step}.f32"))
         for rid in record.get("end", []):
             if r.cache.has(rid):
                 r.release(rid)

@@ -102,3 +102,49 @@ def test_trace_run_program(dtype, tiny_model_dirs, plain_logits, tmp_path):
     outputs = {s["step"]: np.fromfile(out / f"{s['step']}.f32", dtype="<f4").reshape(-1, vocab) for s in steps}
     first, worst = first_mismatch(collect(steps, outputs), plain_logits(name, requests), TOL[dtype])
     assert first is None, f"{first}, worst {worst:.3e}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_replay_odd_records(dtype, tiny_model_dirs, plain_logits):
+    """Records at the edges of the format: a step larger than the runner's batch limit (run as several
+    batches), a place wanted twice and out of order, nothing wanted, an entry without tokens, a request
+    left out of a step, an unknown id in ``end``, an id used again after its end."""
+    from ember_b200.engine.replay import TraceReplayer
+    from ember_b200.engine.runner import ModelRunner
+    import tempfile
+    name = "b"
+    reqs = make_requests(name, (150, 90), seed=9)
+    a, b = reqs["r0"], reqs["r1"]
+    want = plain_logits(name, reqs)
+    runner = ModelRunner.from_dir(tiny_model_dirs[name], dtype=dtype, capacity_tokens=256, max_batch_tokens=48,
+                                  max_requests=4)
+    tol = TOL[dtype]
+
+    def close(got, ref):
+        assert np.abs(got - ref).max() <= tol * max(1.0, np.abs(ref).max())
+
+    with tempfile.TemporaryDirectory() as out:
+        rp = TraceReplayer(runner, out)
+        # 190 tokens in one step under a limit of 48; wants out of order, one twice, across the cuts
+        got = rp.run_step({"step": 0, "entries": [{"id": "x", "tokens": a[:120], "want": [119, 0, 47, 48, 119]},
+                                                  {"id": "y", "tokens": b[:70], "want": [69, 3]}], "end": ["nobody"]})
+        assert got.shape[0] == 7 and os.path.getsize(os.path.join(out, "0.f32")) == got.size * 4
+        for row, (rid, pos) in enumerate([("r0", 119), ("r0", 0), ("r0", 47), ("r0", 48), ("r0", 119), ("r1", 69),
+                                          ("r1", 3)]):
+            close(got[row], want[rid][pos])
+        # y is left out; x wants nothing; an entry without tokens is skipped
+        assert rp.run_step({"step": 1, "entries": [{"id": "x", "tokens": a[120:149], "want": []},
+                                                   {"id": "z", "tokens": [], "want": []}], "end": []}) is None
+        assert not os.path.exists(os.path.join(out, "1.f32"))
+        got = rp.run_step({"step": 2, "entries": [{"id": "y", "tokens": b[70:], "want": [19]},
+                                                  {"id": "x", "tokens": a[149:], "want": [0]}], "end": ["x", "y"]})
+        close(got[0], want["r1"][89])
+        close(got[1], want["r0"][149])
+        assert runner.cache.used_pages() == [0]
+        # the id comes again: a new request
+        got = rp.run_step({"step": 3, "entries": [{"id": "x", "tokens": b[:40], "want": [39]}], "end": ["x"]})
+        close(got[0], want["r1"][39])
+        from ember_b200.engine.replay import ReplayError
+        with pytest.raises(ReplayError):
+            rp.run_step({"step": 4, "entries": [{"id": "q", "tokens": [1, 2], "want": [2]}], "end": []})
+    assert runner.cache.check() == ""
