@@ -1,0 +1,92 @@
+"""Layers of the published Qwen3 sizes (0.6B, 1.7B, 8B widths; few layers, random weights) against the
+plain implementation: the shapes the benchmark times are the shapes whose logits are checked here."""
+import numpy as np
+import pytest
+import torch
+
+from ember_b200.config import Qwen3Config
+from ember_b200.weights import write_model_dir
+from tests.plain.qwen3_plain import PlainQwen3
+from tests.replay_helpers import collect, first_mismatch, max_live_tokens, trace_mixed, trace_tail_decode
+from tests.test_replay_gpu import TOL, replay
+
+pytestmark = pytest.mark.gpu
+
+
+def _json(**kw):
+    base = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", head_dim=128, rope_theta=1000000.0,
+                rms_norm_eps=1e-6, max_position_embeddings=4096, attention_bias=False)
+    base.update(kw)
+    return base
+
+
+SHAPES = {
+    "0.6b": _json(vocab_size=32064, hidden_size=1024, intermediate_size=3072, num_hidden_layers=2,
+                  num_attention_heads=16, num_key_value_heads=8, tie_word_embeddings=True),
+    "1.7b": _json(vocab_size=151936, hidden_size=2048, intermediate_size=6144, num_hidden_layers=2,
+                  num_attention_heads=16, num_key_value_heads=8, tie_word_embeddings=True),
+    "8b": _json(vocab_size=32064, hidden_size=4096, intermediate_size=12288, num_hidden_layers=1,
+                num_attention_heads=32, num_key_value_heads=8, tie_word_embeddings=False),
+}
+
+
+@pytest.fixture(scope="module")
+def shape_dirs(tmp_path_factory):
+    made = {}
+
+    def get(name):
+        if name not in made:
+            d = str(tmp_path_factory.mktemp(f"shape_{name.replace('.', '_')}"))
+            write_model_dir(Qwen3Config.from_json(SHAPES[name]), d, seed=7, dtype=torch.bfloat16, std=0.02, norm_std=0.05)
+            rng = np.random.default_rng(3)
+            reqs = {f"r{i}": rng.integers(0, SHAPES[name]["vocab_size"], size=n).tolist() for i, n in enumerate((97, 40, 66))}
+            plain = PlainQwen3(d, torch.float32)
+            made[name] = (d, reqs, {rid: plain.logits(t).numpy() for rid, t in reqs.items()})
+        return made[name]
+
+    return get
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("mode", ["tail", "mixed"])
+@pytest.mark.parametrize("name", sorted(SHAPES))
+def test_published_layer_sizes(name, mode, dtype, shape_dirs):
+    model_dir, requests, want = shape_dirs(name)
+    steps = trace_tail_decode(requests) if mode == "tail" else trace_mixed(requests, live=3, seed=2)
+    outputs = replay(model_dir, dtype, steps, max_live_tokens(steps))
+    got = collect(steps, outputs)
+    for rid, toks in requests.items():
+        assert sorted(got[rid]) == list(range(len(toks)))
+    first, worst = first_mismatch(got, want, TOL[dtype])
+    print(f"{name} {dtype} {mode}: worst relative error {worst:.3e}")
+    assert first is None, f"first wrong position (request, position, error): {first}; worst {worst:.3e}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_prompt_at_the_benchmark_shape(dtype, shape_dirs):
+    """2,100 tokens in one step (many attention tiles, split keys afterwards), then single tokens: the last
+    prompt position and every decoded position against the plain implementation."""
+    from tests.plain.qwen3_plain import linear, rmsnorm
+    model_dir, _, _ = shape_dirs("1.7b")
+    rng = np.random.default_rng(11)
+    toks = rng.integers(0, SHAPES["1.7b"]["vocab_size"], size=2108).tolist()
+    head = 2100
+    plain = PlainQwen3(model_dir, torch.float32)
+    rows = list(range(head - 1, len(toks)))
+    h = plain.hidden_states(toks)[-1][rows]
+    ref = linear(rmsnorm(h, plain.w["model.norm.weight"], plain.cfg["eps"]), plain.w["model.embed_tokens.weight"]).numpy()
+    steps = [{"step": 0, "entries": [{"id": "a", "tokens": toks[:head], "want": [head - 1]}], "end": []}]
+    for i, t in enumerate(range(head, len(toks))):
+        steps.append({"step": i + 1, "entries": [{"id": "a", "tokens": [toks[t]], "want": [0]}],
+                      "end": ["a"] if t == len(toks) - 1 else []})
+    from ember_b200.engine.replay import TraceReplayer
+    from ember_b200.engine.runner import ModelRunner
+    import tempfile
+    runner = ModelRunner.from_dir(model_dir, dtype=dtype, capacity_tokens=2176, max_batch_tokens=2176, max_requests=2)
+    with tempfile.TemporaryDirectory() as out:
+        rp = TraceReplayer(runner, out)
+        got = np.concatenate([rp.run_step(s) for s in steps])
+    from tests.replay_helpers import rel_err
+    errs = [rel_err(got[i], ref[i]) for i in range(len(rows))]
+    print(f"long prompt {dtype}: worst relative error {max(errs):.3e}")
+    assert max(errs) <= TOL[dtype], errs
