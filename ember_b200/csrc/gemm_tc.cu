@@ -25,6 +25,7 @@
 #include <tuple>
 
 #include "gemm_tc_kernel.cuh"
+#include "gemm_tc_pair.cuh"
 
 EMBER_DEFINE_LAST_ERROR
 
@@ -57,6 +58,85 @@ static bool tensor_map(const void* ptr, int rows, int K, int box_rows, CUtensorM
     cache[key] = m;
     *out = m;
     return true;
+}
+
+// How many pairs of blocks of the pair kernel the device runs at once (0: it cannot).
+static int pair_capacity(int num_sms) {
+    static int max_pairs = -1;
+    if (max_pairs < 0) {
+        int n = 0;
+        if (cudaFuncSetAttribute(gemm_tc_pair_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024) == cudaSuccess) {
+            cudaLaunchConfig_t q = {};
+            q.gridDim = dim3(2 * (num_sms / 2));
+            q.blockDim = dim3(GEMM_THREADS);
+            q.dynamicSmemBytes = 227 * 1024 - 2048;
+            cudaLaunchAttribute a[1];
+            a[0].id = cudaLaunchAttributeClusterDimension;
+            a[0].val.clusterDim.x = 2; a[0].val.clusterDim.y = 1; a[0].val.clusterDim.z = 1;
+            q.attrs = a; q.numAttrs = 1;
+            if (cudaOccupancyMaxActiveClusters(&n, gemm_tc_pair_kernel, &q) != cudaSuccess) { cudaGetLastError(); n = 0; }
+        } else {
+            cudaGetLastError();
+        }
+        max_pairs = n < num_sms / 2 ? n : num_sms / 2;
+    }
+    return max_pairs;
+}
+
+// Tile width for a prefill-sized product.  The time is about (waves of tiles over the SMs) x (tile width + a
+// fixed cost per tile), so a narrower tile wins when it fills the last wave or brings idle SMs in: N = 2048 on
+// 148 SMs with 16 row tiles runs 144 tiles of 240 columns in one wave, faster than 128 tiles of 256.  Tiles
+// narrower than 192 columns re-read the token rows too often to pay.
+static int best_block_cols(int M, int N, int slots, int units, double* cost_out) {
+    const int rows = TILE_ROWS * units, step = 16 * units;
+    const int row_tiles = (M + rows - 1) / rows;
+    int best = 256;
+    double best_cost = 1e30;
+    for (int bc = 256; bc >= 192; bc -= step) {
+        const long long tiles = (long long)row_tiles * ((N + bc - 1) / bc);
+        const double cost = (double)((tiles + slots - 1) / slots) * (bc + 40);
+        if (cost < best_cost * 0.999) { best_cost = cost; best = bc; }
+    }
+    if (N <= 128) { best = 128; best_cost = (double)((row_tiles + slots - 1) / slots) * (128 + 40); }
+    if (const char* f = getenv("EMBER_GEMM_TILE_COLS")) {       // tuning aid: force the width (a multiple of 32)
+        const int v = atoi(f);
+        if (v >= 32 && v <= 256 && v % 32 == 0) best = v;
+    }
+    if (cost_out) *cost_out = best_cost;
+    return best;
+}
+
+// The pair kernel: 256-token tiles on clusters of two blocks, as many pairs as the device co-schedules.
+static int launch_pair(const void* A, const void* W, GemmTcParams p, int block_cols, int max_pairs, cudaStream_t st) {
+    p.block_cols = block_cols;
+    p.row_tiles = (p.M + 2 * TILE_ROWS - 1) / (2 * TILE_ROWS);
+    p.total_tiles = p.row_tiles * ((p.N + block_cols - 1) / block_cols);
+    p.tmem_cols = 512;
+    p.cluster_splits = 1;
+    p.k_blocks_per_split = p.num_k_blocks;
+    const int stage_bytes = pair_stage_bytes(block_cols);
+    int stages = (200 * 1024) / stage_bytes;
+    if (stages > MAX_STAGES) stages = MAX_STAGES;
+    if (stages > p.num_k_blocks) stages = p.num_k_blocks < 2 ? 2 : p.num_k_blocks;
+    p.stages = stages;
+    const size_t smem = (size_t)stages * stage_bytes + 1024 + 256;
+    CUtensorMap map_rows, map_cols;
+    if (!tensor_map(A, p.M, p.K, TILE_ROWS, &map_rows) || !tensor_map(W, p.N, p.K, block_cols / 2, &map_cols))
+        return fail("gemm_tc: cuTensorMapEncodeTiled failed or is unavailable");
+    const int pairs = p.total_tiles < max_pairs ? p.total_tiles : max_pairs;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * pairs);
+    cfg.blockDim = dim3(GEMM_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attrs[2];
+    attrs[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+    attrs[1].id = cudaLaunchAttributeClusterDimension;
+    attrs[1].val.clusterDim.x = 2; attrs[1].val.clusterDim.y = 1; attrs[1].val.clusterDim.z = 1;
+    cfg.attrs = attrs; cfg.numAttrs = 2;
+    cudaLaunchKernelEx(&cfg, gemm_tc_pair_kernel, map_rows, map_cols, p);
+    return check_launch("gemm_tc_pair");
 }
 
 }  // namespace ember
@@ -97,7 +177,24 @@ EMBER_API int ember_gemm_tc(const void* A, const void* W, void* out, int ldc, in
         row_tiles = (N + TILE_ROWS - 1) / TILE_ROWS;
         col_tiles = 1;
     } else {
-        p.block_cols = N >= 1024 ? 256 : 128;
+        // Prefill-sized products: the single-SM persistent kernel or pairs of SMs (tcgen05 cta_group::2),
+        // each with the tile width that fills its waves best.  Under the power cap pairs are the more efficient
+        // kernel (an SM reads half of the weight tile) and win from about 4,096 tokens on.
+        // split_mode 4 asks for pairs whenever the device takes them, 5 forbids them, 3 runs one tile per block.
+        double cost_single = 0, cost_pair = 0;
+        const int bc_single = split_mode == 3 ? (N >= 1024 ? 256 : 128) : best_block_cols(M, N, num_sms, 1, &cost_single);
+        if (split_mode != 3 && split_mode != 5 && N >= 32) {
+            const int max_pairs = pair_capacity(num_sms);
+            if (max_pairs > 0) {
+                const int bc_pair = best_block_cols(M, N, max_pairs, 2, &cost_pair);
+                if (split_mode == 4 || (M >= 4096 && cost_pair <= cost_single * 1.001)) {
+                    p.epilogue = epilogue; p.out = out; p.ldc = ldc; p.err = err;
+                    p.accum = nullptr; p.accum_ld = 0; p.rows_per = TILE_ROWS; p.stages = 0;
+                    return launch_pair(A, W, p, bc_pair, max_pairs, st);
+                }
+            }
+        }
+        p.block_cols = bc_single;
         row_tiles = (M + TILE_ROWS - 1) / TILE_ROWS;
         col_tiles = (N + p.block_cols - 1) / p.block_cols;
     }

@@ -144,12 +144,14 @@ __device__ __forceinline__ void store_chunk_normal(const GemmTcParams& p, int m,
         if (nv == 16 && (((uintptr_t)dst) & 15) == 0) {
 #pragma unroll
             for (int j = 0; j < 4; j++) {
-                float4 o = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
                 if (p.epilogue == 2) {
-                    const float4 c = ((float4*)dst)[j];
-                    o.x += c.x; o.y += c.y; o.z += c.z; o.w += c.w;
+                    // the sum is formed at the L2 (one reduction per element, so the result is the same as a
+                    // load, add and store); nothing comes back, so the epilogue never waits on memory
+                    asm volatile("red.global.add.v4.f32 [%0], {%1, %2, %3, %4};" ::"l"(dst + 4 * j), "f"(v[4 * j]),
+                                 "f"(v[4 * j + 1]), "f"(v[4 * j + 2]), "f"(v[4 * j + 3]) : "memory");
+                } else {
+                    ((float4*)dst)[j] = make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
                 }
-                ((float4*)dst)[j] = o;
             }
         } else {
             for (int j = 0; j < nv; j++) dst[j] = p.epilogue == 2 ? dst[j] + v[j] : v[j];
@@ -235,14 +237,16 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_consta
             pdl_wait();
             for (int i = 0; i < ahead; i++)
                 tma_load_2d(smem + (size_t)i * stage_bytes + x_off, map_x, &full_bar[i], (kb0 + i) * TILE_K, x_y);
+            // the ring position advances by counting (a division per k-block would sit on the critical path)
+            int s = 0;
+            uint32_t phase = 1;                      // ahead == stages here, so the ring has wrapped once
             for (int i = ahead; i < n_kb; i++) {
-                const int s = i % p.stages;
-                const uint32_t phase = (uint32_t)(i / p.stages) & 1u;
                 if (!mbar_wait(&empty_bar[s], phase ^ 1u, abort_flag)) break;
                 uint8_t* st = smem + (size_t)s * stage_bytes;
                 mbar_expect_tx(&full_bar[s], (uint32_t)(rows_bytes + cols_bytes));
                 tma_load_2d(st + w_off, map_w, &full_bar[s], (kb0 + i) * TILE_K, w_y);
                 tma_load_2d(st + x_off, map_x, &full_bar[s], (kb0 + i) * TILE_K, x_y);
+                if (++s == p.stages) { s = 0; phase ^= 1u; }
             }
         }
     } else if (warp == 1) {
@@ -250,9 +254,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_consta
         if (lane == 0 && n_kb > 0) {
             const uint32_t idesc = umma_idesc(p.block_cols);
             bool ok = true;
+            int s = 0;
+            uint32_t phase = 0;
             for (int i = 0; i < n_kb && ok; i++) {
-                const int s = i % p.stages;
-                const uint32_t phase = (uint32_t)(i / p.stages) & 1u;
                 ok = mbar_wait(&full_bar[s], phase, abort_flag);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -264,6 +268,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_consta
                     tcgen05_mma_bf16(tmem_d, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, (i > 0 || k > 0) ? 1u : 0u);
                 }
                 tcgen05_commit(&empty_bar[s]);      // the stage is free once these MMAs have read it
+                if (++s == p.stages) { s = 0; phase ^= 1u; }
             }
             tcgen05_commit(tmem_full_bar);          // the accumulator is complete once all MMAs have finished
         }
@@ -442,43 +447,49 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_rows, const __
 
     if (warp == 0) {
         if (lane == 0) {
-            int it = 0;
-            bool ok = true;
+            int s = 0;
+            uint32_t phase = 0;                      // parity of the ring's current lap
+            bool ok = true, wrapped = false;
+            uint8_t* st = smem;
             for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
                 const int col_tile = t / p.row_tiles, row_tile = t - col_tile * p.row_tiles;
-                for (int i = 0; i < n_kb; i++, it++) {
-                    const int s = it % p.stages;
-                    if (it >= p.stages) ok = mbar_wait(&empty_bar[s], ((uint32_t)(it / p.stages) & 1u) ^ 1u, abort_flag);
+                for (int i = 0; i < n_kb; i++) {
+                    if (wrapped) ok = mbar_wait(&empty_bar[s], phase ^ 1u, abort_flag);
                     if (!ok) break;
-                    uint8_t* st = smem + (size_t)s * stage_bytes;
                     mbar_expect_tx(&full_bar[s], (uint32_t)(rows_bytes + cols_bytes));
                     tma_load_2d(st, &map_rows, &full_bar[s], i * TILE_K, row_tile * TILE_ROWS);
                     tma_load_2d(st + rows_bytes, &map_cols, &full_bar[s], i * TILE_K, col_tile * p.block_cols);
+                    st += stage_bytes;
+                    if (++s == p.stages) { s = 0; st = smem; phase ^= 1u; wrapped = true; }
                 }
             }
         }
     } else if (warp == 1) {
         if (lane == 0) {
             const uint32_t idesc = umma_idesc(p.block_cols);
-            int it = 0, li = 0;
+            int li = 0, s = 0;
+            uint32_t phase = 0;
             bool ok = true;
+            // descriptors advance with the ring: one stage is stage_bytes / 16 in the 16-byte address field
+            const uint64_t da0 = umma_desc_sw128(smem), db0 = umma_desc_sw128(smem + rows_bytes);
+            const uint64_t dstep = (uint64_t)(stage_bytes >> 4);
+            uint64_t da = da0, db = db0;
             for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x, li++) {
                 const int acc = li & 1;
                 if (li >= 2) ok = mbar_wait(&tmem_empty_bar[acc], ((uint32_t)(li >> 1) & 1u) ^ 1u, abort_flag);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t d = tmem_d + (uint32_t)(acc * p.block_cols);
-                for (int i = 0; i < n_kb; i++, it++) {
-                    const int s = it % p.stages;
-                    ok = mbar_wait(&full_bar[s], (uint32_t)(it / p.stages) & 1u, abort_flag);
+                for (int i = 0; i < n_kb; i++) {
+                    ok = mbar_wait(&full_bar[s], phase, abort_flag);
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    uint8_t* a = smem + (size_t)s * stage_bytes;
-                    const uint64_t da = umma_desc_sw128(a), db = umma_desc_sw128(a + rows_bytes);
 #pragma unroll
                     for (int k = 0; k < TILE_K / UMMA_K; k++)
                         tcgen05_mma_bf16(d, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, (i > 0 || k > 0) ? 1u : 0u);
                     tcgen05_commit(&empty_bar[s]);
+                    da += dstep; db += dstep;
+                    if (++s == p.stages) { s = 0; phase ^= 1u; da = da0; db = db0; }
                 }
                 if (ok) tcgen05_commit(&tmem_full_bar[acc]);
             }

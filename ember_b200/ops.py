@@ -282,7 +282,8 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, M: int, epilogu
             err: Optional[torch.Tensor] = None, stream: Optional[int] = None, split_mode: int = 0) -> None:
     """out (+)= a[:M] @ w.T on the tcgen05 tensor cores (bf16 in, fp32 accumulate).
     ``split_mode``: how split-K partial sums are combined (0 automatic, 1 atomics, 2 cluster); 3 runs
-    prefill-sized products one tile per block instead of persistently (for tests)."""
+    prefill-sized products one tile per block instead of persistently, 4 on pairs of SMs whenever the device
+    takes them, 5 never on pairs (for tests and tuning)."""
     _check(a, "a", torch.bfloat16)
     _check(w, "w", torch.bfloat16)
     _check(out, "out")
