@@ -12,14 +12,17 @@ EMBER_DEFINE_LAST_ERROR
 namespace ember {
 
 // ------------------------------------------------------------------------------ embedding
-// h[t, :] = float(table[tokens[t], :]); no scaling.
+// h[t, :] = float(table[tokens[t], :]); no scaling.  A negative token -(r + 1) stands for the id that the
+// sampler left in prev_ids[r]: a step can be launched before the host has read the step before it.
 template <typename TW>
-__global__ void embed_kernel(const int* __restrict__ tokens, const TW* __restrict__ table,
-                             float* __restrict__ out, int H, int V, int* __restrict__ err) {
+__global__ void embed_kernel(const int* __restrict__ tokens, const int* __restrict__ prev_ids, int n_prev,
+                             const TW* __restrict__ table, float* __restrict__ out, int H, int V,
+                             int* __restrict__ err) {
     pdl_launch_dependents();
     pdl_wait();
     const int t = blockIdx.x;
-    const int tok = tokens[t];
+    int tok = tokens[t];
+    if (tok < 0 && prev_ids != nullptr && -tok <= n_prev) tok = prev_ids[-tok - 1];
     float* o = out + (size_t)t * H;
     if (tok < 0 || tok >= V) {
         if (threadIdx.x == 0 && err) atomicOr(err, EMBER_ERR_TOKEN_RANGE);
@@ -213,16 +216,17 @@ __global__ void silu_mul_interleaved_kernel(const T* __restrict__ x, T* __restri
 
 using namespace ember;
 
-EMBER_API int ember_embed(const int* tokens, const void* table, int table_dtype, float* out, int T, int H, int V,
-                          int* err, void* stream) {
+EMBER_API int ember_embed(const int* tokens, const int* prev_ids, int n_prev, const void* table, int table_dtype,
+                          float* out, int T, int H, int V, int* err, void* stream) {
     if (T <= 0) return 0;
     if (H <= 0 || V <= 0) return fail("embed: bad sizes H=%d V=%d", H, V);
     cudaStream_t st = (cudaStream_t)stream;
     const int threads = H >= 1024 ? 256 : 128;
     if (table_dtype == EMBER_F32)
-        launch_kernel(embed_kernel<float>, T, threads, 0, st, tokens, (const float*)table, out, H, V, err);
+        launch_kernel(embed_kernel<float>, T, threads, 0, st, tokens, prev_ids, n_prev, (const float*)table, out, H, V, err);
     else if (table_dtype == EMBER_BF16)
-        launch_kernel(embed_kernel<__nv_bfloat16>, T, threads, 0, st, tokens, (const __nv_bfloat16*)table, out, H, V, err);
+        launch_kernel(embed_kernel<__nv_bfloat16>, T, threads, 0, st, tokens, prev_ids, n_prev, (const __nv_bfloat16*)table, out, H, V,
+                      err);
     else
         return fail("embed: unsupported table dtype %d", table_dtype);
     return check_launch("embed");

@@ -207,7 +207,7 @@ class StepContext:
 
     def __init__(self, batch, workspace: Workspace, device: torch.device, max_tokens: int,
                  err: Optional[torch.Tensor] = None, tile_sizes: Sequence[Tuple[int, str]] = (),
-                 max_context: Optional[int] = None, upload: bool = True):
+                 max_context: Optional[int] = None, upload: bool = True, prev_ids: Optional[torch.Tensor] = None):
         """``batch`` is a ``StepBatch`` (packed here, with numpy) or a ``runtime.PackedStep`` (packed
         already, by the native packer, with the tile lists it was asked for)."""
         self.batch = batch
@@ -218,6 +218,7 @@ class StepContext:
         if self.T > max_tokens:
             raise BatchError(f"the step has {self.T} tokens; the limit is {max_tokens}")
         self.err = err
+        self.prev_ids = prev_ids         # where the sampler left the step before's ids (tokens < 0 point there)
         self.stream = torch.cuda.current_stream(device).cuda_stream
         # host views parts may read (toy mixers, planners)
         self.query_start_host = batch.query_start

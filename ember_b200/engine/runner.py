@@ -62,6 +62,9 @@ class ModelRunner:
         self.workspace = Workspace(self.device)
         self._packer = StepPacker()
         self.err = torch.zeros(1, dtype=torch.int32, device=self.device)
+        # where a sampler may leave a step's ids for the next step to read on the device (a token
+        # -(r + 1) of a step names row r of this buffer); the address is fixed, graphs capture it
+        self.sampled_ids = torch.zeros(max(self.max_requests, 1), dtype=torch.int32, device=self.device)
         self.steps = 0
         # decode steps (one token per run) are captured into CUDA graphs, one per (runs, wanted rows,
         # context bucket); the reference does the same for its decode steps (src/backend/cuda/cuda_backend.cu:376-454)
@@ -98,9 +101,10 @@ class ModelRunner:
         return self.cache.get(request).tokens
 
     # ---------------------------------------------------------------------- step
-    def step(self, entries: Sequence[StepEntry]) -> Optional[torch.Tensor]:
+    def step(self, entries: Sequence[StepEntry], n_prev: int = 0) -> Optional[torch.Tensor]:
         """Runs the entries as one batch; returns logits [wanted rows, vocab] fp32 on the device
-        (a view of a scratch buffer, valid until the next step), or None if nothing is wanted."""
+        (a view of a scratch buffer, valid until the next step), or None if nothing is wanted.
+        With ``n_prev`` > 0 a token -(r + 1), r < n_prev, is read on the device from ``sampled_ids[r]``."""
         graphable = self.cuda_graphs and 0 < len(entries) <= self.graph_max_runs and \
             all(len(e.tokens) == 1 for e in entries)
         min_widths, ctx_bucket = None, None
@@ -119,7 +123,8 @@ class ModelRunner:
             return host.numpy(), host.data_ptr()
 
         packed = self._packer.pack(entries, self.cache, self.spec.vocab_size, self.spec.max_positions,
-                           tile_keys=self.model.tile_requests(), min_widths=min_widths, alloc=alloc)
+                           tile_keys=self.model.tile_requests(), min_widths=min_widths, alloc=alloc,
+                                   n_prev=min(int(n_prev), self.sampled_ids.numel()))
         packed.staging = staging[0]
         return self.run_batch(packed, ctx_bucket)
 
@@ -131,7 +136,7 @@ class ModelRunner:
             logits = self._run_decode_graph(batch, graph_bucket)
         else:
             ctx = StepContext(batch, self.workspace, self.device, self.max_batch_tokens, err=self.err,
-                              tile_sizes=self.model.tile_requests())
+                              tile_sizes=self.model.tile_requests(), prev_ids=self.sampled_ids)
             logits = self.model.forward(ctx, self.storage)
         lens = batch.context_len.tolist()
         for s, req in enumerate(batch.requests):
@@ -145,7 +150,7 @@ class ModelRunner:
         and replay."""
         key = (packed.S, packed.R, ctx_bucket, tuple(packed.widths))
         ctx = StepContext(packed, self.workspace, self.device, self.max_batch_tokens, err=self.err,
-                          max_context=ctx_bucket)          # uploads this step's integers
+                          max_context=ctx_bucket, prev_ids=self.sampled_ids)          # uploads this step's integers
         entry = self._graphs.get(key)
         if entry is not None and entry[1] == self.workspace.version and entry[3] == ctx.ints.data_ptr():
             entry[0].replay()
@@ -160,7 +165,7 @@ class ModelRunner:
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
             cap = StepContext(packed, self.workspace, self.device, self.max_batch_tokens, err=self.err,
-                              max_context=ctx_bucket, upload=False)
+                              max_context=ctx_bucket, upload=False, prev_ids=self.sampled_ids)
             logits = self.model.forward(cap, self.storage)
         if self.workspace.version != version or cap.ints.data_ptr() != ctx.ints.data_ptr():
             # a buffer was (re)allocated while capturing: the graph holds stale pointers; run eagerly

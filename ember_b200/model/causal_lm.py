@@ -80,7 +80,7 @@ class CausalLM:
     def forward(self, ctx, storage) -> Optional[torch.Tensor]:
         s, rt = self.spec, self.rt
         h = ctx.buf("model.residual", (ctx.max_tokens, s.hidden_size), torch.float32)
-        ops.embed(ctx.tokens, self.embedding, h, err=ctx.err, stream=ctx.stream)
+        ops.embed(ctx.tokens, self.embedding, h, err=ctx.err, stream=ctx.stream, prev_ids=ctx.prev_ids)
         for e in s.schedule:
             owner = e.cache_of if e.cache_of >= 0 else e.layer
             self.blocks[e.layer].forward(ctx, h, storage.layer(owner), owns_cache=(owner == e.layer))

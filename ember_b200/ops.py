@@ -85,17 +85,21 @@ def _call(lib, fn, *args):
 
 # ------------------------------------------------------------------------------ elementwise
 def embed(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor, err: Optional[torch.Tensor] = None,
-          stream: Optional[int] = None) -> None:
-    """out[t, :] = float(table[tokens[t], :])."""
+          stream: Optional[int] = None, prev_ids: Optional[torch.Tensor] = None) -> None:
+    """out[t, :] = float(table[tokens[t], :]).  With ``prev_ids`` (int32, device) a token -(r + 1) is
+    read as prev_ids[r]: the id the sampler wrote there in the step before."""
     _check(tokens, "tokens", torch.int32)
+    if prev_ids is not None:
+        _check(prev_ids, "prev_ids", torch.int32)
     _check(table, "table")
     _check(out, "out", torch.float32)
     T, (V, H) = tokens.numel(), table.shape
     if out.shape[-1] != H or out.numel() < T * H:
         raise KernelError(f"embed: output {tuple(out.shape)} does not fit {T} rows of width {H}")
     lib = _lib("elementwise")
-    _call(lib, lib.ember_embed, _p(tokens), _p(table), c_int(dtype_code(table.dtype)), _p(out), c_int(T), c_int(H),
-          c_int(V), _p(err), c_void_p(stream if stream is not None else current_stream_ptr()))
+    _call(lib, lib.ember_embed, _p(tokens), _p(prev_ids), c_int(prev_ids.numel() if prev_ids is not None else 0),
+          _p(table), c_int(dtype_code(table.dtype)), _p(out), c_int(T), c_int(H), c_int(V), _p(err),
+          c_void_p(stream if stream is not None else current_stream_ptr()))
 
 
 def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor, n_rows: int,

@@ -69,7 +69,7 @@ def library() -> ctypes.CDLL:
         lib = ctypes.CDLL(so)
         vp = c_void_p                 # addresses are passed as plain integers
         lib.ember_step_layout.restype = c_int
-        lib.ember_step_layout.argtypes = [c_int, vp, vp, vp, vp, vp, c_int, vp, c_int, vp, vp, c_int,
+        lib.ember_step_layout.argtypes = [c_int, vp, vp, vp, vp, vp, c_int, vp, c_int, vp, vp, c_int, c_int,
                                           POINTER(StepLayout)]
         lib.ember_step_pack.restype = None
         lib.ember_step_pack.argtypes = [c_int, vp, vp, vp, vp, vp, vp, c_int, vp, vp, vp,
@@ -160,11 +160,12 @@ class StepPacker:
 
     def pack(self, entries, cache, vocab_size: int, max_positions: Optional[int] = None,
              tile_keys: Sequence[Tuple[int, str]] = (), widths: Optional[Sequence[int]] = None,
-             min_widths: Optional[Sequence[int]] = None, alloc=None) -> PackedStep:
+             min_widths: Optional[Sequence[int]] = None, alloc=None, n_prev: int = 0) -> PackedStep:
         """Checks the entries, reads cached lengths, slots and block tables from ``cache`` (pages for the
         new tokens must already be ensured) and packs the step.  ``widths`` sets the block tables' widths,
         ``min_widths`` only pads them (graph buckets); ``alloc(n)`` returns (int32 array to fill, its
-        address) — pinned staging memory — else a new array is made."""
+        address) — pinned staging memory — else a new array is made.  With ``n_prev`` > 0 a token
+        -(r + 1), r < n_prev, is allowed: the id sampled in row r of the step before."""
         from ..engine.batch import BatchError
         lib = self._lib
         S = len(entries)
@@ -229,7 +230,7 @@ class StepPacker:
         lay = StepLayout()
         lay_ref = ctypes.byref(lay)
         code = lib.ember_step_layout(S, o_counts, o_starts, o_wc, o_tok, o_want, G, o_widths, L, o_tq, o_tk,
-                                     int(vocab_size), lay_ref)
+                                     int(vocab_size), int(n_prev), lay_ref)
         if code != 0:
             raise BatchError(_ERRORS.get(code, f"the step could not be laid out (code {code})") +
                              f" (vocabulary {vocab_size})")
@@ -252,9 +253,9 @@ _default_packer = None
 
 def pack_step(entries, cache, vocab_size: int, max_positions: Optional[int] = None,
               tile_keys: Sequence[Tuple[int, str]] = (), widths: Optional[Sequence[int]] = None,
-              min_widths: Optional[Sequence[int]] = None, alloc=None) -> PackedStep:
+              min_widths: Optional[Sequence[int]] = None, alloc=None, n_prev: int = 0) -> PackedStep:
     """``StepPacker.pack`` with a packer shared by the process (not for concurrent use)."""
     global _default_packer
     if _default_packer is None:
         _default_packer = StepPacker()
-    return _default_packer.pack(entries, cache, vocab_size, max_positions, tile_keys, widths, min_widths, alloc)
+    return _default_packer.pack(entries, cache, vocab_size, max_positions, tile_keys, widths, min_widths, alloc, n_prev)

@@ -29,9 +29,11 @@ static inline int32_t round8(int32_t n) { return (n + 7) / 8 * 8; }
 // Sizes the layout.  tile_q[i] / tile_kind[i] (0 all runs, 1 runs of two or more tokens, 2 single tokens)
 // describe the tile lists wanted.  Returns 0, or a negative code: -1 empty step, -2 a run without tokens,
 // -3 a wanted row outside its run, -4 a token id outside the vocabulary, -5 too many groups or lists.
+// A token -(r + 1) with r < n_prev names the id sampled in row r of the step before (still on the device).
 int ember_step_layout(int n_runs, const int32_t* counts, const int32_t* starts, const int32_t* want_counts,
                       const int32_t* tokens, const int32_t* want, int n_groups, const int32_t* table_widths,
-                      int n_lists, const int32_t* tile_q, const int32_t* tile_kind, int vocab, EmberStepLayout* out) {
+                      int n_lists, const int32_t* tile_q, const int32_t* tile_kind, int vocab, int n_prev,
+                      EmberStepLayout* out) {
     if (n_runs <= 0) return -1;
     if (n_groups > 8 || n_lists > 8) return -5;
     int32_t T = 0, R = 0, max_ctx = 0;
@@ -40,7 +42,7 @@ int ember_step_layout(int n_runs, const int32_t* counts, const int32_t* starts, 
         for (int i = 0; i < want_counts[s]; i++)
             if (want[R + i] < 0 || want[R + i] >= counts[s]) return -3;
         for (int i = 0; i < counts[s]; i++)
-            if (tokens[T + i] < 0 || tokens[T + i] >= vocab) return -4;
+            if (tokens[T + i] < -n_prev || tokens[T + i] >= vocab) return -4;
         T += counts[s];
         R += want_counts[s];
         if (starts[s] + counts[s] > max_ctx) max_ctx = starts[s] + counts[s];

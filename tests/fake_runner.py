@@ -41,11 +41,23 @@ class FakeRunner:
         self.window = window
         self.steps = 0
         self.fail_next = False
+        self.sampled_ids: List[int] = []
+        self.speculated_steps = 0
 
-    def step(self, entries) -> Optional[torch.Tensor]:
+    def set_sampled_ids(self, ids: List[int]) -> None:
+        """What the sampler drew in the step before (the real runner keeps them on the device)."""
+        self.sampled_ids = list(ids)
+
+    def step(self, entries, n_prev: int = 0) -> Optional[torch.Tensor]:
         if self.fail_next:
             self.fail_next = False
             raise RuntimeError("injected step failure")
+        if n_prev:
+            from ember_b200.engine.batch import StepEntry
+            self.speculated_steps += 1
+            assert n_prev == len(self.sampled_ids)
+            entries = [StepEntry(e.request, [self.sampled_ids[-t - 1] if t < 0 else t for t in e.tokens], e.want)
+                       for e in entries]
         b = build_batch(entries, self.cache, self.spec.vocab_size, self.spec.max_positions)
         assert b.T <= self.max_batch_tokens
         page = self.cache.page_tokens

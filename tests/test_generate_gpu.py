@@ -140,3 +140,29 @@ def test_graph_replay_equals_eager_decoding(dtype, tiny_model_dirs):
     assert n0 == 0 and n1 > 30
     for a, b in zip(eager, graphed):
         assert np.array_equal(a, b) if dtype == "float32" else np.allclose(a, b, rtol=0, atol=1e-2 * np.abs(a).max())
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_pipelined_engine_equals_synchronous_engine(dtype, tiny_model_dirs):
+    """Steps launched before the ids of the step in flight are read (tokens resolved on the device from the
+    sampler's buffer) give the tokens of the synchronous engine: greedy and seeded sampling, a stop token seen
+    one step late, requests of different lengths joining and leaving."""
+    from ember_b200 import SamplingParams
+    from ember_b200.engine.engine import Engine
+    llm = load(tiny_model_dirs, "b", dtype, kv_cache_tokens=2048)
+    rng = np.random.default_rng(21)
+    prompts = [rng.integers(0, 1000, size=n).tolist() for n in (3, 40, 17, 64, 9)]
+    for sp in (SamplingParams(temperature=0.0), SamplingParams(temperature=0.9, top_k=40, top_p=0.9, seed=77)):
+        results = {}
+        for pipeline in (False, True):
+            eng = Engine(llm.runner, max_prefill_chunk=32, pipeline=pipeline)
+            assert eng.pipeline == pipeline
+            free = eng.generate(prompts, sampling=sp, max_tokens=40, ignore_eos=True)
+            stop = free[1][7]                       # a token the second request meets early
+            stopped = eng.generate(prompts, sampling=sp, max_tokens=40, stop_tokens=(stop,))
+            results[pipeline] = (free, stopped)
+            assert llm.runner.cache.used_pages() == [0]
+            for f, s in zip(free, stopped):
+                assert s == (f[:f.index(stop)] if stop in f else f)
+        assert results[True] == results[False]
+    llm.runner.check_device()

@@ -11,10 +11,12 @@ from tests.fake_runner import FakeRunner, argmax_sampler, expected_generation
 GREEDY = SamplingParams(temperature=0.0)
 
 
-def make(capacity, **kw):
+def make(capacity, pipeline=False, **kw):
+    """``pipeline=False``: every step is committed before ``step`` returns, so a test can look at the
+    scheduler between steps; the pipelined engine has tests of its own below."""
     opts = {k: kw.pop(k) for k in ("max_batch_tokens", "max_seqs", "max_prefill_chunk", "max_context") if k in kw}
     runner = FakeRunner(capacity, **kw)
-    return runner, Engine(runner, sampler=argmax_sampler, **opts)
+    return runner, Engine(runner, sampler=argmax_sampler, pipeline=pipeline, **opts)
 
 
 def run_all(eng, runner, seqs, limit=100000):
@@ -142,3 +144,61 @@ def test_seed_zero_gets_a_seed_and_greedy_is_left_alone():
     assert s.request.sampling.seed != 0
     g = eng.submit(Request(prompt=[1], sampling=GREEDY, max_tokens=1))
     assert g.request.sampling.seed == 0
+
+
+# ------------------------------------------------------------------ the one-step pipeline
+def test_pipelined_engine_generates_the_same_tokens():
+    """Steps launched before the ids in flight are read (token references resolved by the model) give the
+    tokens of the synchronous engine: many requests, portions, preemption for lack of pages."""
+    rng = random.Random(3)
+    prompts = [[rng.randrange(1, 900) for _ in range(rng.randint(1, 90))] for _ in range(24)]
+    lens = [rng.randint(1, 40) for _ in prompts]
+    outs = {}
+    for pipeline in (False, True):
+        runner, eng = make(640, pipeline=pipeline, max_batch_tokens=96, max_prefill_chunk=40, max_seqs=6)
+        seqs = [eng.submit(Request(prompt=p, sampling=GREEDY, max_tokens=n, ignore_eos=True)) for p, n in zip(prompts, lens)]
+        run_all(eng, runner, seqs)
+        eng.drain()
+        outs[pipeline] = [list(s.output) for s in seqs]
+        assert runner.cache.check() == "" and runner.cache.used_pages() == [0]
+        assert (runner.speculated_steps > 0) == pipeline
+    assert outs[True] == outs[False]
+    for p, n, o in zip(prompts, lens, outs[True]):
+        assert o == expected_generation(p, n, 977)
+
+
+def test_pipelined_engine_drops_the_share_of_a_request_that_stopped():
+    """A stop token is seen one step late: the speculated step's token for that request is dropped, the
+    others' are kept, and the pages come back."""
+    prompts = [[5, 6, 7], [11, 12, 13, 14], [21, 22]]
+    full = [expected_generation(p, 30, 977) for p in prompts]
+    stop = full[1][9]                                   # request 1 stops on its tenth token
+    cut = [o[:o.index(stop)] if stop in o else o for o in full]
+    assert len(cut[1]) <= 9
+    for pipeline in (False, True):
+        runner, eng = make(512, pipeline=pipeline)
+        seqs = [eng.submit(Request(prompt=p, sampling=GREEDY, max_tokens=30, stop_tokens=(stop,))) for p in prompts]
+        run_all(eng, runner, seqs)
+        eng.drain()
+        assert [list(s.output) for s in seqs] == cut
+        assert [s.finished for s in seqs] == ["stop" if len(c) < 30 else "length" for c in cut]
+        assert runner.cache.check() == "" and runner.cache.used_pages() == [0] and runner.cache.free_slots() == 64
+    assert runner.speculated_steps > 0
+
+
+def test_pipelined_engine_takes_new_requests_and_cancellations():
+    runner, eng = make(512, pipeline=True)
+    a = eng.submit(Request(prompt=[1, 2, 3], sampling=GREEDY, max_tokens=40, ignore_eos=True))
+    for _ in range(6):
+        assert eng.step()
+    n0 = runner.speculated_steps
+    assert n0 > 0
+    b = eng.submit(Request(prompt=[9, 8, 7, 6], sampling=GREEDY, max_tokens=12, ignore_eos=True))
+    for _ in range(4):
+        assert eng.step()
+    a.cancelled = True
+    run_all(eng, runner, [a, b])
+    eng.drain()
+    assert a.finished == "cancelled" and list(b.output) == expected_generation([9, 8, 7, 6], 12, 977)
+    assert list(a.output) == expected_generation([1, 2, 3], 40, 977)[:len(a.output)]
+    assert runner.cache.used_pages() == [0]
