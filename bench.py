@@ -117,14 +117,14 @@ def model_bytes_and_flops(cfg, n_layers):
     return weights + norms, kv_per_token, prefill_flops
 
 
-def build_llm(cfg, n_layers, batch, seed=0):
+def build_llm(cfg, n_layers, batch, seed=0, prefill_tokens=PREFILL_TOKENS):
     import ember_b200
     from ember_b200.config import Qwen3Config
-    d = dict(cfg.to_json(), num_hidden_layers=n_layers)
+    d = dict(cfg.to_json(), num_hidden_layers=n_layers, max_position_embeddings=max(cfg.max_position_embeddings, prefill_tokens))
     c = Qwen3Config.from_json(d)
-    cap = batch * CONTEXT
+    cap = max(batch * CONTEXT, prefill_tokens)
     return ember_b200.load_random(c, seed=seed, dtype="bfloat16", kv_cache_tokens=cap,
-                                  max_batch_tokens=max(PREFILL_TOKENS, 2048), max_seqs=max(batch, 1), prefill_chunk=2048)
+                                  max_batch_tokens=max(prefill_tokens, 2048), max_seqs=max(batch, 1), prefill_chunk=2048)
 
 
 def fill_cache(llm, batch, context):
@@ -247,6 +247,8 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
     ap.add_argument("--only-prefill", action="store_true", help="profiling aid: run just the 2,048-token prefill")
+    ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS,
+                    help="with --only-prefill: another prompt length (the reported line stays at 2,048)")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -268,10 +270,11 @@ def main() -> int:
     wbytes, kv_per_token, prefill_flops = model_bytes_and_flops(cfg, n_layers)
 
     if args.only_prefill:
-        llm = build_llm(cfg, n_layers, 1)
-        pms = time_prefill(llm, PREFILL_TOKENS, reps=max(1, min(5, args.steps)), warmup=min(3, warmup))
-        fl = prefill_flops(PREFILL_TOKENS)
-        print(json.dumps({"prefill": {"value": round(PREFILL_TOKENS / (pms * 1e-3), 1), "tokens": PREFILL_TOKENS,
+        n_tok = max(2, args.prefill_tokens)
+        llm = build_llm(cfg, n_layers, 1, prefill_tokens=n_tok)
+        pms = time_prefill(llm, n_tok, reps=max(1, min(5, args.steps)), warmup=min(3, warmup))
+        fl = prefill_flops(n_tok)
+        print(json.dumps({"prefill": {"value": round(n_tok / (pms * 1e-3), 1), "tokens": n_tok,
                                       "ms": round(pms, 3), "tflops": round(fl / (pms * 1e-3) / 1e12, 1), "layers": n_layers}}))
         return 0
 

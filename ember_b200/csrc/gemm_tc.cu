@@ -88,7 +88,7 @@ static int pair_capacity(int num_sms) {
 // 148 SMs with 16 row tiles runs 144 tiles of 240 columns in one wave, faster than 128 tiles of 256.  Tiles
 // narrower than 192 columns re-read the token rows too often to pay.
 static int best_block_cols(int M, int N, int slots, int units, double* cost_out) {
-    const int rows = TILE_ROWS * units, step = 16 * units;
+    const int rows = TILE_ROWS * units, step = 16;
     const int row_tiles = (M + rows - 1) / rows;
     int best = 256;
     double best_cost = 1e30;
@@ -98,9 +98,9 @@ static int best_block_cols(int M, int N, int slots, int units, double* cost_out)
         if (cost < best_cost * 0.999) { best_cost = cost; best = bc; }
     }
     if (N <= 128) { best = 128; best_cost = (double)((row_tiles + slots - 1) / slots) * (128 + 40); }
-    if (const char* f = getenv("EMBER_GEMM_TILE_COLS")) {       // tuning aid: force the width (a multiple of 32)
+    if (const char* f = getenv("EMBER_GEMM_TILE_COLS")) {       // tuning aid: force the width (a multiple of 16)
         const int v = atoi(f);
-        if (v >= 32 && v <= 256 && v % 32 == 0) best = v;
+        if (v >= 32 && v <= 256 && v % 16 == 0) best = v;
     }
     if (cost_out) *cost_out = best_cost;
     return best;

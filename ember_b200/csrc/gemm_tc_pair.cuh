@@ -19,7 +19,7 @@
 
 namespace ember {
 
-constexpr int PAIR_MAX_COLS = 256;      // weight rows per pair tile (a multiple of 32; each block holds half of them)
+constexpr int PAIR_MAX_COLS = 256;      // weight rows per pair tile (a multiple of 16; each block holds half of them)
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
     uint32_t r;

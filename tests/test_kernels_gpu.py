@@ -50,6 +50,27 @@ def test_gemm_tc(M, N, K, epilogue, split_mode):
         assert float(ops._tc_scratch[a.device].abs().max()) == 0.0
 
 
+@pytest.mark.parametrize("cols", [64, 208, 240])
+@pytest.mark.parametrize("split_mode", [4, 5])
+def test_gemm_tc_tile_widths(cols, split_mode, monkeypatch):
+    """Every tile width the shape heuristic may choose, forced, on one SM and on pairs."""
+    from ember_b200 import ops
+    monkeypatch.setenv("EMBER_GEMM_TILE_COLS", str(cols))
+    torch.manual_seed(cols)
+    M, N, K = 700, 1000, 264
+    a = (torch.randn(M, K, device="cuda") * 0.5).bfloat16()
+    w = (torch.randn(N, K, device="cuda") * 0.5).bfloat16()
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    for epilogue in (0, 2, 3):
+        n_out = N // 2 if epilogue == 3 else N
+        prev = torch.randn(M, n_out, device="cuda")
+        out = prev.clone() if epilogue == 2 else torch.zeros(M, n_out, device="cuda", dtype=torch.bfloat16)
+        ops.gemm_tc(a, w, out, M, epilogue, err=err, split_mode=split_mode)
+        want = ref_epilogue(a.float() @ w.float().t(), epilogue, prev)
+        assert int(err.item()) == 0
+        assert rel(out.float(), want) < (5e-3 if epilogue in (0, 3) else 1e-5)
+
+
 @pytest.mark.parametrize("M,N,K", [(1, 50, 7), (5, 1000, 96), (70, 130, 33), (200, 192, 64)])
 @pytest.mark.parametrize("epilogue", [0, 1, 2, 3])
 @pytest.mark.parametrize("adt,wdt", [(torch.float32, torch.float32), (torch.bfloat16, torch.bfloat16),
