@@ -53,11 +53,13 @@ __device__ __forceinline__ void store4<__nv_bfloat16>(__nv_bfloat16* dst, float 
 }
 
 constexpr int NORM_THREADS = 256;
-constexpr int NORM_VEC = 8;      // float4 per thread kept in registers: rows up to 256 * 8 * 4 = 8192 wide
+constexpr int NORM_MAX_VEC = 8;  // float4 per thread kept in registers: rows up to 256 * 8 * 4 = 8192 wide
 
 // Rows whose width is a multiple of 4 and at most 8192 are read once, 16 bytes at a time, and kept in
-// registers between the reduction and the scaling; other widths take the two-pass scalar path.
-template <typename TO>
+// registers between the reduction and the scaling (NORM_VEC float4 per thread: the smallest of 1, 2, 4, 8 that
+// covers the row, so that a narrow row does not pay for the registers of a wide one); other widths take the
+// two-pass scalar path (NORM_VEC = 0).
+template <typename TO, int NORM_VEC>
 __global__ void __launch_bounds__(NORM_THREADS)
 rmsnorm_kernel(const float* __restrict__ x, const int* __restrict__ rows,
                const float* __restrict__ w, float eps, TO* __restrict__ out, int H) {
@@ -68,7 +70,7 @@ rmsnorm_kernel(const float* __restrict__ x, const int* __restrict__ rows,
     const float* in = x + (size_t)(rows ? rows[r] : r) * H;
     TO* o = out + (size_t)r * H;
     const int nvec = H >> 2;
-    if ((H & 3) == 0 && nvec <= NORM_THREADS * NORM_VEC) {
+    if constexpr (NORM_VEC > 0) {
         float4 v[NORM_VEC];
         float ss = 0.0f;
 #pragma unroll
@@ -201,6 +203,145 @@ __global__ void qk_norm_rope_store_kernel(
     }
 }
 
+// Head size 128 with the whole head rotated (or no rotation): half a warp holds a head in registers, eight
+// consecutive elements per lane, loaded and stored 16 (bf16) or 2 x 16 (fp32) bytes at a time; a warp works on
+// two heads at once.  The rotation partner of element i is i +- 64, eight lanes away, and comes by shuffle.  The
+// token's 64 sines and cosines are computed once per block.  Every lane runs every shuffle (heads that are not
+// wanted are computed on zeros and not stored), so heads of different kinds may share a warp.
+template <typename T>
+__device__ __forceinline__ void load8(const T* p, float* x);
+template <>
+__device__ __forceinline__ void load8<float>(const float* p, float* x) {
+    const float4 a = reinterpret_cast<const float4*>(p)[0], b = reinterpret_cast<const float4*>(p)[1];
+    x[0] = a.x; x[1] = a.y; x[2] = a.z; x[3] = a.w; x[4] = b.x; x[5] = b.y; x[6] = b.z; x[7] = b.w;
+}
+template <>
+__device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* p, float* x) {
+    const uint4 u = *reinterpret_cast<const uint4*>(p);
+    const uint32_t w[4] = {u.x, u.y, u.z, u.w};
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        const float2 f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&w[i]));
+        x[2 * i] = f.x;
+        x[2 * i + 1] = f.y;
+    }
+}
+template <typename T>
+__device__ __forceinline__ void store8(T* p, const float* x);
+template <>
+__device__ __forceinline__ void store8<float>(float* p, const float* x) {
+    reinterpret_cast<float4*>(p)[0] = make_float4(x[0], x[1], x[2], x[3]);
+    reinterpret_cast<float4*>(p)[1] = make_float4(x[4], x[5], x[6], x[7]);
+}
+template <>
+__device__ __forceinline__ void store8<__nv_bfloat16>(__nv_bfloat16* p, const float* x) {
+    uint4 u;
+    __nv_bfloat162 h0 = __floats2bfloat162_rn(x[0], x[1]), h1 = __floats2bfloat162_rn(x[2], x[3]);
+    __nv_bfloat162 h2 = __floats2bfloat162_rn(x[4], x[5]), h3 = __floats2bfloat162_rn(x[6], x[7]);
+    u.x = *reinterpret_cast<uint32_t*>(&h0); u.y = *reinterpret_cast<uint32_t*>(&h1);
+    u.z = *reinterpret_cast<uint32_t*>(&h2); u.w = *reinterpret_cast<uint32_t*>(&h3);
+    *reinterpret_cast<uint4*>(p) = u;
+}
+
+constexpr int ROPE128_WARPS = 4;
+
+template <typename T>
+__global__ void __launch_bounds__(ROPE128_WARPS * 32)
+qk_norm_rope_store_d128_kernel(
+    const T* __restrict__ qkv, int ld, int n_heads, int n_kv,
+    const float* __restrict__ q_norm_w, const float* __restrict__ k_norm_w, float eps,
+    const float* __restrict__ inv_freq, int rotate,
+    const int* __restrict__ positions, const int* __restrict__ seq_of,
+    const int* __restrict__ block_table, int max_blocks, int page, int num_pages,
+    T* __restrict__ q_out, T* __restrict__ k_pool, T* __restrict__ v_pool, int write_kv,
+    int* __restrict__ err) {
+    constexpr int D = 128;
+    __shared__ __align__(16) float cs_s[64];
+    __shared__ __align__(16) float sn_s[64];
+    pdl_launch_dependents();
+    pdl_wait();
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x;
+    const int slots = n_heads + 2 * n_kv;
+    const int pos = positions[t];
+    if (rotate && threadIdx.x < 64) sincosf((float)pos * inv_freq[threadIdx.x], &sn_s[threadIdx.x], &cs_s[threadIdx.x]);
+    int blk = -1;
+    if (write_kv) {
+        blk = block_table[(size_t)seq_of[t] * max_blocks + pos / page];
+        if (blk < 0 || blk >= num_pages) {
+            if (threadIdx.x == 0 && err) atomicOr(err, EMBER_ERR_PAGE_RANGE);
+            blk = -1;
+        }
+    }
+    __syncthreads();
+    const int hl = lane & 15;                      // lane within the half-warp that holds one head
+    const int e0 = 8 * hl;                         // this lane's elements e0 .. e0 + 7
+    const bool upper = hl >= 8;                    // elements 64..127: rotated as b * cos + a * sin
+    float cs[8], sn[8];
+    if (rotate) {
+        const int r0 = e0 & 63;
+#pragma unroll
+        for (int j = 0; j < 8; j += 4) {
+            const float4 c = *reinterpret_cast<const float4*>(&cs_s[r0 + j]), sv = *reinterpret_cast<const float4*>(&sn_s[r0 + j]);
+            cs[j] = c.x; cs[j + 1] = c.y; cs[j + 2] = c.z; cs[j + 3] = c.w;
+            sn[j] = sv.x; sn[j + 1] = sv.y; sn[j + 2] = sv.z; sn[j + 3] = sv.w;
+        }
+    }
+    // where this token's keys and values go: page blk, place pos % page (per key head: + kvh * page * D)
+    const size_t kv_base = blk >= 0 ? ((size_t)blk * n_kv * page + (size_t)(pos % page)) * D + e0 : 0;
+    const size_t kv_head = (size_t)page * D;
+    const T* src_row = qkv + (size_t)t * ld + e0;
+    T* q_row = q_out + (size_t)t * n_heads * D + e0;
+    const bool kv_ok = write_kv && blk >= 0;
+    // a warp takes two heads per turn; blockIdx.y splits the heads between blocks when a step has few tokens
+    for (int slot = 2 * (blockIdx.y * ROPE128_WARPS + warp) + (lane >> 4); slot < slots + 1;
+         slot += 2 * ROPE128_WARPS * gridDim.y) {
+        const int kind = slot < n_heads ? 0 : (slot < n_heads + n_kv ? 1 : 2);  // q, k, v
+        const bool act = slot < slots && (kind == 0 || kv_ok);
+        float x[8];
+        if (act) {
+            load8<T>(src_row + (size_t)slot * D, x);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; j++) x[j] = 0.0f;
+        }
+        const int first = slot - (lane >> 4);       // the warp's lower head: values only from n_heads + n_kv on
+        if (first < n_heads + n_kv) {               // uniform over the warp
+            float ss = 0.0f;
+#pragma unroll
+            for (int j = 0; j < 8; j++) ss = fmaf(x[j], x[j], ss);
+#pragma unroll
+            for (int o = 8; o > 0; o >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, o);     // within the half-warp
+            const float* nw = kind == 0 ? q_norm_w : (kind == 1 ? k_norm_w : nullptr);
+            if (nw && act) {
+                const float scale = 1.0f / sqrtf(ss / (float)D + eps);
+                const float4 g0 = *reinterpret_cast<const float4*>(nw + e0), g1 = *reinterpret_cast<const float4*>(nw + e0 + 4);
+                x[0] = g0.x * (x[0] * scale); x[1] = g0.y * (x[1] * scale); x[2] = g0.z * (x[2] * scale); x[3] = g0.w * (x[3] * scale);
+                x[4] = g1.x * (x[4] * scale); x[5] = g1.y * (x[5] * scale); x[6] = g1.z * (x[6] * scale); x[7] = g1.w * (x[7] * scale);
+            }
+            if (rotate) {
+                const bool turn = kind != 2;
+#pragma unroll
+                for (int j = 0; j < 8; j++) {
+                    const float other = __shfl_xor_sync(0xffffffffu, x[j], 8);
+                    // lower half: a * cos - b * sin (a own, b partner); upper half: b * cos + a * sin (b own, a partner)
+                    const float r = upper ? x[j] * cs[j] + other * sn[j] : x[j] * cs[j] - other * sn[j];
+                    x[j] = turn ? r : x[j];
+                }
+            }
+        }
+        if (!act) continue;
+        T* dst;
+        if (kind == 0) {
+            dst = q_row + (size_t)slot * D;
+        } else {
+            const int kvh = kind == 1 ? slot - n_heads : slot - n_heads - n_kv;
+            dst = (kind == 1 ? k_pool : v_pool) + kv_base + (size_t)kvh * kv_head;
+        }
+        store8<T>(dst, x);
+    }
+}
+
 // out[m, j] = silu(x[m, 2j]) * x[m, 2j+1] for an unfused gate/up product (interleaved rows).
 template <typename T>
 __global__ void silu_mul_interleaved_kernel(const T* __restrict__ x, T* __restrict__ out, size_t n_out) {
@@ -239,12 +380,24 @@ EMBER_API int ember_rmsnorm(const float* x, const int* rows, const float* w, flo
     cudaStream_t st = (cudaStream_t)stream;
     if ((((uintptr_t)x) | ((uintptr_t)w) | ((uintptr_t)out)) & 15) return fail("rmsnorm: buffers must be 16-byte aligned");
     const int threads = NORM_THREADS;
-    if (out_dtype == EMBER_F32)
-        launch_kernel(rmsnorm_kernel<float>, n_rows, threads, 0, st, x, rows, w, eps, (float*)out, H);
-    else if (out_dtype == EMBER_BF16)
-        launch_kernel(rmsnorm_kernel<__nv_bfloat16>, n_rows, threads, 0, st, x, rows, w, eps, (__nv_bfloat16*)out, H);
-    else
-        return fail("rmsnorm: unsupported output dtype %d", out_dtype);
+    const int nvec = H >> 2;
+    int vec = 0;
+    if ((H & 3) == 0 && nvec <= NORM_THREADS * NORM_MAX_VEC)
+        vec = nvec <= NORM_THREADS ? 1 : (nvec <= 2 * NORM_THREADS ? 2 : (nvec <= 4 * NORM_THREADS ? 4 : 8));
+    if (out_dtype != EMBER_F32 && out_dtype != EMBER_BF16) return fail("rmsnorm: unsupported output dtype %d", out_dtype);
+#define EMBER_NORM_LAUNCH(TO, V) \
+    launch_kernel(rmsnorm_kernel<TO, V>, n_rows, threads, 0, st, x, rows, w, eps, (TO*)out, H)
+#define EMBER_NORM_DISPATCH(TO)                                             \
+    switch (vec) {                                                          \
+        case 1: EMBER_NORM_LAUNCH(TO, 1); break;                            \
+        case 2: EMBER_NORM_LAUNCH(TO, 2); break;                            \
+        case 4: EMBER_NORM_LAUNCH(TO, 4); break;                            \
+        case 8: EMBER_NORM_LAUNCH(TO, 8); break;                            \
+        default: EMBER_NORM_LAUNCH(TO, 0); break;                           \
+    }
+    if (out_dtype == EMBER_F32) { EMBER_NORM_DISPATCH(float) } else { EMBER_NORM_DISPATCH(__nv_bfloat16) }
+#undef EMBER_NORM_DISPATCH
+#undef EMBER_NORM_LAUNCH
     return check_launch("rmsnorm");
 }
 
@@ -270,6 +423,26 @@ EMBER_API int ember_qk_norm_rope_store(const void* qkv, int dtype, int T, int ld
     dim3 grid(T, ny);
     const size_t smem = ((size_t)warps * D + (size_t)(inv_freq ? rotary : 0)) * sizeof(float);
     if (ld & 1) return fail("qk_norm_rope_store: the row stride %d must be even", ld);
+    const bool rotate = inv_freq != nullptr && rotary > 0;
+    const bool aligned = (ld % 8) == 0 && (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_pool | (uintptr_t)v_pool |
+                                            (uintptr_t)q_norm_w | (uintptr_t)k_norm_w) & 15) == 0;
+    if (D == 128 && (!rotate || rotary == 128) && aligned && (dtype == EMBER_F32 || dtype == EMBER_BF16)) {
+        int gy = (592 + T - 1) / T;                       // a decode step of a few tokens still fills the SMs
+        const int gy_max = (slots + 2 * ROPE128_WARPS - 1) / (2 * ROPE128_WARPS);
+        if (gy > gy_max) gy = gy_max;
+        if (gy < 1) gy = 1;
+        dim3 g128(T, gy);
+        if (dtype == EMBER_F32)
+            launch_kernel(qk_norm_rope_store_d128_kernel<float>, g128, ROPE128_WARPS * 32, 0, st,
+                (const float*)qkv, ld, n_heads, n_kv, q_norm_w, k_norm_w, eps, inv_freq, rotate ? 1 : 0, positions, seq_of,
+                block_table, max_blocks, page, num_pages, (float*)q_out, (float*)k_pool, (float*)v_pool, write_kv, err);
+        else
+            launch_kernel(qk_norm_rope_store_d128_kernel<__nv_bfloat16>, g128, ROPE128_WARPS * 32, 0, st,
+                (const __nv_bfloat16*)qkv, ld, n_heads, n_kv, q_norm_w, k_norm_w, eps, inv_freq, rotate ? 1 : 0, positions,
+                seq_of, block_table, max_blocks, page, num_pages, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool,
+                (__nv_bfloat16*)v_pool, write_kv, err);
+        return check_launch("qk_norm_rope_store");
+    }
     if (dtype == EMBER_F32)
         launch_kernel(qk_norm_rope_store_kernel<float>, grid, warps * 32, smem, st,
             (const float*)qkv, ld, n_heads, n_kv, D, q_norm_w, k_norm_w, eps, inv_freq, rotary, positions, seq_of,

@@ -145,7 +145,8 @@ def rope_ref(x, pos, inv_freq, rotary):
 
 
 @pytest.mark.parametrize("heads,kv,D,rotary,page", [(4, 2, 16, 16, 16), (6, 1, 32, 32, 16), (5, 5, 48, 24, 32),
-                                                    (16, 8, 128, 128, 16), (3, 1, 256, 256, 64), (2, 2, 80, 0, 16)])
+                                                    (16, 8, 128, 128, 16), (3, 1, 256, 256, 64), (2, 2, 80, 0, 16),
+                                                    (5, 3, 128, 0, 32), (3, 3, 128, 64, 16)])
 @pytest.mark.parametrize("dt", [torch.float32, torch.bfloat16])
 @pytest.mark.parametrize("norm", [True, False])
 def test_qk_norm_rope_store(heads, kv, D, rotary, page, dt, norm):
