@@ -37,7 +37,8 @@ namespace ember {
 constexpr int FA_ROWS = 128;          // query rows per block = TMEM lanes
 constexpr int FA_KT = 64;             // keys per tile
 constexpr int FA_D = 128;             // head size
-constexpr int FA_STAGES = 2;
+constexpr int FA_K_STAGES = 3;        // key tiles in flight or in use (a key tile is free once S = Q K^T has read it)
+constexpr int FA_V_STAGES = 2;        // value tiles (free once O += P V has read them)
 constexpr int FA_THREADS = 192;
 constexpr unsigned FA_WAIT_LIMIT = 1u << 24;
 constexpr float FA_LOG2E = 1.4426950408889634f;
@@ -188,15 +189,17 @@ attention_fa_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
         return;
     }
     uint8_t* q_s = smem;                                  // 32 KiB, two halves
-    uint8_t* k_s = q_s + 2 * Q_HALF;                      // FA_STAGES x 16 KiB
-    uint8_t* v_s = k_s + FA_STAGES * KV_TILE;             // FA_STAGES x 16 KiB
-    uint64_t* kv_full = (uint64_t*)(v_s + FA_STAGES * KV_TILE);
-    uint64_t* kv_empty = kv_full + FA_STAGES;
-    uint64_t* s_full = kv_empty + FA_STAGES;              // [2]
+    uint8_t* k_s = q_s + 2 * Q_HALF;                      // FA_K_STAGES x 16 KiB
+    uint8_t* v_s = k_s + FA_K_STAGES * KV_TILE;           // FA_V_STAGES x 16 KiB
+    uint64_t* k_full = (uint64_t*)(v_s + FA_V_STAGES * KV_TILE);
+    uint64_t* k_empty = k_full + FA_K_STAGES;
+    uint64_t* v_full = k_empty + FA_K_STAGES;
+    uint64_t* v_empty = v_full + FA_V_STAGES;
+    uint64_t* s_full = v_empty + FA_V_STAGES;             // [2]
     uint64_t* s_empty = s_full + 2;                       // [2]
     uint64_t* q_ready = s_empty + 2;
-    uint64_t* p_full = q_ready + 1;
-    uint64_t* pv_full = p_full + 1;
+    uint64_t* p_full = q_ready + 1;                       // [2]: the softmax warps may be a tile ahead of the MMA thread
+    uint64_t* pv_full = p_full + 2;
     uint32_t* tmem_slot = (uint32_t*)(pv_full + 1);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
@@ -213,16 +216,21 @@ attention_fa_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
     const int n_kt = hi > k_begin ? (hi - k_begin + FA_KT - 1) / FA_KT : 0;
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < FA_STAGES; i++) {
-            fa_mbar_init(&kv_full[i], 1);
-            fa_mbar_init(&kv_empty[i], 1);
+        for (int i = 0; i < FA_K_STAGES; i++) {
+            fa_mbar_init(&k_full[i], 1);
+            fa_mbar_init(&k_empty[i], 1);
+        }
+        for (int i = 0; i < FA_V_STAGES; i++) {
+            fa_mbar_init(&v_full[i], 1);
+            fa_mbar_init(&v_empty[i], 1);
         }
         for (int i = 0; i < 2; i++) {
             fa_mbar_init(&s_full[i], 1);
             fa_mbar_init(&s_empty[i], 4);
         }
         fa_mbar_init(q_ready, 4);
-        fa_mbar_init(p_full, 4);
+        fa_mbar_init(&p_full[0], 4);
+        fa_mbar_init(&p_full[1], 4);
         fa_mbar_init(pv_full, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -253,25 +261,53 @@ attention_fa_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
             }
             return (blk * p.n_kv + kvh) * p.page;
         };
-        int y = page_row(0);
-        bool ok = true;
-        for (int it = 0; it < n_kt; it++) {
-            const int b = it % FA_STAGES;
-            const int y_next = page_row(it + 1);
-            if (it >= FA_STAGES) ok = fa_wait(&kv_empty[b], (uint32_t)(it / FA_STAGES - 1) & 1u, abort_flag);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) break;
-            if (lane == 0) fa_expect_tx(&kv_full[b], (uint32_t)(2 * KV_TILE));
+        // Keys and values travel in rings of their own: a key tile is free as soon as S = Q K^T has read it,
+        // long before the value tile of the same keys, so key tiles are requested three tiles ahead and the
+        // latency of a fetch (16 small boxes a tile with 16-token pages) stays off the critical path.
+        // (the tensor maps are named directly: the copy instruction wants the address of the kernel parameter)
+        auto fetch_k = [&](uint8_t* dst, uint64_t* bar, int y) {
+            if (lane == 0) fa_expect_tx(bar, (uint32_t)KV_TILE);
             __syncwarp();
             if (lane < boxes) {
 #pragma unroll
-                for (int h = 0; h < 2; h++) {
-                    const int off = h * KV_HALF + lane * p.page * 128;
-                    fa_tma_2d(k_s + b * KV_TILE + off, &map_k, &kv_full[b], h * 64, y);
-                    fa_tma_2d(v_s + b * KV_TILE + off, &map_v, &kv_full[b], h * 64, y);
-                }
+                for (int h = 0; h < 2; h++) fa_tma_2d(dst + h * KV_HALF + lane * p.page * 128, &map_k, bar, h * 64, y);
             }
-            y = y_next;
+        };
+        auto fetch_v = [&](uint8_t* dst, uint64_t* bar, int y) {
+            if (lane == 0) fa_expect_tx(bar, (uint32_t)KV_TILE);
+            __syncwarp();
+            if (lane < boxes) {
+#pragma unroll
+                for (int h = 0; h < 2; h++) fa_tma_2d(dst + h * KV_HALF + lane * p.page * 128, &map_v, bar, h * 64, y);
+            }
+        };
+        bool ok = true;
+        // order of need: K_0 .. K_{ks-1}, then V_i before K_{i + ks}
+        int yk = page_row(0);
+        for (int it = 0; it < min(n_kt, FA_K_STAGES); it++) {
+            const int y_next = page_row(it + 1);
+            fetch_k(k_s + it * KV_TILE, &k_full[it], yk);
+            yk = y_next;
+        }
+        int yv = page_row(0);
+        for (int it = 0; it < n_kt && ok; it++) {
+            const int bv = it % FA_V_STAGES;
+            const int yv_next = page_row(it + 1);
+            if (it >= FA_V_STAGES) ok = fa_wait(&v_empty[bv], (uint32_t)(it / FA_V_STAGES - 1) & 1u, abort_flag);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) break;
+            fetch_v(v_s + bv * KV_TILE, &v_full[bv], yv);
+            yv = yv_next;
+            const int ik = it + FA_K_STAGES;
+            if (ik < n_kt) {
+                const int bk = ik % FA_K_STAGES;
+                const int yk_next = page_row(ik + 1);
+                ok = fa_wait(&k_empty[bk], (uint32_t)(ik / FA_K_STAGES - 1) & 1u, abort_flag);
+                ok = __all_sync(0xffffffffu, ok);
+                if (!ok) break;
+                fetch_k(k_s + bk * KV_TILE, &k_full[bk], yk);
+                yk = yk_next;
+            }
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA issuer
@@ -279,7 +315,7 @@ attention_fa_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
             const uint32_t idesc_s = fa_idesc(FA_KT, 0), idesc_o = fa_idesc(FA_D, 1);
             bool ok = fa_wait(q_ready, 0, abort_flag);
             auto issue_s = [&](int j) {
-                const int b = j % FA_STAGES;
+                const int b = j % FA_K_STAGES;
                 const uint32_t d = tmem_s0 + (uint32_t)((j & 1) * FA_KT);
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
@@ -289,21 +325,25 @@ attention_fa_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
                     fa_mma(d, da, db, idesc_s, kk > 0 ? 1u : 0u);
                 }
                 fa_commit(&s_full[j & 1]);
+                fa_commit(&k_empty[b]);          // the keys of tile j are no longer read
             };
-            if (ok) ok = fa_wait(&kv_full[0], 0, abort_flag);
+            if (ok) ok = fa_wait(&k_full[0], 0, abort_flag);
             if (ok) issue_s(0);
             for (int j = 0; j < n_kt && ok; j++) {
                 if (j + 1 < n_kt) {
-                    ok = fa_wait(&kv_full[(j + 1) % FA_STAGES], (uint32_t)((j + 1) / FA_STAGES) & 1u, abort_flag);
+                    ok = fa_wait(&k_full[(j + 1) % FA_K_STAGES], (uint32_t)((j + 1) / FA_K_STAGES) & 1u, abort_flag);
                     // S_{j+1} reuses the columns of S_{j-1} / P_{j-1}: the second product of tile j - 1 was
                     // issued before and the tensor core runs in order, and p_full(j - 1) said S_{j-1} was read
                     if (!ok) break;
                     issue_s(j + 1);
                 }
-                ok = fa_wait(p_full, (uint32_t)j & 1u, abort_flag);
+                const int b = j % FA_V_STAGES;
+                // (one barrier per S buffer: the softmax warps finish tile j + 1 without this thread, so a single
+                // barrier could complete twice before it is looked at here)
+                ok = fa_wait(&p_full[j & 1], (uint32_t)(j >> 1) & 1u, abort_flag);
+                if (ok) ok = fa_wait(&v_full[b], (uint32_t)(j / FA_V_STAGES) & 1u, abort_flag);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const int b = j % FA_STAGES;
 #pragma unroll
                 for (int kk = 0; kk < FA_KT / 16; kk++) {
                     // P_j: 64 keys = 32 packed columns in the S buffer of tile j; 16 keys = 8 columns per step
@@ -311,7 +351,7 @@ attention_fa_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
                     const uint64_t db = fa_desc_mn(v_s + b * KV_TILE, KV_HALF) + (uint64_t)((kk * 16 * 128) >> 4);
                     fa_mma_ts(tmem_o, pa, db, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
                 }
-                fa_commit(&kv_empty[b]);        // keys and values of tile j are no longer read
+                fa_commit(&v_empty[b]);         // the values of tile j are no longer read
                 fa_commit(pv_full);             // O_j is complete, P may be overwritten
             }
         }
@@ -416,7 +456,7 @@ attention_fa_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             l_run += sum;
             __syncwarp();
-            if (lane == 0) fa_arrive(p_full);
+            if (lane == 0) fa_arrive(&p_full[j & 1]);
         }
         if (n_kt > 0 && ok) ok = fa_wait(pv_full, (uint32_t)(n_kt - 1) & 1u, abort_flag);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -526,7 +566,7 @@ EMBER_API int ember_attention_fa(const void* q, const void* k_pool, const void* 
     p.q = (const __nv_bfloat16*)q; p.out = (__nv_bfloat16*)out; p.tiles = tiles; p.block_table = block_table;
     p.max_blocks = max_blocks; p.page = page; p.num_pages = num_pages; p.n_heads = n_heads; p.n_kv = n_kv;
     p.window = window; p.scale_log2 = scale * FA_LOG2E; p.n_tiles = n_tiles; p.err = err;
-    const size_t smem = (size_t)2 * FA_ROWS * 128 + (size_t)FA_STAGES * 2 * 2 * FA_KT * 128 + 256;
+    const size_t smem = (size_t)2 * FA_ROWS * 128 + (size_t)(FA_K_STAGES + FA_V_STAGES) * 2 * FA_KT * 128 + 256;
     static bool attr = false;
     if (!attr) {
         cudaError_t e = cudaFuncSetAttribute(attention_fa_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
