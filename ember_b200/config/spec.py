@@ -137,6 +137,10 @@ class ModelSpec:
     eos_ids: Tuple[int, ...] = ()
     init_std: float = 0.02                # random-weights mode: std of linear weights
     init_norm_std: float = 0.05           # random-weights mode: norm weights are 1 + N(0, this)
+    # a position encoding that acts on the embedded tokens (learned or sinusoidal tables); rotary ones
+    # belong to their mixer's spec instead
+    embedding_position: PartSpec = field(default_factory=NoPositionSpec)
+    embedding_position_prefix: str = "model.embed_positions."
 
     def __post_init__(self):
         n = len(self.layers)

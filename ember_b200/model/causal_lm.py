@@ -24,6 +24,7 @@ class CausalLM:
         self.spec = spec
         self.blocks = [part_class("arrangement", ls.arrangement)(ls) for ls in spec.layers]
         self.final_norm = build_part("norm", spec.final_norm, spec.final_norm_prefix)
+        self.embedding_position = build_part("position", spec.embedding_position, spec.embedding_position_prefix)
         self.rt: Optional[Runtime] = None
 
     # ------------------------------------------------------------------ weights
@@ -33,6 +34,7 @@ class CausalLM:
         if not s.tie_embeddings:
             d.append(WeightDecl(s.head_name, (s.vocab_size, s.hidden_size), optional=s.head_optional))
         d += self.final_norm.weight_decls()
+        d += self.embedding_position.weight_decls()
         for b in self.blocks:
             d += b.weight_decls()
         return d
@@ -53,6 +55,7 @@ class CausalLM:
         if self.embedding is not None:
             self.head = Linear.from_host(head, rt) if head is not None else Linear(self.embedding)
         self.final_norm.load(store, rt)
+        self.embedding_position.load(store, rt)
         for b in self.blocks:
             b.load(store, rt)
         store.finish()
@@ -81,6 +84,7 @@ class CausalLM:
         s, rt = self.spec, self.rt
         h = ctx.buf("model.residual", (ctx.max_tokens, s.hidden_size), torch.float32)
         ops.embed(ctx.tokens, self.embedding, h, err=ctx.err, stream=ctx.stream, prev_ids=ctx.prev_ids)
+        self.embedding_position.on_embedding(ctx, h)          # nothing for rotary or absent encodings
         for e in s.schedule:
             owner = e.cache_of if e.cache_of >= 0 else e.layer
             self.blocks[e.layer].forward(ctx, h, storage.layer(owner), owns_cache=(owner == e.layer))

@@ -260,3 +260,138 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped():
     assert rel(torch.cat(got), whole) < 2e-5
     assert r.cache.check() == ""
     assert not torch.isnan(whole).any() and whole.abs().max() > 0
+
+
+# ------------------------------------- a toy feed-forward with routing and a toy position encoding
+@dataclass(frozen=True)
+class RoutedSpec:
+    """Two experts, each y = W2 . relu(W1 . x); a token goes to the expert with the larger fp32 router logit."""
+    kind: ClassVar[str] = "toy_top1_of_2"
+    hidden_size: int = 0
+    expert_size: int = 0
+
+
+@dataclass(frozen=True)
+class LearnedPositionSpec:
+    """h_t += table[position of t]: acts on the embedded tokens, not inside a mixer."""
+    kind: ClassVar[str] = "toy_learned_positions"
+    hidden_size: int = 0
+    max_positions: int = 0
+
+
+def make_toy_feed_forward_and_positions():
+    from ember_b200.parts import FeedForward, PositionEncoding, WeightDecl
+
+    class Routed(FeedForward):
+        used = set()                                            # which experts any step chose (looked at by the test)
+
+        def weight_decls(self):
+            h, e, p = self.spec.hidden_size, self.spec.expert_size, self.prefix
+            d = [WeightDecl(p + "router.weight", (2, h))]
+            for i in range(2):
+                d += [WeightDecl(p + f"experts.{i}.w1", (e, h)), WeightDecl(p + f"experts.{i}.w2", (h, e))]
+            return d
+
+        def load(self, store, rt):
+            h, e, p = self.spec.hidden_size, self.spec.expert_size, self.prefix
+            self.router = store.take(p + "router.weight", (2, h)).to(rt.device, torch.float32)
+            self.w1 = [store.take(p + f"experts.{i}.w1", (e, h)).to(rt.device, torch.float32) for i in range(2)]
+            self.w2 = [store.take(p + f"experts.{i}.w2", (h, e)).to(rt.device, torch.float32) for i in range(2)]
+
+        def forward(self, ctx, x, residual):
+            xs = x[:ctx.T].float()
+            choice = (xs @ self.router.t()).argmax(dim=-1)      # router logits in fp32
+            for i in range(2):
+                rows = torch.nonzero(choice == i).flatten()
+                if rows.numel():
+                    Routed.used.add(i)
+                    residual[rows] += torch.relu(xs[rows] @ self.w1[i].t()) @ self.w2[i].t()
+
+    class LearnedPositions(PositionEncoding):
+        def weight_decls(self):
+            return [WeightDecl(self.prefix + "weight", (self.spec.max_positions, self.spec.hidden_size))]
+
+        def load(self, store, rt):
+            self.table = store.take(self.prefix + "weight", (self.spec.max_positions, self.spec.hidden_size)).to(
+                rt.device, torch.float32)
+
+        def on_embedding(self, ctx, h):
+            h[:ctx.T] += self.table[ctx.positions.long()]
+
+    return Routed, LearnedPositions
+
+
+def test_toy_routed_feed_forward_and_learned_positions():
+    """A feed-forward with routing and a position encoding on the embedding, both defined here, registered and
+    run through the engine's model, step function and cache: portions and mixed batches equal the whole, and
+    the whole equals a plain computation of the same model."""
+    from ember_b200 import StepEntry
+    from ember_b200.config import (AttentionSpec, GatedMLPSpec, LayerSpec, ModelSpec, NoPositionSpec, RMSNormSpec,
+                                   default_schedule)
+    from ember_b200.engine.runner import ModelRunner
+    from ember_b200.parts import register_part
+    from ember_b200.weights import WeightStore, random_tensors
+    Routed, LearnedPositions = make_toy_feed_forward_and_positions()
+    register_part("feed_forward", "toy_top1_of_2", Routed)
+    register_part("position", "toy_learned_positions", LearnedPositions)
+    H, V, P = 64, 200, 160
+    norm = RMSNormSpec(size=H, eps=1e-5)
+    attn = AttentionSpec(hidden_size=H, num_heads=2, num_kv_heads=2, head_dim=32, qk_norm=False, position=NoPositionSpec())
+    routed, dense = RoutedSpec(hidden_size=H, expert_size=40), GatedMLPSpec(hidden_size=H, intermediate_size=96)
+
+    def layer(i, ff):
+        p = f"toy.layers.{i}."
+        return LayerSpec(mixer=attn, feed_forward=ff, mixer_norm=norm, feed_forward_norm=norm, mixer_prefix=p + "attn.",
+                         feed_forward_prefix=p + "ff.", mixer_norm_prefix=p + "norm_a.", feed_forward_norm_prefix=p + "norm_b.")
+
+    spec = ModelSpec(architecture="ToyRoutedForCausalLM", vocab_size=V, hidden_size=H,
+                     layers=(layer(0, routed), layer(1, dense), layer(2, routed)),   # feed-forwards differ by layer
+                     schedule=default_schedule(3), final_norm=norm, final_norm_prefix="toy.norm.",
+                     embedding_name="toy.embed.weight", head_name="toy.head.weight", tie_embeddings=True, max_positions=P,
+                     embedding_position=LearnedPositionSpec(hidden_size=H, max_positions=P),
+                     embedding_position_prefix="toy.positions.", init_std=0.2)
+    weights = dict(random_tensors(spec, seed=9, dtype=torch.float32))
+    assert {"toy.positions.weight", "toy.layers.0.ff.router.weight", "toy.layers.2.ff.experts.1.w2",
+            "toy.layers.1.ff.gate_proj.weight"} <= set(weights)
+
+    rng = np.random.default_rng(17)
+    a, b = rng.integers(0, V, size=75).tolist(), rng.integers(0, V, size=31).tolist()
+    r = ModelRunner(spec, WeightStore.from_tensors(weights), dtype="float32", capacity_tokens=256, max_batch_tokens=128,
+                    max_requests=4)
+    r.admit("a"), r.reserve("a", 75)
+    whole = r.step([StepEntry("a", a, tuple(range(75)))]).cpu().clone()
+    r.release("a")
+    assert Routed.used == {0, 1}                                # both experts were chosen by some token
+    r.admit("b"), r.admit("a")
+    got, at, bt = [], 0, 0
+    for n, m in ((11, 4), (1, 1), (40, 20), (2, 1), (21, 5)):
+        r.reserve("a", n), r.reserve("b", m)
+        got.append(r.step([StepEntry("b", b[bt:bt + m], ()), StepEntry("a", a[at:at + n], tuple(range(n)))]).cpu().clone())
+        at, bt = at + n, bt + m
+    assert rel(torch.cat(got), whole) < 2e-5
+
+    # the same model, plainly: no rotation (the positions come from the table), full causal attention
+    w = {k: v.double() for k, v in weights.items()}
+    h = w["toy.embed.weight"][a] + w["toy.positions.weight"][:75]
+    for i, ff in enumerate((routed, dense, routed)):
+        p = f"toy.layers.{i}."
+        x = plain.rmsnorm(h, w[p + "norm_a.weight"], 1e-5)
+        q = (x @ w[p + "attn.q_proj.weight"].t()).view(75, 2, 32)
+        k = (x @ w[p + "attn.k_proj.weight"].t()).view(75, 2, 32)
+        v = (x @ w[p + "attn.v_proj.weight"].t()).view(75, 2, 32)
+        s = torch.einsum("thd,uhd->htu", q, k) / 32 ** 0.5
+        s = s.masked_fill(torch.triu(torch.ones(75, 75, dtype=torch.bool), 1), float("-inf"))
+        o = torch.einsum("htu,uhd->thd", torch.softmax(s, dim=-1), v).reshape(75, 64)
+        h = h + o @ w[p + "attn.o_proj.weight"].t()
+        x = plain.rmsnorm(h, w[p + "norm_b.weight"], 1e-5)
+        if ff is dense:
+            h = h + plain.swiglu(x, w[p + "ff.gate_proj.weight"], w[p + "ff.up_proj.weight"], w[p + "ff.down_proj.weight"])
+        else:
+            choice = (x.float() @ w[p + "ff.router.weight"].float().t()).argmax(dim=-1)
+            y = torch.zeros_like(h)
+            for e in range(2):
+                rows = choice == e
+                y[rows] = torch.relu(x[rows] @ w[p + f"ff.experts.{e}.w1"].t()) @ w[p + f"ff.experts.{e}.w2"].t()
+            h = h + y
+    want = plain.rmsnorm(h, w["toy.norm.weight"], 1e-5) @ w["toy.embed.weight"].t()
+    assert rel(whole, want) < 1e-4
