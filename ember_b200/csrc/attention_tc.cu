@@ -415,30 +415,53 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
     }
 }
 
-// Merges split partials in ascending order (same arithmetic as attention.cu's combine).
+// Merges split partials in ascending order (same arithmetic as attention.cu's combine).  The maxima and
+// denominators of a head are read once into shared memory, and the weights exp(m_s - M) are formed once, so
+// that a thread's loads of the partial sums are independent of one another (they were a chain of n_splits
+// dependent loads before, which is what the kernel's time was at batch 1 with 13 splits).
 __global__ void attention_tc_combine_kernel(const float* __restrict__ part_o, const float* __restrict__ part_ml,
                                             __nv_bfloat16* __restrict__ out, const int* __restrict__ tiles,
                                             int n_heads, int n_splits, int D) {
+    extern __shared__ float w_s[];                                         // [n_splits] weights, then 1 / L
+    float& inv_s = w_s[n_splits];
     pdl_launch_dependents();
     pdl_wait();
     const size_t th = blockIdx.x;                                          // tile * n_heads + head
     const int tile = (int)(th / n_heads), head = (int)(th % n_heads);
     const size_t oh = (size_t)tiles[tile * 4 + 1] * n_heads + head;        // the tile's single token row
     const float* ml = part_ml + th * n_splits * 2;
-    float M = -INFINITY;
-    for (int s = 0; s < n_splits; s++) M = fmaxf(M, ml[2 * s]);
-    float L = 0.0f;
-    for (int s = 0; s < n_splits; s++) {
-        const float ms = ml[2 * s];
-        if (ms != -INFINITY) L += ml[2 * s + 1] * expf(ms - M);
-    }
-    const float inv = L > 0.0f ? 1.0f / L : 0.0f;
-    for (int d = threadIdx.x; d < D; d += blockDim.x) {
-        float o = 0.0f;
-        for (int s = 0; s < n_splits; s++) {
-            const float ms = ml[2 * s];
-            if (ms != -INFINITY) o = fmaf(part_o[(th * n_splits + s) * D + d], expf(ms - M), o);
+    if (threadIdx.x < 32) {
+        // one warp: lanes take the splits (in rounds of 32), the sums run in ascending order of the split
+        float M = -INFINITY;
+        for (int s = threadIdx.x; s < n_splits; s += 32) M = fmaxf(M, ml[2 * s]);
+        M = warp_max(M);
+        float L = 0.0f;
+        for (int s0 = 0; s0 < n_splits; s0 += 32) {
+            const int s = s0 + (int)threadIdx.x;
+            float w = 0.0f, l = 0.0f;
+            if (s < n_splits) {
+                const float ms = ml[2 * s];
+                if (ms != -INFINITY) { w = expf(ms - M); l = ml[2 * s + 1] * w; }
+                w_s[s] = w;
+            }
+            for (int i = 0; i < 32 && s0 + i < n_splits; i++) L += __shfl_sync(0xffffffffu, l, i);   // ascending
         }
+        if (threadIdx.x == 0) inv_s = L > 0.0f ? 1.0f / L : 0.0f;
+    }
+    __syncthreads();
+    const float inv = inv_s;
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        const float* po = part_o + th * n_splits * D + d;
+        float o = 0.0f;
+        int s = 0;
+        for (; s + 4 <= n_splits; s += 4) {
+            const float a0 = po[(size_t)s * D], a1 = po[(size_t)(s + 1) * D], a2 = po[(size_t)(s + 2) * D], a3 = po[(size_t)(s + 3) * D];
+            o = fmaf(a0, w_s[s], o);
+            o = fmaf(a1, w_s[s + 1], o);
+            o = fmaf(a2, w_s[s + 2], o);
+            o = fmaf(a3, w_s[s + 3], o);
+        }
+        for (; s < n_splits; s++) o = fmaf(po[(size_t)s * D], w_s[s], o);
         out[oh * D + d] = __float2bfloat16_rn(o * inv);
     }
 }
@@ -517,7 +540,7 @@ EMBER_API int ember_attention_tc(const void* q, const void* k_pool, const void* 
     if (mode == 0 && n_splits != 1) return fail("attention_tc: prompt portions are not split");
     if (n_splits < 1 || (n_splits > 1 && (split_keys <= 0 || split_keys % KT || !part_o || !part_ml)))
         return fail("attention_tc: bad split configuration (%d splits of %d keys)", n_splits, split_keys);
-    if (n_splits > 65535 || n_kv > 65535) return fail("attention_tc: grid too large");
+    if (n_splits > 8192 || n_kv > 65535) return fail("attention_tc: grid too large");
     CUtensorMap mk, mv;
     const long long total_rows = (long long)num_pages * n_kv * page;
     if (!pool_map(k_pool, total_rows, D, page, &mk) || !pool_map(v_pool, total_rows, D, page, &mv))
@@ -545,7 +568,8 @@ EMBER_API int ember_attention_tc(const void* q, const void* k_pool, const void* 
     else rc = mode == 1 ? run(attention_tc_kernel<1, true>) : run(attention_tc_kernel<1, false>);
     if (rc) return rc;
     if (n_splits > 1) {
-        launch_kernel(attention_tc_combine_kernel, (unsigned)((size_t)n_tiles * n_heads), D, 0, st, (const float*)part_o,
+        launch_kernel(attention_tc_combine_kernel, (unsigned)((size_t)n_tiles * n_heads), D, (size_t)(n_splits + 1) * sizeof(float), st,
+                      (const float*)part_o,
                       (const float*)part_ml, (__nv_bfloat16*)out, tiles, n_heads, n_splits, D);
         return check_launch("attention_tc_combine");
     }
