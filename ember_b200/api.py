@@ -27,7 +27,7 @@ from .weights.random_init import random_tensors
 class LLM:
     """A loaded model with its engine."""
 
-    def __init__(self, runner: ModelRunner, max_prefill_chunk: int = 512, max_context: Optional[int] = None):
+    def __init__(self, runner: ModelRunner, max_prefill_chunk: int = 2048, max_context: Optional[int] = None):
         self.runner = runner
         self.engine = Engine(runner, max_prefill_chunk=max_prefill_chunk, max_context=max_context)
 
@@ -51,7 +51,7 @@ class LLM:
 
 
 def load(model: str, dtype: str = "bfloat16", device: str = "cuda:0", kv_cache_tokens: int = 0,
-         max_batch_tokens: int = 2048, max_seqs: int = 64, prefill_chunk: int = 512,
+         max_batch_tokens: int = 2048, max_seqs: int = 64, prefill_chunk: int = 2048,
          max_context: Optional[int] = None, page_tokens: int = 16, cuda_graphs: bool = True) -> LLM:
     """Loads a model folder (config.json + safetensors).  ``kv_cache_tokens`` 0 sizes the cache
     for ``max_seqs`` requests of the model's position limit, capped at 262,144 tokens."""
@@ -66,7 +66,7 @@ def load(model: str, dtype: str = "bfloat16", device: str = "cuda:0", kv_cache_t
 
 
 def load_random(config, seed: int = 0, dtype: str = "bfloat16", device: str = "cuda:0", kv_cache_tokens: int = 0,
-                max_batch_tokens: int = 2048, max_seqs: int = 64, prefill_chunk: int = 512,
+                max_batch_tokens: int = 2048, max_seqs: int = 64, prefill_chunk: int = 2048,
                 max_context: Optional[int] = None, page_tokens: int = 16, cuda_graphs: bool = True,
                 weight_dtype=torch.bfloat16,
                 std: Optional[float] = None, norm_std: Optional[float] = None) -> LLM:

@@ -179,7 +179,8 @@ EMBER_API int ember_gemm_tc(const void* A, const void* W, void* out, int ldc, in
     } else {
         // Prefill-sized products: the single-SM persistent kernel or pairs of SMs (tcgen05 cta_group::2),
         // each with the tile width that fills its waves best.  Under the power cap pairs are the more efficient
-        // kernel (an SM reads half of the weight tile) and win from about 4,096 tokens on.
+        // kernel (an SM reads half of the weight tile) and win from about 2,048 tokens on (a 2,048-token prefill
+        // step: 7.55 ms with pairs, 7.9 ms without; at 1,024 tokens the single-SM kernel is 1 % ahead).
         // split_mode 4 asks for pairs whenever the device takes them, 5 forbids them, 3 runs one tile per block.
         double cost_single = 0, cost_pair = 0;
         const int bc_single = split_mode == 3 ? (N >= 1024 ? 256 : 128) : best_block_cols(M, N, num_sms, 1, &cost_single);
@@ -187,7 +188,7 @@ EMBER_API int ember_gemm_tc(const void* A, const void* W, void* out, int ldc, in
             const int max_pairs = pair_capacity(num_sms);
             if (max_pairs > 0) {
                 const int bc_pair = best_block_cols(M, N, max_pairs, 2, &cost_pair);
-                if (split_mode == 4 || (M >= 4096 && cost_pair <= cost_single * 1.001)) {
+                if (split_mode == 4 || (M >= 2048 && cost_pair <= cost_single * 1.001)) {
                     p.epilogue = epilogue; p.out = out; p.ldc = ldc; p.err = err;
                     p.accum = nullptr; p.accum_ld = 0; p.rows_per = TILE_ROWS; p.stages = 0;
                     return launch_pair(A, W, p, bc_pair, max_pairs, st);
