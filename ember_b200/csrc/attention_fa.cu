@@ -37,8 +37,9 @@ namespace ember {
 constexpr int FA_ROWS = 128;          // query rows per block = TMEM lanes
 constexpr int FA_KT = 64;             // keys per tile
 constexpr int FA_D = 128;             // head size
-constexpr int FA_K_STAGES = 3;        // key tiles in flight or in use (a key tile is free once S = Q K^T has read it)
-constexpr int FA_V_STAGES = 2;        // value tiles (free once O += P V has read them)
+constexpr int FA_K_STAGES = 2;        // key tiles in flight or in use (a key tile is free once S = Q K^T has read it,
+                                      // two tiles before its values are: two stages look as far ahead as three of values)
+constexpr int FA_V_STAGES = 3;        // value tiles (free once O += P V has read them)
 constexpr int FA_THREADS = 192;
 constexpr unsigned FA_WAIT_LIMIT = 1u << 24;
 constexpr float FA_LOG2E = 1.4426950408889634f;
@@ -75,7 +76,17 @@ __device__ __forceinline__ bool fa_try_wait(uint64_t* bar, uint32_t parity) {
         : "=r"(ok) : "r"(fa_s32(bar)), "r"(parity) : "memory");
     return ok != 0;
 }
+__device__ __forceinline__ bool fa_test_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n}"
+        : "=r"(ok) : "r"(fa_s32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
 __device__ __forceinline__ bool fa_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+    if (fa_test_wait(bar, parity)) return true;      // a phase that is already over costs one look, not a suspended wait
     for (unsigned i = 0; i < FA_WAIT_LIMIT; i++) {
         if (fa_try_wait(bar, parity)) return true;
         if ((i & 1023u) == 1023u && *abort_flag) return false;
@@ -314,15 +325,21 @@ attention_fa_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
         if (lane == 0 && n_kt > 0) {
             const uint32_t idesc_s = fa_idesc(FA_KT, 0), idesc_o = fa_idesc(FA_D, 1);
             bool ok = fa_wait(q_ready, 0, abort_flag);
+            // operand descriptors are made once: the issuing thread is the critical path of a tile (every
+            // instruction it spends between two waits is time the softmax warps wait for S)
+            uint64_t dq[FA_D / 16];
+#pragma unroll
+            for (int kk = 0; kk < FA_D / 16; kk++) dq[kk] = fa_desc_k(q_s + (kk >> 2) * Q_HALF) + (uint64_t)(2 * (kk & 3));
+            const uint64_t dk0 = fa_desc_k(k_s), dv0 = fa_desc_mn(v_s, KV_HALF);      // stage b: + b * KV_TILE / 16
             auto issue_s = [&](int j) {
                 const int b = j % FA_K_STAGES;
                 const uint32_t d = tmem_s0 + (uint32_t)((j & 1) * FA_KT);
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
                 for (int kk = 0; kk < FA_D / 16; kk++) {
-                    const uint64_t da = fa_desc_k(q_s + (kk >> 2) * Q_HALF) + (uint64_t)(2 * (kk & 3));
-                    const uint64_t db = fa_desc_k(k_s + b * KV_TILE + (kk >> 2) * KV_HALF) + (uint64_t)(2 * (kk & 3));
-                    fa_mma(d, da, db, idesc_s, kk > 0 ? 1u : 0u);
+                    // second half of the head: KV_HALF bytes further; 16 elements: 32 bytes inside the swizzled row
+                    const uint64_t db = dk0 + (uint64_t)((b * KV_TILE + (kk >> 2) * KV_HALF) >> 4) + (uint64_t)(2 * (kk & 3));
+                    fa_mma(d, dq[kk], db, idesc_s, kk > 0 ? 1u : 0u);
                 }
                 fa_commit(&s_full[j & 1]);
                 fa_commit(&k_empty[b]);          // the keys of tile j are no longer read
@@ -348,7 +365,7 @@ attention_fa_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
                 for (int kk = 0; kk < FA_KT / 16; kk++) {
                     // P_j: 64 keys = 32 packed columns in the S buffer of tile j; 16 keys = 8 columns per step
                     const uint32_t pa = tmem_s0 + (uint32_t)((j & 1) * FA_KT + kk * 8);
-                    const uint64_t db = fa_desc_mn(v_s + b * KV_TILE, KV_HALF) + (uint64_t)((kk * 16 * 128) >> 4);
+                    const uint64_t db = dv0 + (uint64_t)((b * KV_TILE + kk * 16 * 128) >> 4);
                     fa_mma_ts(tmem_o, pa, db, idesc_o, (j > 0 || kk > 0) ? 1u : 0u);
                 }
                 fa_commit(&v_empty[b]);         // the values of tile j are no longer read
