@@ -239,6 +239,7 @@ def time_prefill(llm, tokens, reps, warmup):
 
 
 def main() -> int:
+    global PAGE_TOKENS
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=64)
@@ -252,9 +253,8 @@ def main() -> int:
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS,
                     help="with --only-prefill: another prompt length (the reported line stays at 2,048)")
     args = ap.parse_args()
-
-    global PAGE_TOKENS
     PAGE_TOKENS = args.page_tokens
+
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
                           "the reference is a C++/CMake program, not a Python package (pip: 'neither setup.py nor "
