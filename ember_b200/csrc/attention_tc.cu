@@ -92,7 +92,17 @@ __device__ __forceinline__ bool atc_try_wait(uint64_t* bar, uint32_t parity) {
         : "=r"(ok) : "r"(s32(bar)), "r"(parity) : "memory");
     return ok != 0;
 }
+__device__ __forceinline__ bool atc_test_wait(uint64_t* bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n}"
+        : "=r"(ok) : "r"(s32(bar)), "r"(parity) : "memory");
+    return ok != 0;
+}
 __device__ __forceinline__ bool atc_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+    if (atc_test_wait(bar, parity)) return true;      // a phase that is over costs one look, not a suspended wait
     for (unsigned i = 0; i < ATC_WAIT_LIMIT; i++) {
         if (atc_try_wait(bar, parity)) return true;
         if ((i & 1023u) == 1023u && *abort_flag) return false;
