@@ -48,6 +48,12 @@ class Qwen3Config:
     hidden_act: str = "silu"
     initializer_range: float = 0.02
     eos_token_ids: Tuple[int, ...] = ()
+    # config.json's use_sliding_window / sliding_window / max_window_layers: the first max_window_layers
+    # layers see all keys, the layers after them only the last sliding_window (their own position included).
+    # The reference has no such layers (it ignores the keys); here they are a second cache group.
+    use_sliding_window: bool = False
+    sliding_window: int = 0
+    max_window_layers: int = 0
 
     architecture = "Qwen3ForCausalLM"
     model_type = "qwen3"
@@ -66,8 +72,11 @@ class Qwen3Config:
         head_dim = _int(config, "head_dim", hidden // heads) if config.get("head_dim") is not None else hidden // heads
         if config.get("rope_scaling") is not None:
             raise ConfigError("rope_scaling is not supported")
-        if config.get("use_sliding_window"):
-            raise ConfigError("use_sliding_window=true is not supported for Qwen3ForCausalLM")
+        use_window = bool(config.get("use_sliding_window", False))
+        window = _int(config, "sliding_window", 0) if config.get("sliding_window") is not None else 0
+        window_from = _int(config, "max_window_layers", 0) if config.get("max_window_layers") is not None else 0
+        if use_window and window <= 0:
+            raise ConfigError("use_sliding_window=true needs a positive sliding_window")
         act = config.get("hidden_act", "silu")
         if act != "silu":
             raise ConfigError(f"hidden_act {act!r} is not supported (silu only)")
@@ -100,6 +109,9 @@ class Qwen3Config:
             hidden_act=act,
             initializer_range=float(config.get("initializer_range") or 0.02),
             eos_token_ids=eos_ids,
+            use_sliding_window=use_window,
+            sliding_window=window if use_window else 0,
+            max_window_layers=max(0, window_from) if use_window else 0,
         )
         out.validate()
         return out
@@ -166,22 +178,31 @@ class Qwen3Config:
         }
         if self.eos_token_ids:
             d["eos_token_id"] = list(self.eos_token_ids) if len(self.eos_token_ids) > 1 else self.eos_token_ids[0]
+        if self.use_sliding_window:
+            d.update(use_sliding_window=True, sliding_window=self.sliding_window, max_window_layers=self.max_window_layers)
         return d
+
+    def layer_window(self, layer: int) -> int:
+        """Keys a query of this layer sees (its own included); 0 = all."""
+        return self.sliding_window if self.use_sliding_window and layer >= self.max_window_layers else 0
 
     # --------------------------------------------------------------- as a model
     def to_model_spec(self) -> ModelSpec:
-        """Pre-norm decoder, L identical layers (cpu_backend.cpp:139-213), final norm,
-        tied or untied head (cpu_backend.cpp:51-53)."""
+        """Pre-norm decoder, L layers that differ at most in their window (cpu_backend.cpp:139-213), final
+        norm, tied or untied head (cpu_backend.cpp:51-53)."""
         rope = RotarySpec(head_dim=self.head_dim, rotary_dim=self.head_dim, theta=self.rope_theta)
-        attn = AttentionSpec(hidden_size=self.hidden_size, num_heads=self.num_attention_heads,
-                             num_kv_heads=self.num_key_value_heads, head_dim=self.head_dim,
-                             qk_norm=True, qk_norm_eps=self.rms_norm_eps, bias=self.attention_bias,
-                             window=0, softmax_scale=None, position=rope)
+
+        def attn(layer: int) -> AttentionSpec:
+            return AttentionSpec(hidden_size=self.hidden_size, num_heads=self.num_attention_heads,
+                                 num_kv_heads=self.num_key_value_heads, head_dim=self.head_dim,
+                                 qk_norm=True, qk_norm_eps=self.rms_norm_eps, bias=self.attention_bias,
+                                 window=self.layer_window(layer), softmax_scale=None, position=rope)
+
         mlp = GatedMLPSpec(hidden_size=self.hidden_size, intermediate_size=self.intermediate_size,
                            activation=self.hidden_act)
         norm = RMSNormSpec(size=self.hidden_size, eps=self.rms_norm_eps)
         layers = tuple(
-            LayerSpec(mixer=attn, feed_forward=mlp, mixer_norm=norm, feed_forward_norm=norm,
+            LayerSpec(mixer=attn(i), feed_forward=mlp, mixer_norm=norm, feed_forward_norm=norm,
                       mixer_prefix=f"model.layers.{i}.self_attn.", feed_forward_prefix=f"model.layers.{i}.mlp.",
                       mixer_norm_prefix=f"model.layers.{i}.input_layernorm.",
                       feed_forward_norm_prefix=f"model.layers.{i}.post_attention_layernorm.",

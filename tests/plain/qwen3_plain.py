@@ -33,6 +33,10 @@ def read_config(model_dir: str) -> dict:
         "theta": c.get("rope_theta", 10000.0) if c.get("rope_theta") is not None else 10000.0,
         "tie": bool(c.get("tie_word_embeddings", False)),
         "bias": bool(c.get("attention_bias", False)),
+        # not in the reference (it ignores these keys): the layers from max_window_layers on see only the last
+        # sliding_window keys, their own position included
+        "window": int(c.get("sliding_window") or 0) if c.get("use_sliding_window") else 0,
+        "window_from": int(c.get("max_window_layers") or 0),
     }
 
 
@@ -162,7 +166,8 @@ class PlainQwen3:
         for l in range(c["layers"]):
             p = f"model.layers.{l}."
             x = rmsnorm(h, w[p + "input_layernorm.weight"], c["eps"])
-            h = h + attention_block(x, w, p + "self_attn.", c, pos, self.inv_freq)
+            window = c["window"] if l >= c["window_from"] else 0
+            h = h + attention_block(x, w, p + "self_attn.", c, pos, self.inv_freq, window=window)
             x = rmsnorm(h, w[p + "post_attention_layernorm.weight"], c["eps"])
             h = h + swiglu(x, w[p + "mlp.gate_proj.weight"], w[p + "mlp.up_proj.weight"], w[p + "mlp.down_proj.weight"])
             out.append(h)

@@ -5,7 +5,7 @@ import pytest
 
 from ember_b200.config import (AttentionSpec, ConfigError, Qwen3Config, RMSNormSpec, RotarySpec, config_from_dict,
                                load_config, registered_architectures)
-from tests.tiny_configs import TINY
+from tests.tiny_configs import TINY, tiny_config
 
 
 def test_keys_defaults_and_derived():
@@ -74,3 +74,19 @@ def test_round_trip_and_parameter_count():
                                      head_dim=128, tie_word_embeddings=True))
     assert abs(big.parameters() / 1e9 - 1.72) < 0.01
     assert big.kv_bytes_per_token(2) == 114688
+
+
+def test_sliding_window_keys_give_layers_of_two_kinds():
+    """use_sliding_window / sliding_window / max_window_layers: the first layers see all keys, the rest a window;
+    the model then needs two cache groups.  Without use_sliding_window the other two keys mean nothing."""
+    from ember_b200.cache import CacheManager
+    from ember_b200.model.causal_lm import CausalLM
+    cfg = tiny_config("f")
+    assert [cfg.layer_window(i) for i in range(3)] == [0, 24, 24]
+    spec = cfg.to_model_spec()
+    assert [l.mixer.window for l in spec.layers] == [0, 24, 24]
+    assert Qwen3Config.from_json(cfg.to_json()) == cfg
+    groups = CacheManager(CausalLM(spec).cache_needs(), 16, 256, 4).groups
+    assert [(g.need.kind, g.layers) for g in groups] == [("full", [0]), ("window", [1, 2])]
+    d = dict(TINY["f"]["json"], use_sliding_window=False)
+    assert [l.mixer.window for l in Qwen3Config.from_json(d).to_model_spec().layers] == [0, 0, 0]

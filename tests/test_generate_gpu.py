@@ -29,7 +29,7 @@ def test_greedy_generation_float32_equals_plain(name, tiny_model_dirs):
     for p, o in zip(prompts, outs):
         assert o == plain.greedy(p, 16)
     assert llm.generate(prompts[-1], max_tokens=16, ignore_eos=True) == outs[-1]  # alone: the same tokens
-    assert llm.runner.cache.used_pages() == [0]
+    assert not any(llm.runner.cache.used_pages())          # one count per cache group
 
 
 def test_greedy_generation_bfloat16_follows_plain_logits(tiny_model_dirs):

@@ -61,7 +61,7 @@ def replay(model_dir, dtype, steps, capacity):
 
 
 LENGTHS = {"a": (5, 17, 33, 100), "b": (1, 31, 64, 100, 130), "c": (3, 70, 200, 333), "d": (2, 65, 129, 260),
-           "e": (4, 47, 97, 150)}
+           "e": (4, 47, 97, 150), "f": (3, 24, 25, 77, 160)}
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

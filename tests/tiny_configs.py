@@ -1,7 +1,7 @@
 """The tests' own tiny Qwen3 configurations.  They differ in every size and option: layers,
 width, heads and groups, head size, projection width vs model width, feed-forward width,
 vocabulary (one a power of two, one not), rope theta, norm eps, tied vs untied head, initial
-scales, position limit."""
+scales, position limit, biases, a sliding window on some of the layers."""
 from __future__ import annotations
 
 import numpy as np
@@ -38,6 +38,14 @@ TINY = {
                         intermediate_size=150, num_hidden_layers=2, num_attention_heads=5, num_key_value_heads=5,
                         head_dim=48, rope_theta=50000.0, rms_norm_eps=1e-6, tie_word_embeddings=True,
                         max_position_embeddings=300, attention_bias=True)),
+    # layers that differ: the first sees all keys, the two after it a window of 24 (two cache groups; window pages
+    # are given back while a request runs); head size 64 with a group of 2
+    "f": dict(seed=43, std=0.05, norm_std=0.1,
+              json=dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_size=450, hidden_size=128,
+                        intermediate_size=176, num_hidden_layers=3, num_attention_heads=4, num_key_value_heads=2,
+                        head_dim=64, rope_theta=10000.0, rms_norm_eps=1e-6, tie_word_embeddings=True,
+                        max_position_embeddings=400, attention_bias=False, use_sliding_window=True, sliding_window=24,
+                        max_window_layers=1)),
 }
 GOLDEN_CONFIGS = ("a", "b")          # the ones the reference's CPU backend was run on
 
