@@ -1,4 +1,4 @@
-// Sorting-free sampling, one block per logits row.
+// Sorting-free sampling: a logits row is shared by a cluster of eight blocks (one block for small vocabularies).
 //
 // Semantics (src/backend/sampling_host.cpp:20-85, src/backend/sampling_rng.hpp:21-33):
 //   temperature <= 1e-5: argmax, lowest index on ties.
@@ -50,22 +50,53 @@ __device__ __forceinline__ unsigned float_key(float x) {
     return (b & 0x80000000u) ? ~b : (b | 0x80000000u);
 }
 
+// A row is shared by a cluster of CL blocks (CL = 1: one block, no cluster).  Block r scans the r-th
+// contiguous part of the row; whatever the single-block algorithm reduces over the block is reduced over the
+// cluster through the first block's shared memory (distributed shared memory), in rank order, so that every
+// block holds the same values and takes the same branches.
 struct Shared {
     unsigned count[256];
     double mass[256];
     float red_f[32];
     int red_i[32];
     double red_d[32];
+    int warp_counts[32];
+    // written by the blocks of the cluster into the first block's copy, read back by all
+    float x_f[16];
+    int x_i[16];
+    double x_d[16];
     unsigned prefix, select_mask;   // key bits fixed so far
     unsigned long long remaining_k;
     double remaining_mass;
-    int warp_counts[32];
     int found;
 };
 
-__device__ float block_max_arg(float v, int idx, int* arg_out, Shared& sh) {
-    // max value, lowest index among equals
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+__device__ __forceinline__ unsigned cl_rank() { unsigned r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
+template <int CL>
+__device__ __forceinline__ void cl_sync() {
+    if constexpr (CL > 1) {
+        asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+        asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+    } else {
+        __syncthreads();
+    }
+}
+// The same object in block `rank` of the cluster.
+template <int CL, typename T>
+__device__ __forceinline__ T* cl_peer(T* local, unsigned rank) {
+    if constexpr (CL > 1) {
+        unsigned long long out;
+        asm volatile("mapa.u64 %0, %1, %2;" : "=l"(out) : "l"((unsigned long long)local), "r"(rank));
+        return (T*)out;
+    } else {
+        return local;
+    }
+}
+
+// max value, lowest index among equals: over the block, then over the cluster
+template <int CL>
+__device__ float cluster_max_arg(float v, int idx, int* arg_out, Shared& sh) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
         const float ov = __shfl_xor_sync(0xffffffffu, v, o);
@@ -76,92 +107,198 @@ __device__ float block_max_arg(float v, int idx, int* arg_out, Shared& sh) {
     if (lane == 0) { sh.red_f[warp] = v; sh.red_i[warp] = idx; }
     __syncthreads();
     if (warp == 0) {
-        v = sh.red_f[lane];
-        idx = sh.red_i[lane];
+        v = lane < nwarps ? sh.red_f[lane] : -INFINITY;
+        idx = lane < nwarps ? sh.red_i[lane] : 0x7fffffff;
 #pragma unroll
         for (int o = 16; o > 0; o >>= 1) {
             const float ov = __shfl_xor_sync(0xffffffffu, v, o);
             const int oi = __shfl_xor_sync(0xffffffffu, idx, o);
             if (ov > v || (ov == v && oi < idx)) { v = ov; idx = oi; }
         }
-        if (lane == 0) { sh.red_f[0] = v; sh.red_i[0] = idx; }
+        if (lane == 0) {
+            Shared* first = cl_peer<CL>(&sh, 0);
+            const unsigned r = CL > 1 ? cl_rank() : 0;
+            first->x_f[r] = v;
+            first->x_i[r] = idx;
+        }
     }
-    __syncthreads();
-    *arg_out = sh.red_i[0];
-    return sh.red_f[0];
+    cl_sync<CL>();
+    Shared* first = cl_peer<CL>(&sh, 0);
+    float bv = first->x_f[0];
+    int bi = first->x_i[0];
+#pragma unroll
+    for (int r = 1; r < CL; r++) {
+        const float ov = first->x_f[r];
+        const int oi = first->x_i[r];
+        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    cl_sync<CL>();                      // everybody has read before the slots are written again
+    *arg_out = bi;
+    return bv;
 }
 
-__device__ double block_sum_double(double v, Shared& sh) {
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+template <int CL>
+__device__ double cluster_sum_double(double v, Shared& sh) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
     __syncthreads();
     if (lane == 0) sh.red_d[warp] = v;
     __syncthreads();
-    double r = sh.red_d[lane];
+    if (warp == 0) {
+        double r = lane < nwarps ? sh.red_d[lane] : 0.0;
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) r += __shfl_xor_sync(0xffffffffu, r, o);
-    return r;
+        for (int o = 16; o > 0; o >>= 1) r += __shfl_xor_sync(0xffffffffu, r, o);
+        if (lane == 0) cl_peer<CL>(&sh, 0)->x_d[CL > 1 ? cl_rank() : 0] = r;
+    }
+    cl_sync<CL>();
+    Shared* first = cl_peer<CL>(&sh, 0);
+    double total = 0.0;
+#pragma unroll
+    for (int r = 0; r < CL; r++) total += first->x_d[r];
+    cl_sync<CL>();
+    return total;
+}
+
+// After every block has filled its count[] (and mass[]): the first block's thread 0 gets the sums over the
+// cluster in its own arrays.  Ends with a cluster barrier; the caller's decision step follows.
+template <int CL, bool MASS>
+__device__ void cluster_merge_bins(Shared& sh) {
+    cl_sync<CL>();
+    if constexpr (CL > 1) {
+        if (cl_rank() == 0 && threadIdx.x < 256) {
+            // the peers' bins are fetched together (independent loads), then added in rank order
+            unsigned pc[CL];
+            double pm[CL];
+#pragma unroll
+            for (unsigned r = 1; r < CL; r++) {
+                Shared* peer = cl_peer<CL>(&sh, r);
+                pc[r] = peer->count[threadIdx.x];
+                pm[r] = MASS ? peer->mass[threadIdx.x] : 0.0;
+            }
+            unsigned c = sh.count[threadIdx.x];
+            double m = MASS ? sh.mass[threadIdx.x] : 0.0;
+#pragma unroll
+            for (unsigned r = 1; r < CL; r++) {
+                c += pc[r];
+                if (MASS) m += pm[r];
+            }
+            sh.count[threadIdx.x] = c;
+            if (MASS) sh.mass[threadIdx.x] = m;
+        }
+        __syncthreads();
+    }
+}
+// The first block's decision (prefix, mask, remaining) copied into every block.
+template <int CL>
+__device__ void cluster_share_decision(Shared& sh) {
+    cl_sync<CL>();
+    if constexpr (CL > 1) {
+        if (cl_rank() != 0 && threadIdx.x == 0) {
+            Shared* first = cl_peer<CL>(&sh, 0);
+            sh.prefix = first->prefix;
+            sh.select_mask = first->select_mask;
+            sh.remaining_k = first->remaining_k;
+            sh.remaining_mass = first->remaining_mass;
+        }
+        cl_sync<CL>();                  // the first block may overwrite its bins and decision again
+    }
 }
 
 // Index of the n-th (1-based) element, in index order, whose key equals `key` and passes `pred`.
-// Returns V if there are fewer than n.
-template <typename Pred>
-__device__ int nth_equal_index(const float* __restrict__ logits, float inv_t_div, int V, unsigned key, int n, Pred pred,
-                               Shared& sh) {
-    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
-    int seen = 0;
-    __syncthreads();
-    if (threadIdx.x == 0) sh.found = V;
-    __syncthreads();
-    for (int base = 0; base < V; base += SAMPLE_THREADS) {
-        const int i = base + threadIdx.x;
-        bool hit = false;
-        if (i < V) {
-            const float x = logits[i] / inv_t_div;
-            hit = float_key(x) == key && pred(i, x);
-        }
-        const unsigned ballot = __ballot_sync(0xffffffffu, hit);
-        if (lane == 0) sh.warp_counts[warp] = __popc(ballot);
-        __syncthreads();
-        int before = 0, total = 0;
-        for (int w = 0; w < SAMPLE_THREADS / 32; w++) {
-            const int c = sh.warp_counts[w];
-            if (w < warp) before += c;
-            total += c;
-        }
-        const int rank = seen + before + __popc(ballot & ((1u << lane) - 1u)) + 1;  // 1-based if hit
-        if (hit && rank == n) sh.found = i;
-        seen += total;
-        __syncthreads();
-        if (seen >= n) break;
+// Returns V if there are fewer than n.  [lo, hi) is this block's part of the row.
+template <int CL, typename Pred>
+__device__ int nth_equal_index(const float* __restrict__ logits, float inv_t_div, int V, int lo, int hi, unsigned key, int n,
+                               Pred pred, Shared& sh) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nwarps = blockDim.x >> 5;
+    // hits of this block, then of every block (in rank order)
+    int mine = 0;
+    for (int i = lo + (int)threadIdx.x; i < hi; i += blockDim.x) {
+        const float x = logits[i] / inv_t_div;
+        mine += (float_key(x) == key && pred(i, x)) ? 1 : 0;
     }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) mine += __shfl_xor_sync(0xffffffffu, mine, o);
     __syncthreads();
-    return sh.found;
+    if (lane == 0) sh.red_i[warp] = mine;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        int total = 0;
+        for (int w = 0; w < nwarps; w++) total += sh.red_i[w];
+        Shared* first = cl_peer<CL>(&sh, 0);
+        const unsigned r = CL > 1 ? cl_rank() : 0;
+        first->x_i[r] = total;
+        if (r == 0) first->found = V;
+    }
+    cl_sync<CL>();
+    Shared* first = cl_peer<CL>(&sh, 0);
+    const unsigned me = CL > 1 ? cl_rank() : 0;
+    int before_me = 0, my_total = 0;
+#pragma unroll
+    for (unsigned r = 0; r < (unsigned)CL; r++) {
+        const int c = first->x_i[r];
+        if (r < me) before_me += c;
+        if (r == me) my_total = c;
+    }
+    if (before_me < n && n <= before_me + my_total) {        // uniform over the block: the n-th lies in this part
+        const int want = n - before_me;
+        int seen = 0;
+        for (int base = lo; base < hi; base += blockDim.x) {
+            const int i = base + (int)threadIdx.x;
+            bool hit = false;
+            if (i < hi) {
+                const float x = logits[i] / inv_t_div;
+                hit = float_key(x) == key && pred(i, x);
+            }
+            const unsigned ballot = __ballot_sync(0xffffffffu, hit);
+            if (lane == 0) sh.warp_counts[warp] = __popc(ballot);
+            __syncthreads();
+            int before = 0, total = 0;
+            for (int w = 0; w < nwarps; w++) {
+                const int c = sh.warp_counts[w];
+                if (w < warp) before += c;
+                total += c;
+            }
+            const int rank = seen + before + __popc(ballot & ((1u << lane) - 1u)) + 1;  // 1-based if hit
+            if (hit && rank == want) first->found = i;
+            seen += total;
+            __syncthreads();
+            if (seen >= want) break;
+        }
+    }
+    cl_sync<CL>();
+    const int found = first->found;
+    cl_sync<CL>();
+    return found;
 }
 
+template <int CL>
 __global__ void __launch_bounds__(SAMPLE_THREADS)
 sample_kernel(const float* __restrict__ logits_all, int V, const SampleParams* __restrict__ params,
               int* __restrict__ out) {
     __shared__ Shared sh;
-    const int row = blockIdx.x;
+    const int row = blockIdx.x / CL;
+    const unsigned rank = CL > 1 ? cl_rank() : 0;
     const float* logits = logits_all + (size_t)row * V;
     const SampleParams p = params[row];
     const int tid = threadIdx.x;
+    // this block's part of the row: contiguous, so that "in index order" holds across the cluster in rank order
+    const int per = (V + CL - 1) / CL;
+    const int lo = min(V, (int)rank * per), hi = min(V, lo + per);
 
     // ---- greedy, and the maximum for everything else
     const bool greedy = p.temperature <= 1e-5f;
     const float tdiv = greedy ? 1.0f : p.temperature;
     float best = -INFINITY;
     int best_i = 0x7fffffff;
-    for (int i = tid; i < V; i += SAMPLE_THREADS) {
+    for (int i = lo + tid; i < hi; i += SAMPLE_THREADS) {
         const float x = logits[i] / tdiv;
         if (x > best) { best = x; best_i = i; }   // ascending i: the first maximum stays
     }
     int arg;
-    const float xmax = block_max_arg(best, best_i, &arg, sh);
+    const float xmax = cluster_max_arg<CL>(best, best_i, &arg, sh);
     if (greedy) {
-        if (tid == 0) out[row] = arg;
+        if (tid == 0 && rank == 0) out[row] = arg;
         return;
     }
 
@@ -176,50 +313,71 @@ sample_kernel(const float* __restrict__ logits_all, int V, const SampleParams* _
             if (tid < 256) sh.count[tid] = 0;
             __syncthreads();
             const unsigned prefix = sh.prefix, mask = sh.select_mask;
-            for (int i = tid; i < V; i += SAMPLE_THREADS) {
+            for (int i = lo + tid; i < hi; i += SAMPLE_THREADS) {
                 const unsigned key = float_key(logits[i] / tdiv);
                 if ((key & mask) == prefix) atomicAdd(&sh.count[(key >> shift) & 255u], 1u);
             }
             __syncthreads();
-            if (tid == 0) {
-                unsigned long long rem = sh.remaining_k;
-                int b = 255;
-                for (; b > 0; b--) {
-                    if (sh.count[b] >= rem) break;
-                    rem -= sh.count[b];
+            cluster_merge_bins<CL, false>(sh);
+            if (rank == 0 && tid < 256) {
+                // the bin of the k-th largest: walking down from bin 255, the first bin (above 0) at which the
+                // running count reaches what is still wanted, else bin 0.  Done by 256 threads: thread b holds
+                // the count of bins b..255 (a suffix sum over eight warps).
+                const int lane = tid & 31, warp = tid >> 5;
+                const unsigned own = sh.count[tid];
+                unsigned suf = own;                                 // within the warp: bins tid .. warp end
+#pragma unroll
+                for (int o = 1; o < 32; o <<= 1) {
+                    const unsigned v = __shfl_down_sync(0xffffffffu, suf, o);
+                    if (lane + o < 32) suf += v;
                 }
-                sh.remaining_k = rem;               // how many of bin b (with the prefix) are still wanted
-                sh.prefix = prefix | ((unsigned)b << shift);
-                sh.select_mask = mask | (255u << shift);
+                if (lane == 0) sh.warp_counts[warp] = (int)suf;     // total of this warp's 32 bins
+                asm volatile("bar.sync 1, 256;" ::: "memory");
+                unsigned above = 0;                                 // bins of the warps above this one
+                for (int w = warp + 1; w < 8; w++) above += (unsigned)sh.warp_counts[w];
+                const unsigned long long rem = sh.remaining_k;
+                const unsigned long long s_b = (unsigned long long)suf + above;     // count of bins tid..255
+                const unsigned long long s_next = s_b - own;                        // count of bins tid+1..255
+                const bool here = tid > 0 && s_b >= rem && s_next < rem;
+                const unsigned any = __ballot_sync(0xffffffffu, here);
+                if (lane == 0) sh.red_i[warp] = (int)any;
+                asm volatile("bar.sync 1, 256;" ::: "memory");
+                bool found = false;
+                for (int w = 0; w < 8; w++) found |= sh.red_i[w] != 0;
+                if (here || (!found && tid == 0)) {
+                    sh.remaining_k = rem - s_next;      // how many of this bin (with the prefix) are still wanted
+                    sh.prefix = prefix | ((unsigned)tid << shift);
+                    sh.select_mask = mask | (255u << shift);
+                }
             }
+            cluster_share_decision<CL>(sh);
             __syncthreads();
         }
         k_key = sh.prefix;
         const int need_eq = (int)sh.remaining_k;   // of the values equal to the k-th, the lowest need_eq indices
-        k_cut = nth_equal_index(logits, tdiv, V, k_key, need_eq, [](int, float) { return true; }, sh);
+        k_cut = nth_equal_index<CL>(logits, tdiv, V, lo, hi, k_key, need_eq, [](int, float) { return true; }, sh);
     }
     auto kept_k = [&](int i, unsigned key) { return !use_k || key > k_key || (key == k_key && i <= k_cut); };
-
-    // ---- mass of the kept set
-    double z_local = 0.0;
-    for (int i = tid; i < V; i += SAMPLE_THREADS) {
-        const float x = logits[i] / tdiv;
-        if (kept_k(i, float_key(x))) z_local += exp((double)x - (double)xmax);
-    }
-    const double Z = block_sum_double(z_local, sh);
 
     // ---- top-p: the smallest prefix (value descending, index ascending) whose mass reaches top_p * Z
     unsigned p_key = 0;
     int p_cut = V;
     const bool use_p = p.top_p < 1.0f;
     if (use_p) {
+        // mass of the kept set (nothing else needs it)
+        double z_local = 0.0;
+        for (int i = lo + tid; i < hi; i += SAMPLE_THREADS) {
+            const float x = logits[i] / tdiv;
+            if (kept_k(i, float_key(x))) z_local += exp((double)x - (double)xmax);
+        }
+        const double Z = cluster_sum_double<CL>(z_local, sh);
         if (tid == 0) { sh.prefix = 0; sh.select_mask = 0; sh.remaining_mass = (double)p.top_p * Z; }
         for (int pass = 0; pass < 4; pass++) {
             const int shift = 24 - 8 * pass;
             if (tid < 256) { sh.mass[tid] = 0.0; sh.count[tid] = 0; }
             __syncthreads();
             const unsigned prefix = sh.prefix, mask = sh.select_mask;
-            for (int i = tid; i < V; i += SAMPLE_THREADS) {
+            for (int i = lo + tid; i < hi; i += SAMPLE_THREADS) {
                 const float x = logits[i] / tdiv;
                 const unsigned key = float_key(x);
                 if ((key & mask) == prefix && kept_k(i, key)) {
@@ -228,7 +386,8 @@ sample_kernel(const float* __restrict__ logits_all, int V, const SampleParams* _
                 }
             }
             __syncthreads();
-            if (tid == 0) {
+            cluster_merge_bins<CL, true>(sh);
+            if (tid == 0 && rank == 0) {
                 double rem = sh.remaining_mass;
                 int b = 255;
                 for (; b > 0; b--) {
@@ -243,6 +402,7 @@ sample_kernel(const float* __restrict__ logits_all, int V, const SampleParams* _
                 sh.prefix = prefix | ((unsigned)b << shift);
                 sh.select_mask = mask | (255u << shift);
             }
+            cluster_share_decision<CL>(sh);
             __syncthreads();
         }
         p_key = sh.prefix;
@@ -252,15 +412,15 @@ sample_kernel(const float* __restrict__ logits_all, int V, const SampleParams* _
         double need = ceil(sh.remaining_mass / e);
         if (!(need >= 1.0)) need = 1.0;
         const int need_eq = need > 2147483000.0 ? 2147483000 : (int)need;
-        p_cut = nth_equal_index(logits, tdiv, V, p_key, need_eq,
-                                [&](int i, float x) { return kept_k(i, float_key(x)); }, sh);
+        p_cut = nth_equal_index<CL>(logits, tdiv, V, lo, hi, p_key, need_eq,
+                                    [&](int i, float x) { return kept_k(i, float_key(x)); }, sh);
     }
 
     // ---- min-p and the draw
     const double floor_p = p.min_p > 0.0f ? (double)p.min_p : -1.0;
     float best_s = -INFINITY;
     int best_t = 0x7fffffff;
-    for (int i = tid; i < V; i += SAMPLE_THREADS) {
+    for (int i = lo + tid; i < hi; i += SAMPLE_THREADS) {
         const float x = logits[i] / tdiv;
         const unsigned key = float_key(x);
         bool keep = kept_k(i, key);
@@ -271,8 +431,8 @@ sample_kernel(const float* __restrict__ logits_all, int V, const SampleParams* _
         if (s > best_s) { best_s = s; best_t = i; }
     }
     int tok;
-    block_max_arg(best_s, best_t, &tok, sh);
-    if (tid == 0) out[row] = tok == 0x7fffffff ? arg : tok;
+    cluster_max_arg<CL>(best_s, best_t, &tok, sh);
+    if (tid == 0 && rank == 0) out[row] = tok == 0x7fffffff ? arg : tok;
 }
 
 // ---- greedy rows only: argmax in two steps so that many blocks share a row
@@ -342,6 +502,22 @@ EMBER_API int ember_sample(const float* logits, int rows, int V, const void* par
     if (rows <= 0) return 0;
     if (V <= 0) return fail("sample: vocabulary %d", V);
     static_assert(sizeof(SampleParams) == 32, "parameter rows are 32 bytes");
-    sample_kernel<<<rows, SAMPLE_THREADS, 0, (cudaStream_t)stream>>>(logits, V, (const SampleParams*)params, out);
+    // A row is shared by a cluster of 8 blocks (one block alone spends 0.2-2 ms on a vocabulary of 150,000: its
+    // passes are instruction-bound on one SM); small vocabularies stay with one block.
+    constexpr int CL = 8;
+    if (V >= 8192) {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3((unsigned)rows * CL);
+        cfg.blockDim = dim3(SAMPLE_THREADS);
+        cfg.stream = (cudaStream_t)stream;
+        cudaLaunchAttribute attr[1];
+        attr[0].id = cudaLaunchAttributeClusterDimension;
+        attr[0].val.clusterDim.x = CL; attr[0].val.clusterDim.y = 1; attr[0].val.clusterDim.z = 1;
+        cfg.attrs = attr; cfg.numAttrs = 1;
+        if (cudaLaunchKernelEx(&cfg, sample_kernel<CL>, logits, V, (const SampleParams*)params, out) == cudaSuccess)
+            return check_launch("sample");
+        cudaGetLastError();                     // clusters of 8 not available: one block per row
+    }
+    sample_kernel<1><<<rows, SAMPLE_THREADS, 0, (cudaStream_t)stream>>>(logits, V, (const SampleParams*)params, out);
     return check_launch("sample");
 }

@@ -18,7 +18,7 @@ def pack_params(params: Sequence[SamplingParams], counters: Sequence[int]) -> np
     for i, (p, c) in enumerate(zip(params, counters)):
         _ROW.pack_into(buf, i * _ROW.size, float(p.temperature), int(p.top_k), float(p.top_p), float(p.min_p),
                        int(p.seed) & ((1 << 64) - 1), int(c) & ((1 << 64) - 1))
-    return np.frombuffer(bytes(buf), dtype=np.uint8)
+    return np.frombuffer(buf, dtype=np.uint8)          # a view of the bytearray: writable
 
 
 _scratch = {}
@@ -31,6 +31,27 @@ def _argmax_scratch(device, rows: int):
         got = (torch.empty(n, dtype=torch.float32, device=device), torch.empty(n, dtype=torch.int32, device=device))
         _scratch[device] = got
     return got
+
+
+_staging = {}
+
+
+def _param_staging(device, nbytes: int):
+    """Pinned and device buffers for the parameter rows, from a ring of four (pinning memory per call costs more
+    than the kernel); a slot is taken again only after the copy out of it has run."""
+    ring = _staging.setdefault(device, {"at": 0, "slots": []})
+    if len(ring["slots"]) < 4:
+        n = max(nbytes, 64 * _ROW.size)
+        ring["slots"].append([torch.empty(n, dtype=torch.uint8, pin_memory=True),
+                              torch.empty(n, dtype=torch.uint8, device=device), torch.cuda.Event()])
+        return ring["slots"][-1]
+    ring["at"] = (ring["at"] + 1) % 4
+    slot = ring["slots"][ring["at"]]
+    slot[2].synchronize()
+    if slot[0].numel() < nbytes:
+        slot[0] = torch.empty(nbytes, dtype=torch.uint8, pin_memory=True)
+        slot[1] = torch.empty(nbytes, dtype=torch.uint8, device=device)
+    return slot
 
 
 def sample(logits: torch.Tensor, params: Sequence[SamplingParams], counters: Sequence[int],
@@ -46,7 +67,9 @@ def sample(logits: torch.Tensor, params: Sequence[SamplingParams], counters: Seq
         part_v, part_i = _argmax_scratch(logits.device, rows)
         ops.argmax(logits, out, rows, part_v, part_i)
         return out
-    host = torch.from_numpy(pack_params(params, counters).copy()).pin_memory()
-    dev = host.to(logits.device, non_blocking=True)
+    host, dev, event = _param_staging(logits.device, rows * _ROW.size)
+    host[:rows * _ROW.size].copy_(torch.from_numpy(pack_params(params, counters)))
+    dev[:rows * _ROW.size].copy_(host[:rows * _ROW.size], non_blocking=True)
+    event.record()
     ops.sample(logits, dev, out, rows)
     return out
