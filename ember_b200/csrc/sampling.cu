@@ -21,6 +21,7 @@ EMBER_DEFINE_LAST_ERROR
 namespace ember {
 
 constexpr int SAMPLE_THREADS = 1024;
+constexpr int SAMPLE_LIST = 1024;      // a top-k up to this size is finished on a list in shared memory
 
 struct SampleParams {  // 32 bytes per row, mirrored by the Python side
     float temperature;
@@ -69,6 +70,14 @@ struct Shared {
     unsigned long long remaining_k;
     double remaining_mass;
     int found;
+    // the kept set of a small top-k, gathered in the first block (any order), then sorted by (value descending,
+    // index ascending)
+    int n_list;
+    float list_x[SAMPLE_LIST];
+    int list_i[SAMPLE_LIST];
+    float sort_x[SAMPLE_LIST];
+    int sort_i[SAMPLE_LIST];
+    double sort_e[SAMPLE_LIST];
 };
 
 __device__ __forceinline__ unsigned cl_rank() { unsigned r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
@@ -358,6 +367,70 @@ sample_kernel(const float* __restrict__ logits_all, int V, const SampleParams* _
         k_cut = nth_equal_index<CL>(logits, tdiv, V, lo, hi, k_key, need_eq, [](int, float) { return true; }, sh);
     }
     auto kept_k = [&](int i, unsigned key) { return !use_k || key > k_key || (key == k_key && i <= k_cut); };
+
+    if (use_k && p.top_k <= SAMPLE_LIST) {
+        // ---- a small kept set: gather it in the first block and finish there as the host does, on a list
+        // sorted by (value descending, index ascending): cumulative mass for top-p, min-p, the draw.  This
+        // replaces seven more scans of the row (and their cluster barriers) by one.
+        if (tid == 0 && rank == 0) sh.n_list = 0;
+        cl_sync<CL>();
+        Shared* first = cl_peer<CL>(&sh, 0);
+        for (int i = lo + tid; i < hi; i += SAMPLE_THREADS) {
+            const float x = logits[i] / tdiv;
+            if (kept_k(i, float_key(x))) {
+                const int slot = atomicAdd(&first->n_list, 1);
+                if (slot < SAMPLE_LIST) { first->list_x[slot] = x; first->list_i[slot] = i; }
+            }
+        }
+        cl_sync<CL>();
+        if (rank != 0) return;                       // the first block goes on alone (block barriers only)
+        const int n = min(sh.n_list, SAMPLE_LIST);
+        // position of every element in the sorted order: how many come before it
+        for (int j = tid; j < n; j += SAMPLE_THREADS) {
+            const float xj = sh.list_x[j];
+            const int ij = sh.list_i[j];
+            int before = 0;
+            for (int l = 0; l < n; l++) {
+                const float xl = sh.list_x[l];
+                before += (xl > xj || (xl == xj && sh.list_i[l] < ij)) ? 1 : 0;
+            }
+            sh.sort_x[before] = xj;
+            sh.sort_i[before] = ij;
+            sh.sort_e[before] = exp((double)xj - (double)xmax);
+        }
+        __syncthreads();
+        // top-p: the shortest prefix whose mass reaches top_p * Z (one thread walks the list: it is short)
+        if (tid == 0) {
+            int keep_n = n;
+            if (p.top_p < 1.0f) {
+                double Z = 0.0;
+                for (int j = 0; j < n; j++) Z += sh.sort_e[j];
+                const double want = (double)p.top_p * Z;
+                double cum = 0.0;
+                keep_n = 0;
+                while (keep_n < n) {
+                    cum += sh.sort_e[keep_n++];
+                    if (cum >= want) break;
+                }
+            }
+            sh.found = keep_n;
+        }
+        __syncthreads();
+        const int keep_n = sh.found;
+        const double floor_p = p.min_p > 0.0f ? (double)p.min_p : -1.0;
+        float best_s = -INFINITY;
+        int best_t = 0x7fffffff;
+        for (int j = tid; j < keep_n; j += SAMPLE_THREADS) {
+            const int i = sh.sort_i[j];
+            if (floor_p > 0.0 && i != arg && !(sh.sort_e[j] >= floor_p)) continue;
+            const float s_ = sh.sort_x[j] + gumbel_noise(p.seed, p.counter, (unsigned)i);
+            if (s_ > best_s || (s_ == best_s && i < best_t)) { best_s = s_; best_t = i; }
+        }
+        int tok;
+        cluster_max_arg<1>(best_s, best_t, &tok, sh);
+        if (tid == 0) out[row] = tok == 0x7fffffff ? arg : tok;
+        return;
+    }
 
     // ---- top-p: the smallest prefix (value descending, index ascending) whose mass reaches top_p * Z
     unsigned p_key = 0;
