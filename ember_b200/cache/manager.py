@@ -8,72 +8,78 @@ every key on them is older than the window; freed pages are handed out again (mo
 freed first).  Beside the pages, every admitted request holds one *slot* for state of fixed
 size; mixers of kind "state" keep their per-request tensors there.
 
-The manager owns no memory: ``ember_b200.cache.storage`` allocates the device tensors the ids
-point into.  (Page accounting in the reference: src/kvcache/block_manager.{hpp,cpp},
-src/engine/engine.cpp:176-184; groups, windows and slots have no counterpart there.)
+The books themselves are kept natively (``ember_b200/runtime/cache_core.cpp``, as the reference
+keeps its own in C++: src/kvcache/block_manager.{hpp,cpp}, src/engine/engine.cpp:176-184; groups,
+windows and slots have no counterpart there).  This module is their Python face: it names
+requests by any hashable key, groups layers by need, and turns return codes into ``CacheError``.
+The manager owns no device memory: ``ember_b200.cache.storage`` allocates the tensors the ids
+point into.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass, field
+import ctypes
+from ctypes import POINTER, c_int32
+from dataclasses import dataclass
 from typing import Dict, Hashable, List, Mapping, Optional, Sequence, Tuple
 
 import numpy as np
 
 from ..parts.base import CacheNeed
+from ..runtime import library
+
+_KINDS = {"full": 0, "window": 1, "state": 2}
 
 
 class CacheError(RuntimeError):
     pass
 
 
+def _message(fn, handle) -> str:
+    buf = ctypes.create_string_buffer(256)
+    fn(handle, buf, 256)
+    return buf.value.decode("utf-8", "replace")
+
+
 class PagePool:
     """Ids 0..n-1; low ids first from a fresh pool, then most recently freed first."""
 
-    def __init__(self, n_pages: int):
+    def __init__(self, n_pages: int, _native=None, _owner=None):
         if n_pages < 0:
             raise CacheError("a pool cannot have a negative number of pages")
-        self.n_pages = n_pages
-        self._free: List[int] = list(range(n_pages - 1, -1, -1))
-        self._held = [False] * n_pages
+        self._lib = library()
+        self.n_pages = int(n_pages)
+        self._owner = _owner                 # a pool inside a manager lives and dies with it
+        self._own = _native is None
+        self._p = _native if _native is not None else self._lib.ember_pool_create(self.n_pages)
+
+    def __del__(self):
+        if getattr(self, "_own", False) and self._p:
+            self._lib.ember_pool_destroy(self._p)
+            self._p = None
 
     @property
     def available(self) -> int:
-        return len(self._free)
+        return self._lib.ember_pool_available(self._p)
 
     @property
     def used(self) -> int:
-        return self.n_pages - len(self._free)
+        return self.n_pages - self.available
 
     def allocate(self) -> int:
-        if not self._free:
-            return -1
-        p = self._free.pop()
-        self._held[p] = True
-        return p
+        return self._lib.ember_pool_allocate(self._p)
 
     def release(self, page: int) -> None:
-        if not (0 <= page < self.n_pages):
+        code = self._lib.ember_pool_release(self._p, int(page))
+        if code == 1:
             raise CacheError(f"page {page} is outside the pool of {self.n_pages}")
-        if not self._held[page]:
+        if code == 2:
             raise CacheError(f"page {page} is freed twice")
-        self._held[page] = False
-        self._free.append(page)
 
     def is_held(self, page: int) -> bool:
-        return self._held[page]
+        return bool(self._lib.ember_pool_is_held(self._p, int(page)))
 
     def check(self) -> str:
-        seen = set()
-        for p in self._free:
-            if p in seen:
-                return f"page {p} is on the free list twice"
-            seen.add(p)
-            if self._held[p]:
-                return f"page {p} is both free and held"
-        held = sum(self._held)
-        if held + len(self._free) != self.n_pages:
-            return f"{held} held + {len(self._free)} free != {self.n_pages} pages (a page is lost)"
-        return ""
+        return _message(self._lib.ember_pool_check, self._p)
 
 
 @dataclass
@@ -89,29 +95,33 @@ class CacheGroup:
         return self.need.kind in ("full", "window")
 
 
-@dataclass
 class RequestCache:
-    slot: int
-    tables: List[List[int]]        # per group: physical page of each logical page, -1 once given back
-    first_live: List[int]          # per group: first logical page still held
-    tokens: int = 0                # tokens whose keys are in the cache
-    arrays: List[np.ndarray] = field(default_factory=list)   # per group: int32 mirror of `tables` (grown by doubling)
-    addrs: List[int] = field(default_factory=list)           # per group: address of the mirror (for the native packer)
+    """What one admitted request holds: a view of the native record."""
+
+    __slots__ = ("_m", "handle", "slot", "tokens")
+
+    def __init__(self, manager: "CacheManager", handle: int, slot: int):
+        self._m = manager
+        self.handle = handle
+        self.slot = slot
+        self.tokens = 0                # tokens whose keys are in the cache (kept in step by the manager)
 
     def table_array(self, group: int) -> np.ndarray:
-        """The group's block table as an int32 array (a view: valid until the table changes)."""
-        n = len(self.tables[group])
-        return self.arrays[group][:n]
+        """The group's block table as an int32 array (a copy): physical page of each logical page, -1 once
+        given back."""
+        ptr = POINTER(c_int32)()
+        n = self._m._lib.ember_cache_table(self._m.core, self.handle, group, ctypes.byref(ptr))
+        if n <= 0:
+            return np.zeros(0, dtype=np.int32)
+        return np.ctypeslib.as_array(ptr, shape=(n,)).copy()
 
-    def _mirror_append(self, group: int, page: int) -> None:
-        n = len(self.tables[group])          # the list already holds the new page at n - 1
-        a = self.arrays[group]
-        if n > a.shape[0]:
-            b = np.full(max(16, 2 * a.shape[0]), -1, dtype=np.int32)
-            b[:a.shape[0]] = a
-            self.arrays[group] = a = b
-            self.addrs[group] = a.ctypes.data
-        a[n - 1] = page
+    @property
+    def tables(self) -> List[List[int]]:
+        return [self.table_array(g).tolist() for g in range(len(self._m.groups))]
+
+    @property
+    def first_live(self) -> List[int]:
+        return [self._m._lib.ember_cache_first_live(self._m.core, self.handle, g) for g in range(len(self._m.groups))]
 
 
 def group_needs(needs: Mapping[int, Optional[CacheNeed]]) -> List[Tuple[CacheNeed, List[int]]]:
@@ -135,20 +145,40 @@ class CacheManager:
                  max_requests: int, pages_per_group: Optional[Sequence[int]] = None):
         if page_tokens <= 0:
             raise CacheError("page_tokens must be positive")
+        self._lib = library()
         self.page_tokens = page_tokens
         self.max_requests = max_requests
-        self.groups: List[CacheGroup] = []
-        for gi, (need, layers) in enumerate(group_needs(needs)):
-            if need.kind not in ("full", "window", "state"):
+        grouped = group_needs(needs)
+        kinds, windows, pages = [], [], []
+        for gi, (need, _) in enumerate(grouped):
+            if need.kind not in _KINDS:
                 raise CacheError(f"unknown cache need {need.kind!r}")
+            n = 0
+            if need.kind != "state":
+                n = int(pages_per_group[gi] if pages_per_group is not None else capacity_tokens // page_tokens)
+                if n < 0:
+                    raise CacheError("a pool cannot have a negative number of pages")
+            kinds.append(_KINDS[need.kind])
+            windows.append(int(getattr(need, "window", 0) or 0))
+            pages.append(n)
+        G = len(grouped)
+        arr = lambda v: (c_int32 * max(G, 1))(*v)          # noqa: E731
+        self.core = self._lib.ember_cache_create(G, arr(kinds), arr(windows), arr(pages), int(page_tokens), int(max_requests))
+        if not self.core:
+            raise CacheError("the cache core could not be created")
+        self.groups: List[CacheGroup] = []
+        for gi, (need, layers) in enumerate(grouped):
             pool = None
             if need.kind != "state":
-                n = pages_per_group[gi] if pages_per_group is not None else capacity_tokens // page_tokens
-                pool = PagePool(int(n))
+                pool = PagePool(pages[gi], _native=self._lib.ember_cache_pool(self.core, gi), _owner=self)
             self.groups.append(CacheGroup(gi, need, layers, page_tokens, pool))
         self.layer_group: Dict[int, int] = {l: g.index for g in self.groups for l in g.layers}
-        self._free_slots: List[int] = list(range(max_requests - 1, -1, -1))
         self._requests: Dict[Hashable, RequestCache] = {}
+
+    def __del__(self):
+        core, self.core = getattr(self, "core", None), None
+        if core:
+            self._lib.ember_cache_destroy(core)
 
     # ---------------------------------------------------------------- requests
     def has(self, request: Hashable) -> bool:
@@ -160,83 +190,49 @@ class CacheManager:
         except KeyError:
             raise CacheError(f"request {request!r} holds no cache") from None
 
+    def handle_of(self, request: Hashable) -> int:
+        """The native handle of an admitted request (what the step packer passes back to the core)."""
+        return self.get(request).handle
+
     def admit(self, request: Hashable) -> Optional[RequestCache]:
         """Gives the request a state slot and empty block tables; None if no slot is free."""
         if request in self._requests:
             raise CacheError(f"request {request!r} is admitted twice")
-        if not self._free_slots:
+        h = self._lib.ember_cache_admit(self.core)
+        if h < 0:
             return None
-        arrays = [np.full(16, -1, dtype=np.int32) for _ in self.groups]
-        rc = RequestCache(slot=self._free_slots.pop(), tables=[[] for _ in self.groups],
-                          first_live=[0 for _ in self.groups], arrays=arrays,
-                          addrs=[a.ctypes.data for a in arrays])
+        rc = RequestCache(self, h, self._lib.ember_cache_slot(self.core, h))
         self._requests[request] = rc
         return rc
 
     def pages_needed(self, request: Hashable, upto_tokens: int) -> List[int]:
         rc = self.get(request)
         want = (upto_tokens + self.page_tokens - 1) // self.page_tokens
-        return [max(0, want - len(rc.tables[g.index])) if g.paged else 0 for g in self.groups]
+        return [max(0, want - self._lib.ember_cache_table(self.core, rc.handle, g.index, None)) if g.paged else 0
+                for g in self.groups]
 
     def ensure(self, request: Hashable, upto_tokens: int) -> bool:
         """Makes sure pages exist for tokens [0, upto_tokens) in every paged group (all or nothing)."""
-        rc = self.get(request)
-        need = self.pages_needed(request, upto_tokens)
-        for g, n in zip(self.groups, need):
-            if g.paged and g.pool.available < n:
-                return False
-        for g, n in zip(self.groups, need):
-            for _ in range(n):
-                page = g.pool.allocate()
-                rc.tables[g.index].append(page)
-                rc._mirror_append(g.index, page)
-        return True
+        return self._lib.ember_cache_ensure(self.core, self.get(request).handle, int(upto_tokens)) == 1
 
     def advance(self, request: Hashable, tokens: int) -> int:
         """Records that ``tokens`` tokens are now cached; gives back window pages no later query
         can see.  Returns how many pages were freed."""
         rc = self.get(request)
-        rc.tokens = tokens
-        freed = 0
-        for g in self.groups:
-            if g.need.kind != "window":
-                continue
-            # the next query is at position >= tokens and sees keys > position - window
-            first_key = max(0, tokens - g.need.window + 1)
-            dead = first_key // self.page_tokens
-            table = rc.tables[g.index]
-            for i in range(rc.first_live[g.index], min(dead, len(table))):
-                if table[i] >= 0:
-                    g.pool.release(table[i])
-                    table[i] = -1
-                    rc.arrays[g.index][i] = -1
-                    freed += 1
-            rc.first_live[g.index] = max(rc.first_live[g.index], min(dead, len(table)))
-        return freed
+        rc.tokens = int(tokens)
+        return self._lib.ember_cache_advance(self.core, rc.handle, rc.tokens)
 
     def release(self, request: Hashable) -> None:
         """Gives back everything the request holds (pages in reverse order, then its slot)."""
         rc = self._requests.pop(request, None)
         if rc is None:
             raise CacheError(f"request {request!r} is released but holds nothing")
-        for g in self.groups:
-            if not g.paged:
-                continue
-            for p in reversed(rc.tables[g.index]):
-                if p >= 0:
-                    g.pool.release(p)
-        self._free_slots.append(rc.slot)
+        self._lib.ember_cache_release(self.core, rc.handle)
 
     def reset(self, request: Hashable) -> None:
         """Preemption: pages go back, the slot stays with the request."""
         rc = self.get(request)
-        for g in self.groups:
-            if g.paged:
-                for p in reversed(rc.tables[g.index]):
-                    if p >= 0:
-                        g.pool.release(p)
-            rc.tables[g.index] = []
-            rc.first_live[g.index] = 0
+        self._lib.ember_cache_reset(self.core, rc.handle)
         rc.tokens = 0
 
     # ------------------------------------------------------------------ queries
@@ -244,7 +240,7 @@ class CacheManager:
         return list(self._requests)
 
     def free_slots(self) -> int:
-        return len(self._free_slots)
+        return self._lib.ember_cache_free_slots(self.core)
 
     def available_pages(self) -> List[int]:
         return [g.pool.available if g.paged else 0 for g in self.groups]
@@ -257,30 +253,11 @@ class CacheManager:
         return min(paged) if paged else 1 << 30
 
     def check(self) -> str:
-        """Audit: every page is free or held by exactly one request; every slot likewise."""
-        for g in self.groups:
-            if not g.paged:
-                continue
-            msg = g.pool.check()
-            if msg:
-                return f"group {g.index}: {msg}"
-            owners: Dict[int, Hashable] = {}
-            for req, rc in self._requests.items():
-                for p in rc.tables[g.index]:
-                    if p < 0:
-                        continue
-                    if p in owners:
-                        return f"group {g.index}: page {p} is held by {owners[p]!r} and {req!r}"
-                    owners[p] = req
-                    if not g.pool.is_held(p):
-                        return f"group {g.index}: page {p} of {req!r} is on the free list"
-            if len(owners) != g.pool.used:
-                return f"group {g.index}: {g.pool.used} pages are out but requests hold {len(owners)}"
-        slots = [rc.slot for rc in self._requests.values()]
-        if len(set(slots)) != len(slots):
-            return "a state slot is held twice"
-        if set(slots) & set(self._free_slots):
-            return "a state slot is both held and free"
-        if len(slots) + len(self._free_slots) != self.max_requests:
-            return "a state slot is lost"
+        """Audit: every page is free or held by exactly one request; every slot likewise; and the
+        requests known here are the ones the core holds."""
+        msg = _message(self._lib.ember_cache_check, self.core)
+        if msg:
+            return msg
+        if len(self._requests) + self.free_slots() != self.max_requests:
+            return "the requests known to the manager and the slots held in the core differ"
         return ""

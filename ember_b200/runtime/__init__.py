@@ -50,19 +50,22 @@ def library() -> ctypes.CDLL:
     with _lock:
         if _lib is not None:
             return _lib
-        src = os.path.join(_HERE, "step_pack.cpp")
-        with open(src, "rb") as f:
-            digest = hashlib.sha256(f.read()).hexdigest()[:16]
+        srcs = [os.path.join(_HERE, n) for n in ("step_pack.cpp", "cache_core.cpp")]
+        h = hashlib.sha256()
+        for src in srcs:
+            with open(src, "rb") as f:
+                h.update(f.read())
+        digest = h.hexdigest()[:16]
         so = os.path.join(kernel_build.build_dir(), "libember_runtime.so")
         stamp = so + ".stamp"
         current = os.path.isfile(so) and os.path.isfile(stamp) and open(stamp).read().strip() == digest
         if not current:
-            print("[ember_b200] compiling the host runtime (step_pack.cpp) ...", file=sys.stderr, flush=True)
+            print("[ember_b200] compiling the host runtime (step_pack.cpp, cache_core.cpp) ...", file=sys.stderr, flush=True)
             tmp = f"{so}.{os.getpid()}.tmp"
-            proc = subprocess.run([_compiler(), "-O2", "-std=c++17", "-shared", "-fPIC", "-o", tmp, src],
+            proc = subprocess.run([_compiler(), "-O2", "-std=c++17", "-shared", "-fPIC", "-o", tmp] + srcs,
                                   capture_output=True, text=True)
             if proc.returncode != 0:
-                raise RuntimeBuildError(f"the C++ compiler failed on step_pack.cpp:\n{proc.stdout}{proc.stderr}")
+                raise RuntimeBuildError(f"the C++ compiler failed on the host runtime:\n{proc.stdout}{proc.stderr}")
             os.replace(tmp, so)
             with open(stamp, "w") as f:
                 f.write(digest)
@@ -74,6 +77,29 @@ def library() -> ctypes.CDLL:
         lib.ember_step_pack.restype = None
         lib.ember_step_pack.argtypes = [c_int, vp, vp, vp, vp, vp, vp, c_int, vp, vp, vp,
                                         c_int, vp, vp, POINTER(StepLayout), vp]
+        # the cache core (cache_core.cpp)
+        i32p, i64p, u64p = POINTER(c_int32), POINTER(ctypes.c_int64), POINTER(c_uint64)
+        sigs = {
+            "ember_pool_create": (c_void_p, [c_int]), "ember_pool_destroy": (None, [c_void_p]),
+            "ember_pool_allocate": (c_int, [c_void_p]), "ember_pool_release": (c_int, [c_void_p, c_int]),
+            "ember_pool_available": (c_int, [c_void_p]), "ember_pool_is_held": (c_int, [c_void_p, c_int]),
+            "ember_pool_check": (c_int, [c_void_p, ctypes.c_char_p, c_int]),
+            "ember_cache_create": (c_void_p, [c_int, i32p, i32p, i32p, c_int, c_int]),
+            "ember_cache_destroy": (None, [c_void_p]), "ember_cache_pool": (c_void_p, [c_void_p, c_int]),
+            "ember_cache_admit": (c_int, [c_void_p]), "ember_cache_slot": (c_int, [c_void_p, c_int]),
+            "ember_cache_tokens": (ctypes.c_longlong, [c_void_p, c_int]),
+            "ember_cache_first_live": (c_int, [c_void_p, c_int, c_int]),
+            "ember_cache_table": (c_int, [c_void_p, c_int, c_int, POINTER(i32p)]),
+            "ember_cache_ensure": (c_int, [c_void_p, c_int, ctypes.c_longlong]),
+            "ember_cache_advance": (c_int, [c_void_p, c_int, ctypes.c_longlong]),
+            "ember_cache_release": (c_int, [c_void_p, c_int]), "ember_cache_reset": (c_int, [c_void_p, c_int]),
+            "ember_cache_free_slots": (c_int, [c_void_p]),
+            "ember_cache_describe": (c_int, [c_void_p, c_int, vp, vp, vp, vp, vp]),
+            "ember_cache_check": (c_int, [c_void_p, ctypes.c_char_p, c_int]),
+        }
+        for name, (res, args) in sigs.items():
+            fn = getattr(lib, name)
+            fn.restype, fn.argtypes = res, args
         _lib = lib
         return lib
 
@@ -174,37 +200,38 @@ class StepPacker:
         groups = cache.groups
         G = len(groups)
         page = cache.page_tokens
-        requests, counts, starts, slots, want_counts = [], [], [], [], []
+        requests, counts, want_counts, handles = [], [], [], []
         tok_flat, want_flat = [], []
-        table_addr = [0] * (G * S)
-        table_lens = [0] * (G * S)
-        get = cache.get
-        s = 0
+        handle_of = cache.handle_of
         for e in entries:
-            toks = e.tokens
-            n = len(toks)
-            rc = get(e.request)
-            start = rc.tokens
-            if max_positions is not None and start + n > max_positions:
-                raise BatchError(f"request {e.request!r} would reach position {start + n}; "
-                                 f"the model's limit is {max_positions}")
-            tables, addrs = rc.tables, rc.addrs
-            for g in groups:
-                gi = g.index
-                ln = len(tables[gi])
-                if ln * page < start + n and g.paged:
-                    raise BatchError(f"request {e.request!r} has no pages for tokens up to {start + n}")
-                table_addr[gi * S + s] = addrs[gi]
-                table_lens[gi * S + s] = ln
             requests.append(e.request)
-            counts.append(n)
-            starts.append(start)
-            slots.append(rc.slot)
+            handles.append(handle_of(e.request))
+            counts.append(len(e.tokens))
             want_counts.append(len(e.want))
-            tok_flat += toks
+            tok_flat += e.tokens
             if e.want:
                 want_flat += e.want
-            s += 1
+        # cached lengths, slots and block tables of all entries in one native call
+        d_i32, d_i32_at = self._array("describe.i32", S * (2 + G) + 8)
+        d_i64, d_i64_at = self._array("describe.i64", S * (1 + G) + 8, np.int64)
+        d_i32[:S] = handles
+        bad = lib.ember_cache_describe(cache.core, S, d_i32_at, d_i64_at, d_i32_at + 4 * S, d_i64_at + 8 * S,
+                                       d_i32_at + 8 * S)
+        if bad >= 0:
+            from ..cache.manager import CacheError
+            raise CacheError(f"request {entries[bad].request!r} holds no cache")
+        starts = d_i64[:S].tolist()
+        slots = d_i32[S:2 * S].tolist()
+        table_addr = d_i64[S:S + G * S].view(np.uint64).tolist()
+        table_lens = d_i32[2 * S:2 * S + G * S].tolist()
+        for s in range(S):
+            n, start = counts[s], starts[s]
+            if max_positions is not None and start + n > max_positions:
+                raise BatchError(f"request {requests[s]!r} would reach position {start + n}; "
+                                 f"the model's limit is {max_positions}")
+            for g in groups:
+                if g.paged and table_lens[g.index * S + s] * page < start + n:
+                    raise BatchError(f"request {requests[s]!r} has no pages for tokens up to {start + n}")
         if len(set(requests)) != S:
             raise BatchError("a request appears twice in one step")
         if widths is None:
