@@ -238,6 +238,62 @@ def time_prefill(llm, tokens, reps, warmup):
     return statistics.median(times)
 
 
+def breakdown(cfg, n_layers, batch) -> int:
+    """Per-kernel device time of decode steps and of a prefill step, kernels serialised (no programmatic
+    dependent launch, no graphs), caches warm: what each kernel costs by itself inside a step."""
+    os.environ["EMBER_PDL"] = "0"
+    import torch
+    from torch.profiler import ProfilerActivity, profile
+    from ember_b200 import StepEntry
+    import random
+    llm = build_llm(cfg, n_layers, max(batch, 1))
+    r = llm.runner
+    r.cuda_graphs = False
+    ids = fill_cache(llm, batch, DECODE_FROM)
+    rng = random.Random(1)
+    vocab = r.spec.vocab_size
+
+    def decode():
+        for rid in ids:
+            assert r.reserve(rid, 1)
+        r.step([StepEntry(rid, [rng.randrange(1000, min(100000, vocab))], (0,)) for rid in ids])
+
+    def table(title, prof, steps):
+        rows = [(e.key, e.self_device_time_total / steps, e.count // steps) for e in prof.key_averages()
+                if e.self_device_time_total > 0]
+        rows.sort(key=lambda x: -x[1])
+        total = sum(x[1] for x in rows)
+        print(f"{title}: {total / 1000:.3f} ms of kernels per step")
+        for name, us, n in rows[:12]:
+            print(f"  {us:9.1f} us {100 * us / total:5.1f} %  x{n:<4d} {name.split('(')[0][-60:]}")
+
+    for _ in range(3):
+        decode()
+    torch.cuda.synchronize()
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        for _ in range(3):
+            decode()
+        torch.cuda.synchronize()
+    table(f"decode step, batch {batch}, context {DECODE_FROM}, {n_layers} layers", prof, 3)
+    for rid in ids:
+        r.release(rid)
+    toks = [rng.randrange(1000, min(100000, vocab)) for _ in range(PREFILL_TOKENS)]
+
+    def prefill(i):
+        rid = ("prefill", i)
+        assert r.admit(rid) and r.reserve(rid, PREFILL_TOKENS)
+        r.step([StepEntry(rid, toks, (PREFILL_TOKENS - 1,))])
+        torch.cuda.synchronize()
+        r.release(rid)
+
+    for i in range(2):
+        prefill(i)
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        prefill(2)
+    table(f"prefill step, {PREFILL_TOKENS} tokens, {n_layers} layers", prof, 1)
+    return 0
+
+
 def main() -> int:
     global PAGE_TOKENS
     ap = argparse.ArgumentParser()
@@ -249,6 +305,9 @@ def main() -> int:
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--skip-points", action="store_true", help="skip the batch 1 / 64 points and the prefill")
     ap.add_argument("--only-prefill", action="store_true", help="profiling aid: run just the 2,048-token prefill")
+    ap.add_argument("--breakdown", action="store_true",
+                    help="profiling aid: device time per kernel of three decode steps and one 2,048-token prefill step "
+                         "(kernels serialised: EMBER_PDL=0 and no CUDA graphs are set by this flag)")
     ap.add_argument("--page-tokens", type=int, default=PAGE_TOKENS, choices=[16, 32, 64], help="tokens per cache page")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS,
                     help="with --only-prefill: another prompt length (the reported line stays at 2,048)")
@@ -273,6 +332,8 @@ def main() -> int:
     pk = peaks()
     wbytes, kv_per_token, prefill_flops = model_bytes_and_flops(cfg, n_layers)
 
+    if args.breakdown:
+        return breakdown(cfg, n_layers, args.batch)
     if args.only_prefill:
         n_tok = max(2, args.prefill_tokens)
         llm = build_llm(cfg, n_layers, 1, prefill_tokens=n_tok)
