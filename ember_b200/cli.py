@@ -148,6 +148,12 @@ def cmd_bench(args) -> int:
     llm = _load(args)
     eng = llm.engine
     vocab = llm.spec.vocab_size
+    # a model with a short position limit gets shorter prompts and generations than the reference's defaults
+    limit = eng.scheduler.max_context
+    if prompt_len + 2 > limit or 64 + gen + 1 > limit:
+        prompt_len = max(1, min(prompt_len, limit // 2))
+        gen = max(2, min(gen, limit - min(64, limit // 2) - 2))
+        print(f"(the context limit is {limit}: prompt {prompt_len}, {gen} generated tokens)")
     rng = random.Random(1234)
 
     def prompt(n):
