@@ -6,7 +6,8 @@
 // every key tile -- of one key/value head and walks the key tiles of 64 keys up to the causal
 // diagonal:
 //   warp 0      fetches key and value pages by TMA (one box per page and 64-wide half, 128-byte
-//               swizzle) into a ring of stages;
+//               swizzle) into two rings: a key tile is free once S = Q K^T has read it, its values
+//               only after O += P V, so keys (two stages) run as far ahead as values (three);
 //   warp 1      issues tcgen05.mma: S_j = Q K_j^T (128 x 64, accumulator in tensor memory, two
 //               buffers) and O_j = P_j V_j (128 x 128, V read MN-major straight from the page layout);
 //   warps 2-5   own one query row per thread: they read S_j from tensor memory (tcgen05.ld), keep
@@ -17,7 +18,10 @@
 //               more than 8 (a factor 256, harmless in bf16 and fp32); then the row of O is rescaled
 //               in tensor memory (tcgen05.ld / tcgen05.st).  After the first tiles this is rare, so O
 //               stays in tensor memory and the output registers are only filled at the end.
-// S_{j+1} is multiplied while the rows of S_j are being exponentiated.  Every wait is bounded
+// S_{j+1} is multiplied while the rows of S_j are being exponentiated.  What bounds a tile is the
+// issuing thread (a tcgen05.mma costs it about 60 cycles, a wait that passes at once 100, twelve
+// instructions and four commits a tile) and the chain S visible -> exponentials -> P ready -> O += P V;
+// measured per 64-key tile: 2,200 cycles, of which the softmax warps work 960.  Every wait is bounded
 // (EMBER_ERR_WAIT_LIMIT) and the tensor memory is freed on every path.
 //
 // The reference's prefill attention (src/backend/cuda/k_attention.cu:214-370) is a Turing
@@ -207,8 +211,7 @@ attention_fa_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
     uint64_t* v_full = k_empty + FA_K_STAGES;
     uint64_t* v_empty = v_full + FA_V_STAGES;
     uint64_t* s_full = v_empty + FA_V_STAGES;             // [2]
-    uint64_t* s_empty = s_full + 2;                       // [2]
-    uint64_t* q_ready = s_empty + 2;
+    uint64_t* q_ready = s_full + 2;
     uint64_t* p_full = q_ready + 1;                       // [2]: the softmax warps may be a tile ahead of the MMA thread
     uint64_t* pv_full = p_full + 2;
     uint32_t* tmem_slot = (uint32_t*)(pv_full + 1);
@@ -237,7 +240,6 @@ attention_fa_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
         }
         for (int i = 0; i < 2; i++) {
             fa_mbar_init(&s_full[i], 1);
-            fa_mbar_init(&s_empty[i], 4);
         }
         fa_mbar_init(q_ready, 4);
         fa_mbar_init(&p_full[0], 4);
@@ -432,11 +434,9 @@ attention_fa_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
             // raise the reference maximum only when the true one has outgrown it by more than 2^8
             const bool raise = tmax > m_ref + 8.0f || (m_ref == -INFINITY && tmax > -INFINITY);
             const bool warp_raise = __any_sync(0xffffffffu, raise);
-            bool pv_waited = j == 0;
             if (warp_raise && j > 0) {
                 // O is complete up to tile j - 1 once the previous second product has finished
                 if (ok) ok = fa_wait(pv_full, (uint32_t)(j - 1) & 1u, abort_flag);
-                pv_waited = true;
                 const float factor = raise ? (m_ref == -INFINITY ? 0.0f : exp2f(m_ref - tmax)) : 1.0f;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
