@@ -214,7 +214,8 @@ attention_fa_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
     uint64_t* q_ready = s_full + 2;
     uint64_t* p_full = q_ready + 1;                       // [2]: the softmax warps may be a tile ahead of the MMA thread
     uint64_t* pv_full = p_full + 2;
-    uint32_t* tmem_slot = (uint32_t*)(pv_full + 1);
+    uint64_t* o_done = pv_full + 1;                       // the last O += P V has finished
+    uint32_t* tmem_slot = (uint32_t*)(o_done + 1);
     volatile int* abort_flag = (volatile int*)(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -245,6 +246,7 @@ attention_fa_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
         fa_mbar_init(&p_full[0], 4);
         fa_mbar_init(&p_full[1], 4);
         fa_mbar_init(pv_full, 1);
+        fa_mbar_init(o_done, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -372,6 +374,7 @@ attention_fa_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
                 }
                 fa_commit(&v_empty[b]);         // the values of tile j are no longer read
                 fa_commit(pv_full);             // O_j is complete, P may be overwritten
+                if (j == n_kt - 1) fa_commit(o_done);
             }
         }
     } else {
@@ -475,7 +478,10 @@ attention_fa_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
             __syncwarp();
             if (lane == 0) fa_arrive(&p_full[j & 1]);
         }
-        if (n_kt > 0 && ok) ok = fa_wait(pv_full, (uint32_t)(n_kt - 1) & 1u, abort_flag);
+        // (a barrier of its own: the rows of the last tile can be done while O += P V of the tile before the last
+        // still waits for its values, two phases of pv_full behind, and a parity cannot tell two phases apart;
+        // the wait in the loop above is safe, S_j being complete only after O += P V of tile j - 2)
+        if (n_kt > 0 && ok) ok = fa_wait(o_done, 0, abort_flag);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
         if (n_kt > 0) {
             const float inv = l_run > 0.0f ? 1.0f / l_run : 0.0f;
