@@ -33,7 +33,7 @@ QWEN3_1P7B = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_
 CONTEXT = 4096          # decode runs up to this many positions
 DECODE_FROM = 3072      # the timed decode steps start here (the middle of 2,048 -> 4,096)
 PREFILL_TOKENS = 2048
-PAGE_TOKENS = 16          # the reference's block size; --page-tokens 32 or 64 is a few per cent faster (fewer TMA boxes a tile)
+PAGE_TOKENS = 64          # the engine's default; the reference's block size is 16 (--page-tokens 16: a few per cent slower, more TMA boxes a tile)
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0, "source": "fallback"}
 
 

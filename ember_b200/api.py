@@ -52,7 +52,7 @@ class LLM:
 
 def load(model: str, dtype: str = "bfloat16", device: str = "cuda:0", kv_cache_tokens: int = 0,
          max_batch_tokens: int = 2048, max_seqs: int = 64, prefill_chunk: int = 2048,
-         max_context: Optional[int] = None, page_tokens: int = 16, cuda_graphs: bool = True) -> LLM:
+         max_context: Optional[int] = None, page_tokens: int = 64, cuda_graphs: bool = True) -> LLM:
     """Loads a model folder (config.json + safetensors).  ``kv_cache_tokens`` 0 sizes the cache
     for ``max_seqs`` requests of the model's position limit, capped at 262,144 tokens."""
     cfg = load_config(model)
@@ -67,7 +67,7 @@ def load(model: str, dtype: str = "bfloat16", device: str = "cuda:0", kv_cache_t
 
 def load_random(config, seed: int = 0, dtype: str = "bfloat16", device: str = "cuda:0", kv_cache_tokens: int = 0,
                 max_batch_tokens: int = 2048, max_seqs: int = 64, prefill_chunk: int = 2048,
-                max_context: Optional[int] = None, page_tokens: int = 16, cuda_graphs: bool = True,
+                max_context: Optional[int] = None, page_tokens: int = 64, cuda_graphs: bool = True,
                 weight_dtype=torch.bfloat16,
                 std: Optional[float] = None, norm_std: Optional[float] = None) -> LLM:
     """Random-weights mode without a folder: the tensors are made from ``seed`` in memory

@@ -100,7 +100,7 @@ def test_preemption_on_the_device_keeps_the_tokens(tiny_model_dirs):
     """So few pages that requests are preempted and recomputed: the tokens stay the same."""
     name = "a"
     plain = PlainQwen3(tiny_model_dirs[name], torch.float64)
-    llm = load(tiny_model_dirs, name, "float32", kv_cache_tokens=96, max_seqs=4)
+    llm = load(tiny_model_dirs, name, "float32", kv_cache_tokens=96, max_seqs=4, page_tokens=16)
     rng = np.random.default_rng(8)
     prompts = [rng.integers(0, 512, size=n).tolist() for n in (20, 25, 30, 18)]
     outs = llm.generate(prompts, max_tokens=30, ignore_eos=True)
