@@ -342,6 +342,25 @@ qk_norm_rope_store_d128_kernel(
     }
 }
 
+// The angles of a step's tokens, made once per step for the products that rotate in their epilogue (the same fp32
+// expression as the kernels above): out[i / 2][t] = (cos, sin) of float(position[t]) * inv_freq[i] for frequencies
+// i and i + 1, rows `ld` tokens long.  Token-minor, so that threads that hold neighbouring tokens read neighbouring
+// 16 bytes.
+__global__ void rope_table_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq, int T, int half,
+                                  int ld, float4* __restrict__ out) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int idx = blockIdx.x * blockDim.x + threadIdx.x;
+    const int pairs = half / 2;
+    if (idx >= T * pairs) return;
+    const int j = idx / T, t = idx - j * T;
+    const float pos = (float)positions[t];
+    float s0, c0, s1, c1;
+    sincosf(pos * inv_freq[2 * j], &s0, &c0);
+    sincosf(pos * inv_freq[2 * j + 1], &s1, &c1);
+    out[(size_t)j * ld + t] = make_float4(c0, s0, c1, s1);
+}
+
 // out[m, j] = silu(x[m, 2j]) * x[m, 2j+1] for an unfused gate/up product (interleaved rows).
 template <typename T>
 __global__ void silu_mul_interleaved_kernel(const T* __restrict__ x, T* __restrict__ out, size_t n_out) {
@@ -455,6 +474,15 @@ EMBER_API int ember_qk_norm_rope_store(const void* qkv, int dtype, int T, int ld
     else
         return fail("qk_norm_rope_store: unsupported dtype %d", dtype);
     return check_launch("qk_norm_rope_store");
+}
+
+EMBER_API int ember_rope_table(const int* positions, const float* inv_freq, int T, int half, int ld, void* out, void* stream) {
+    if (T <= 0 || half <= 0) return 0;
+    if ((half & 1) || ld < T) return fail("rope_table: %d frequencies (an even number is wanted), rows of %d for %d tokens", half, ld, T);
+    if (((uintptr_t)out) & 15) return fail("rope_table: the output must be 16-byte aligned");
+    launch_kernel(rope_table_kernel, (unsigned)(((long long)T * (half / 2) + 255) / 256), 256, 0, (cudaStream_t)stream, positions,
+                  inv_freq, T, half, ld, (float4*)out);
+    return check_launch("rope_table");
 }
 
 EMBER_API int ember_silu_mul_interleaved(const void* x, void* out, int dtype, long long n_out, void* stream) {

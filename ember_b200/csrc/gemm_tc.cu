@@ -139,6 +139,41 @@ static int launch_pair(const void* A, const void* W, GemmTcParams p, int block_c
     return check_launch("gemm_tc_pair");
 }
 
+// The single-SM persistent kernel (normal orientation): one block per SM walks the tiles of 128 tokens x block_cols.
+static int launch_persistent(const void* A, const void* W, GemmTcParams p, int block_cols, int num_sms, cudaStream_t st) {
+    p.swapped = 0;
+    p.block_cols = block_cols;
+    p.row_tiles = (p.M + TILE_ROWS - 1) / TILE_ROWS;
+    p.total_tiles = p.row_tiles * ((p.N + block_cols - 1) / block_cols);
+    p.cluster_splits = 1;
+    p.rows_per = TILE_ROWS;
+    p.k_blocks_per_split = p.num_k_blocks;
+    p.accum = nullptr; p.accum_ld = 0;
+    int tc = 32;
+    while (tc < 2 * block_cols) tc <<= 1;
+    p.tmem_cols = tc;
+    const int rows_bytes = TILE_ROWS * TILE_K * 2;
+    const int stage_bytes = rows_bytes + ((block_cols * TILE_K * 2 + 1023) & ~1023);
+    int stages = (200 * 1024) / stage_bytes;
+    if (stages > MAX_STAGES) stages = MAX_STAGES;
+    if (stages < 2) stages = 2;
+    if (stages > p.num_k_blocks) stages = p.num_k_blocks < 2 ? 2 : p.num_k_blocks;
+    p.stages = stages;
+    const size_t smem = (size_t)stages * stage_bytes + 1024 /* alignment slack */ + 256 /* barriers */;
+    CUtensorMap map_rows, map_cols;
+    if (!tensor_map(A, p.M, p.K, TILE_ROWS, &map_rows) || !tensor_map(W, p.N, p.K, block_cols, &map_cols))
+        return fail("gemm_tc: cuTensorMapEncodeTiled failed or is unavailable");
+    static bool pattr = false;
+    if (!pattr) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        if (e != cudaSuccess) return fail("gemm_tc: cannot raise the shared-memory limit: %s", cudaGetErrorString(e));
+        pattr = true;
+    }
+    const int blocks = p.total_tiles < num_sms ? p.total_tiles : num_sms;
+    launch_kernel(gemm_tc_persistent_kernel, dim3(blocks), dim3(GEMM_THREADS), smem, st, map_rows, map_cols, p);
+    return check_launch("gemm_tc_persistent");
+}
+
 }  // namespace ember
 
 using namespace ember;
@@ -195,6 +230,10 @@ EMBER_API int ember_gemm_tc(const void* A, const void* W, void* out, int ldc, in
                 }
             }
         }
+        if (split_mode != 3) {
+            p.epilogue = epilogue; p.out = out; p.ldc = ldc; p.err = err;
+            return launch_persistent(A, W, p, bc_single, num_sms, st);
+        }
         p.block_cols = bc_single;
         row_tiles = (M + TILE_ROWS - 1) / TILE_ROWS;
         col_tiles = (N + p.block_cols - 1) / p.block_cols;
@@ -243,12 +282,10 @@ EMBER_API int ember_gemm_tc(const void* A, const void* W, void* out, int ldc, in
             p.accum_ld = N;
         }
     }
-    // Prefill-sized products run as persistent blocks with two accumulators in tensor memory.
-    const bool persistent = !p.swapped && split_mode != 3;
     p.row_tiles = row_tiles;
     p.total_tiles = row_tiles * col_tiles;
     int tc = 32;
-    while (tc < p.block_cols * (persistent ? 2 : 1)) tc <<= 1;
+    while (tc < p.block_cols) tc <<= 1;
     p.tmem_cols = tc;
     const int rows_bytes = TILE_ROWS * TILE_K * 2;
     const int cols_bytes = p.block_cols * TILE_K * 2;
@@ -280,17 +317,6 @@ EMBER_API int ember_gemm_tc(const void* A, const void* W, void* out, int ldc, in
         cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared);
         attr_set = true;
     }
-    if (persistent) {
-        static bool pattr = false;
-        if (!pattr) {
-            cudaError_t e = cudaFuncSetAttribute(gemm_tc_persistent_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
-            if (e != cudaSuccess) return fail("gemm_tc: cannot raise the shared-memory limit: %s", cudaGetErrorString(e));
-            pattr = true;
-        }
-        const int blocks = p.total_tiles < num_sms ? p.total_tiles : num_sms;
-        launch_kernel(gemm_tc_persistent_kernel, dim3(blocks), dim3(GEMM_THREADS), smem, st, map_rows, map_cols, p);
-        return check_launch("gemm_tc_persistent");
-    }
     dim3 grid(row_tiles, col_tiles, splits);
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
@@ -318,4 +344,44 @@ EMBER_API int ember_gemm_tc(const void* A, const void* W, void* out, int ldc, in
         return check_launch("gemm_tc_finalize");
     }
     return 0;
+}
+
+// The fused projection of a layer's attention: [q | k | v] = A . W^T for M > 128 tokens, and straight from the
+// accumulator every query and key head gets its RMSNorm (weights may be null) and its rotation (cos_sin, the table
+// of ember_rope_table with cs_ld tokens a row, may be null), queries go to q_out, keys and values into their cache pages.  Heads are 128 wide.  1 if these sizes are taken.
+EMBER_API int ember_gemm_tc_qkv_supported(int M, int N, int K, int n_heads, int n_kv, int head_dim) {
+    return M > 128 && K > 0 && K % 8 == 0 && head_dim == 128 && n_heads > 0 && n_kv > 0 && N == (n_heads + 2 * n_kv) * 128;
+}
+
+EMBER_API int ember_gemm_tc_qkv(const void* A, const void* W, int M, int N, int K, int n_heads, int n_kv,
+                                const float* q_norm_w, const float* k_norm_w, float eps, const void* cos_sin, int cs_ld,
+                                const int* positions, const int* seq_of, const int* block_table, int max_blocks, int page,
+                                int num_pages, void* q_out, void* k_pool, void* v_pool, int write_kv, int num_sms,
+                                int split_mode, int* err, void* stream) {
+    if (!ember_gemm_tc_qkv_supported(M, N, K, n_heads, n_kv, 128))
+        return fail("gemm_tc_qkv: M=%d N=%d K=%d with %d/%d heads of 128 is not taken", M, N, K, n_heads, n_kv);
+    if ((((uintptr_t)A) | ((uintptr_t)W) | ((uintptr_t)q_out) | ((uintptr_t)k_pool) | ((uintptr_t)v_pool) | ((uintptr_t)cos_sin) |
+         ((uintptr_t)q_norm_w) | ((uintptr_t)k_norm_w)) & 15)
+        return fail("gemm_tc_qkv: operands must be 16-byte aligned");
+    if (!positions || !seq_of || !block_table || page <= 0 || max_blocks <= 0 || num_pages <= 0)
+        return fail("gemm_tc_qkv: bad cache geometry");
+    if (num_sms <= 0) num_sms = 148;
+    cudaStream_t st = (cudaStream_t)stream;
+    GemmTcParams p = {};
+    p.M = M; p.N = N; p.K = K;
+    p.num_k_blocks = (K + TILE_K - 1) / TILE_K;
+    p.epilogue = 4; p.out = nullptr; p.ldc = 0; p.err = err;
+    p.rows_per = TILE_ROWS;
+    p.qkv.n_heads = n_heads; p.qkv.n_kv = n_kv; p.qkv.q_norm_w = q_norm_w; p.qkv.k_norm_w = k_norm_w; p.qkv.eps = eps;
+    if (cos_sin && cs_ld < M) return fail("gemm_tc_qkv: the rotation table has %d columns for %d tokens", cs_ld, M);
+    p.qkv.cos_sin = (const float4*)cos_sin; p.qkv.cs_ld = cs_ld; p.qkv.positions = positions; p.qkv.seq_of = seq_of;
+    p.qkv.block_table = block_table; p.qkv.max_blocks = max_blocks; p.qkv.page = page; p.qkv.num_pages = num_pages;
+    p.qkv.q_out = (__nv_bfloat16*)q_out; p.qkv.k_pool = (__nv_bfloat16*)k_pool; p.qkv.v_pool = (__nv_bfloat16*)v_pool;
+    p.qkv.write_kv = write_kv;
+    const int block_cols = (N % 256 == 0) ? 256 : 128;          // whole heads in a tile
+    if (split_mode != 5) {
+        const int max_pairs = pair_capacity(num_sms);
+        if (max_pairs > 0 && (split_mode == 4 || M >= 2048)) return launch_pair(A, W, p, block_cols, max_pairs, st);
+    }
+    return launch_persistent(A, W, p, block_cols, num_sms, st);
 }

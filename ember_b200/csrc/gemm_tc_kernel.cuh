@@ -17,6 +17,27 @@ constexpr int GEMM_THREADS = 192;
 constexpr int MAX_STAGES = 8;
 constexpr unsigned WAIT_LIMIT = 1u << 24;
 
+// Epilogue 4: the output columns are head slots of 128 (query heads, then key heads, then value heads); instead of
+// being stored as they are, a token's query and key heads get their RMSNorm and rotation and go to the query
+// buffer and into the token's cache page, value heads go into the cache page.
+struct QkvEpilogue {
+    int n_heads, n_kv;
+    const float* q_norm_w;          // [128] or null
+    const float* k_norm_w;
+    float eps;
+    const float4* cos_sin;          // [32][cs_ld] (cos, sin) of position * inv_freq for frequencies 2j and 2j + 1 of token t
+                                    // at [j][t]: the lanes of a warp (neighbouring tokens) read neighbouring 16 bytes; null: no rotation
+    int cs_ld;
+    const int* positions;           // [tokens]
+    const int* seq_of;              // [tokens] -> row of the block table
+    const int* block_table;
+    int max_blocks, page, num_pages;
+    __nv_bfloat16* q_out;           // [tokens][n_heads][128]
+    __nv_bfloat16* k_pool;          // [pages][n_kv][page][128]
+    __nv_bfloat16* v_pool;
+    int write_kv;
+};
+
 struct GemmTcParams {
     int M, N, K;
     int swapped;          // 0: accumulator rows are tokens; 1: accumulator rows are weight rows
@@ -35,6 +56,7 @@ struct GemmTcParams {
     int total_tiles;
     int tmem_cols;
     int* err;
+    QkvEpilogue qkv;      // epilogue 4 only
 };
 
 // ------------------------------------------------------------------------------ PTX helpers
@@ -112,6 +134,15 @@ __device__ __forceinline__ void tmem_ld16(uint32_t taddr, float* v) {
     for (int i = 0; i < 16; i++) v[i] = __uint_as_float(r[i]);
 }
 
+// 64 consecutive columns of this thread's lane; the caller waits (tcgen05.wait::ld) before it uses them.
+__device__ __forceinline__ void tmem_ld64_nowait(uint32_t taddr, uint32_t* r) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x64.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32, %33, %34, %35, %36, %37, %38, %39, %40, %41, %42, %43, %44, %45, %46, %47, %48, %49, %50, %51, %52, %53, %54, %55, %56, %57, %58, %59, %60, %61, %62, %63}, [%64];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31]), "=r"(r[32]), "=r"(r[33]), "=r"(r[34]), "=r"(r[35]), "=r"(r[36]), "=r"(r[37]), "=r"(r[38]), "=r"(r[39]), "=r"(r[40]), "=r"(r[41]), "=r"(r[42]), "=r"(r[43]), "=r"(r[44]), "=r"(r[45]), "=r"(r[46]), "=r"(r[47]), "=r"(r[48]), "=r"(r[49]), "=r"(r[50]), "=r"(r[51]), "=r"(r[52]), "=r"(r[53]), "=r"(r[54]), "=r"(r[55]), "=r"(r[56]), "=r"(r[57]), "=r"(r[58]), "=r"(r[59]), "=r"(r[60]), "=r"(r[61]), "=r"(r[62]), "=r"(r[63])
+        : "r"(taddr));
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
 __device__ __forceinline__ uint32_t map_to_rank(uint32_t smem_addr, uint32_t rank) {
     uint32_t r;
     asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
@@ -181,6 +212,94 @@ __device__ __forceinline__ void store_chunk_normal(const GemmTcParams& p, int m,
             *(uint4*)dst = q;
         } else {
             for (int j = 0; j + 1 < nv; j += 2) dst[j >> 1] = __float2bfloat16_rn(silu_mul(v[j], v[j + 1]));
+        }
+    }
+}
+
+// Epilogue 4 for one token row (normal orientation): `heads` head slots of 128 accumulator columns starting at
+// tensor-memory address `taddr` (this thread's lane) and at head slot `slot0`.  All of a head is in this thread's
+// lane, so the norm is a sum over 128 columns read once and the rotation pairs columns i and i + 64 of a second
+// read; the sums, the norm and the rotation are fp32 on the fp32 accumulator, rounded to bf16 once.
+// Every lane runs the tensor-memory loads (they are warp-wide); `live` says whether this row is stored.
+__device__ __forceinline__ void store_heads_normal(const GemmTcParams& p, int m, int slot0, int heads, uint32_t taddr, bool live) {
+    const QkvEpilogue& e = p.qkv;
+    int pos = 0;
+    size_t kv_off = 0;
+    bool kv_ok = false;
+    if (live) {
+        pos = e.positions[m];
+        if (e.write_kv) {
+            const int blk = e.block_table[(size_t)e.seq_of[m] * e.max_blocks + pos / e.page];
+            if (blk < 0 || blk >= e.num_pages) {
+                if (p.err) atomicOr(p.err, EMBER_ERR_PAGE_RANGE);
+            } else {
+                kv_ok = true;
+                kv_off = ((size_t)blk * e.n_kv * e.page + (size_t)(pos % e.page)) * 128;
+            }
+        }
+    }
+    const float4* cs_row = e.cos_sin ? e.cos_sin + (live ? m : 0) : nullptr;
+    for (int h = 0; h < heads; h++) {
+        const int slot = slot0 + h;
+        const int kind = slot < e.n_heads ? 0 : (slot < e.n_heads + e.n_kv ? 1 : 2);       // q, k, v
+        // the whole head in registers: one round trip to tensor memory instead of one per 16 columns
+        uint32_t u[128];
+        tmem_ld64_nowait(taddr + (uint32_t)(h * 128), u);
+        tmem_ld64_nowait(taddr + (uint32_t)(h * 128 + 64), u + 64);
+        tmem_wait_ld();
+        __nv_bfloat16* dst = nullptr;
+        if (live) {
+            if (kind == 0) dst = e.q_out + ((size_t)m * e.n_heads + slot) * 128;
+            else if (kv_ok) dst = (kind == 1 ? e.k_pool : e.v_pool) + kv_off + (size_t)(slot - e.n_heads - (kind == 2 ? e.n_kv : 0)) * e.page * 128;
+        }
+        if (!dst) continue;
+        const float* nw = kind == 0 ? e.q_norm_w : (kind == 1 ? e.k_norm_w : nullptr);
+        float scale = 1.0f;
+        if (nw) {
+            float s0 = 0.0f, s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
+#pragma unroll
+            for (int i = 0; i < 128; i += 4) {
+                const float x0 = __uint_as_float(u[i]), x1 = __uint_as_float(u[i + 1]), x2 = __uint_as_float(u[i + 2]), x3 = __uint_as_float(u[i + 3]);
+                s0 = fmaf(x0, x0, s0); s1 = fmaf(x1, x1, s1); s2 = fmaf(x2, x2, s2); s3 = fmaf(x3, x3, s3);
+            }
+            scale = 1.0f / sqrtf(((s0 + s1) + (s2 + s3)) / 128.0f + e.eps);
+        }
+        const bool turn = kind != 2 && cs_row != nullptr;
+#pragma unroll
+        for (int c = 0; c < 8; c++) {                               // columns 8c .. 8c + 7 and their partners 64 further
+            float a[8], b[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                a[i] = __uint_as_float(u[c * 8 + i]);
+                b[i] = __uint_as_float(u[64 + c * 8 + i]);
+            }
+            if (nw) {
+                const float4 ga0 = __ldg(reinterpret_cast<const float4*>(nw + c * 8)), ga1 = __ldg(reinterpret_cast<const float4*>(nw + c * 8 + 4));
+                const float4 gb0 = __ldg(reinterpret_cast<const float4*>(nw + 64 + c * 8)), gb1 = __ldg(reinterpret_cast<const float4*>(nw + 64 + c * 8 + 4));
+                a[0] = ga0.x * (a[0] * scale); a[1] = ga0.y * (a[1] * scale); a[2] = ga0.z * (a[2] * scale); a[3] = ga0.w * (a[3] * scale);
+                a[4] = ga1.x * (a[4] * scale); a[5] = ga1.y * (a[5] * scale); a[6] = ga1.z * (a[6] * scale); a[7] = ga1.w * (a[7] * scale);
+                b[0] = gb0.x * (b[0] * scale); b[1] = gb0.y * (b[1] * scale); b[2] = gb0.z * (b[2] * scale); b[3] = gb0.w * (b[3] * scale);
+                b[4] = gb1.x * (b[4] * scale); b[5] = gb1.y * (b[5] * scale); b[6] = gb1.z * (b[6] * scale); b[7] = gb1.w * (b[7] * scale);
+            }
+            if (turn) {
+#pragma unroll
+                for (int i = 0; i < 8; i += 2) {
+                    const float4 t = __ldg(cs_row + (size_t)((c * 8 + i) / 2) * e.cs_ld);      // (cos, sin) of two frequencies
+                    const float a0 = a[i] * t.x - b[i] * t.y, b0 = b[i] * t.x + a[i] * t.y;
+                    const float a1 = a[i + 1] * t.z - b[i + 1] * t.w, b1 = b[i + 1] * t.z + a[i + 1] * t.w;
+                    a[i] = a0; b[i] = b0; a[i + 1] = a1; b[i + 1] = b1;
+                }
+            }
+            uint4 qa, qb;
+            __nv_bfloat162* ha = (__nv_bfloat162*)&qa;
+            __nv_bfloat162* hb = (__nv_bfloat162*)&qb;
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                ha[j] = __floats2bfloat162_rn(a[2 * j], a[2 * j + 1]);
+                hb[j] = __floats2bfloat162_rn(b[2 * j], b[2 * j + 1]);
+            }
+            *(uint4*)(dst + c * 8) = qa;
+            *(uint4*)(dst + 64 + c * 8) = qb;
         }
     }
 }
@@ -520,12 +639,17 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_rows, const __
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t taddr_row = tmem_d + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * p.block_cols);
             const int m = row_tile * TILE_ROWS + r;
-            for (int c0 = 0; c0 < p.block_cols; c0 += 16) {
-                float v[16];
-                tmem_ld16(taddr_row + (uint32_t)c0, v);
-                const int n0 = col_tile * p.block_cols + c0;
-                if (!ok || m >= p.M || n0 >= p.N) continue;
-                store_chunk_normal(p, m, n0, min(16, p.N - n0), v);
+            if (p.epilogue == 4) {
+                const int slot0 = col_tile * (p.block_cols >> 7);
+                store_heads_normal(p, m, slot0, min(p.block_cols >> 7, (p.N >> 7) - slot0), taddr_row, ok && m < p.M);
+            } else {
+                for (int c0 = 0; c0 < p.block_cols; c0 += 16) {
+                    float v[16];
+                    tmem_ld16(taddr_row + (uint32_t)c0, v);
+                    const int n0 = col_tile * p.block_cols + c0;
+                    if (!ok || m >= p.M || n0 >= p.N) continue;
+                    store_chunk_normal(p, m, n0, min(16, p.N - n0), v);
+                }
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();

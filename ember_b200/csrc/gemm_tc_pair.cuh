@@ -169,12 +169,17 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t taddr_row = tmem_d + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * p.block_cols);
             const int m = row_tile * 2 * TILE_ROWS + (int)rank * TILE_ROWS + r;
-            for (int c0 = 0; c0 < p.block_cols; c0 += 16) {
-                float v[16];
-                tmem_ld16(taddr_row + (uint32_t)c0, v);
-                const int n0 = col_tile * p.block_cols + c0;
-                if (!ok || m >= p.M || n0 >= p.N) continue;
-                store_chunk_normal(p, m, n0, min(16, p.N - n0), v);
+            if (p.epilogue == 4) {
+                const int slot0 = col_tile * (p.block_cols >> 7);
+                store_heads_normal(p, m, slot0, min(p.block_cols >> 7, (p.N >> 7) - slot0), taddr_row, ok && m < p.M);
+            } else {
+                for (int c0 = 0; c0 < p.block_cols; c0 += 16) {
+                    float v[16];
+                    tmem_ld16(taddr_row + (uint32_t)c0, v);
+                    const int n0 = col_tile * p.block_cols + c0;
+                    if (!ok || m >= p.M || n0 >= p.N) continue;
+                    store_chunk_normal(p, m, n0, min(16, p.N - n0), v);
+                }
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();

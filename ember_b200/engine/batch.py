@@ -258,6 +258,7 @@ class StepContext:
         self.ints = workspace.dynamic("step.ints", max(self._total, 1 << 16), torch.int32)
         self._ng = len(self._table_shapes)
         self._tiles = {}
+        self.memo = {}                # what parts compute once per step and share between layers
         if upload:
             self.upload()
 

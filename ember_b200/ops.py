@@ -308,6 +308,73 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, M: int, epilogu
           c_void_p(stream if stream is not None else current_stream_ptr()))
 
 
+def gemm_tc_qkv_usable(x: torch.Tensor, w: torch.Tensor, bias, M: int, n_heads: int, n_kv: int, head_dim: int,
+                       rotary: int) -> bool:
+    """Whether the fused projection takes this step: bf16, no bias, heads of 128 rotated whole (or not at all),
+    more than 128 tokens (the rule of ember_gemm_tc_qkv_supported)."""
+    if not gemm_tc_usable(x, w, bias, EPI_STORE):
+        return False
+    n, k = w.shape
+    return M > 128 and head_dim == 128 and rotary in (0, 128) and n == (n_heads + 2 * n_kv) * 128
+
+
+# From how many tokens on a step's q/k/v product finishes the heads itself.  Measured at the 1.7B shape, product +
+# head kernel against the fused product: 23.3 / 24.7 us at 512 tokens, 28.1 / 24.4 at 1,024, 42.4 / 37.4 at 2,048,
+# 74.8 / 57.9 at 4,096 (the longer epilogue shares its SM's issue slots with the thread that issues the MMAs, and
+# with few tiles per SM there is no next tile to hide it behind).
+QKV_FUSE_MIN_TOKENS = 1024
+
+
+def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, T: int, out: torch.Tensor, stream: Optional[int] = None) -> None:
+    """out[i // 2, t] = (cos_i, sin_i, cos_{i+1}, sin_{i+1}) of float(positions[t]) * inv_freq[i] in fp32;
+    ``out`` is [frequencies / 2, tokens a row, 4] (token-minor: what the rotating epilogue reads)."""
+    _check(positions, "positions", torch.int32)
+    _check(inv_freq, "inv_freq", torch.float32)
+    _check(out, "out", torch.float32)
+    half = inv_freq.numel()
+    if out.dim() != 3 or out.shape[0] != half // 2 or out.shape[2] != 4 or out.shape[1] < T or half % 2:
+        raise KernelError(f"rope_table: output {tuple(out.shape)} for {half} frequencies and {T} tokens")
+    lib = _lib("elementwise")
+    _call(lib, lib.ember_rope_table, _p(positions), _p(inv_freq), c_int(T), c_int(half), c_int(out.shape[1]), _p(out),
+          c_void_p(stream if stream is not None else current_stream_ptr()))
+
+
+def gemm_tc_qkv(a: torch.Tensor, w: torch.Tensor, M: int, n_heads: int, n_kv: int, q_norm_w: Optional[torch.Tensor],
+                k_norm_w: Optional[torch.Tensor], eps: float, cos_sin: Optional[torch.Tensor], positions: torch.Tensor,
+                seq_of: torch.Tensor, block_table: torch.Tensor, page: int, k_pool: torch.Tensor, v_pool: torch.Tensor,
+                q_out: torch.Tensor, write_kv: bool = True, err: Optional[torch.Tensor] = None,
+                stream: Optional[int] = None, split_mode: int = 0) -> None:
+    """[q | k | v] = a[:M] @ w.T on the tcgen05 tensor cores with the heads finished in the epilogue: RMSNorm and
+    rotation of query and key heads in fp32 on the accumulator, queries to ``q_out``, keys and values into their
+    cache pages.  ``cos_sin`` [32, tokens a row, 4] comes from ``rope_table`` (None: no rotation).  Heads are 128 wide."""
+    _check(a, "a", torch.bfloat16)
+    _check(w, "w", torch.bfloat16)
+    _check(q_out, "q_out", torch.bfloat16)
+    _check(k_pool, "k_pool", torch.bfloat16)
+    _check(v_pool, "v_pool", torch.bfloat16)
+    _check(positions, "positions", torch.int32)
+    _check(seq_of, "seq_of", torch.int32)
+    _check(block_table, "block_table", torch.int32)
+    for t, n in ((q_norm_w, "q_norm_w"), (k_norm_w, "k_norm_w"), (cos_sin, "cos_sin")):
+        if t is not None:
+            _check(t, n, torch.float32)
+    N, K = w.shape
+    if a.shape[-1] != K or a.numel() < M * K:
+        raise KernelError(f"gemm_qkv: activations {tuple(a.shape)} against weights {tuple(w.shape)} for M={M}")
+    if k_pool.dim() != 4 or tuple(k_pool.shape[1:]) != (n_kv, page, 128) or v_pool.shape != k_pool.shape:
+        raise KernelError(f"gemm_qkv: pools {tuple(k_pool.shape)} are not [pages, {n_kv}, {page}, 128]")
+    if q_out.numel() < M * n_heads * 128 or positions.numel() < M or seq_of.numel() < M:
+        raise KernelError("gemm_qkv: query buffer or token arrays too small")
+    if cos_sin is not None and (cos_sin.dim() != 3 or cos_sin.shape[0] != 32 or cos_sin.shape[1] < M or cos_sin.shape[2] != 4):
+        raise KernelError(f"gemm_qkv: rotation table {tuple(cos_sin.shape)} is not [32, >= {M}, 4]")
+    lib = _lib("gemm_tc")
+    _call(lib, lib.ember_gemm_tc_qkv, _p(a), _p(w), c_int(M), c_int(N), c_int(K), c_int(n_heads), c_int(n_kv),
+          _p(q_norm_w), _p(k_norm_w), c_float(eps), _p(cos_sin), c_int(cos_sin.shape[1] if cos_sin is not None else 0), _p(positions), _p(seq_of), _p(block_table),
+          c_int(block_table.shape[-1]), c_int(page), c_int(k_pool.shape[0]), _p(q_out), _p(k_pool), _p(v_pool),
+          c_int(1 if write_kv else 0), c_int(_sms(a.device)), c_int(split_mode), _p(err),
+          c_void_p(stream if stream is not None else current_stream_ptr()))
+
+
 def num_sms(device) -> int:
     return _sms(device)
 

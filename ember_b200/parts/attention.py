@@ -86,14 +86,24 @@ class Attention(Mixer):
         qkv = ctx.buf("attention.qkv", (mt, s.q_dim + 2 * s.kv_dim), rt.dtype)
         q = ctx.buf("attention.q", (mt, s.q_dim), rt.dtype)
         att = ctx.buf("attention.out", (mt, s.q_dim), rt.dtype)
-        self.qkv(ctx, x, qkv, T, ops.EPI_STORE)
         table = ctx.block_table(cache.group)
-        ops.qk_norm_rope_store(qkv, T, s.num_heads, s.num_kv_heads, s.head_dim, self.q_norm_w, self.k_norm_w,
-                               s.qk_norm_eps, self.inv_freq, self.rotary, ctx.positions, ctx.seq_of, table,
-                               cache.page_tokens, cache.k, cache.v, q, write_kv=owns_cache, err=ctx.err,
-                               stream=ctx.stream)
+        if self.FUSE_QKV and T >= ops.QKV_FUSE_MIN_TOKENS and ops.gemm_tc_qkv_usable(x, self.qkv.weight, self.qkv.bias, T, s.num_heads, s.num_kv_heads,
+                                                    s.head_dim, self.rotary if self.inv_freq is not None else 0):
+            # a prompt portion: norm, rotation and the cache write happen in the product's epilogue
+            cos_sin = self.position.cos_sin(ctx, rt) if self.inv_freq is not None and self.rotary else None
+            ops.gemm_tc_qkv(x, self.qkv.weight, T, s.num_heads, s.num_kv_heads, self.q_norm_w, self.k_norm_w,
+                            s.qk_norm_eps, cos_sin, ctx.positions, ctx.seq_of, table, cache.page_tokens, cache.k, cache.v,
+                            q, write_kv=owns_cache, err=ctx.err, stream=ctx.stream)
+        else:
+            self.qkv(ctx, x, qkv, T, ops.EPI_STORE)
+            ops.qk_norm_rope_store(qkv, T, s.num_heads, s.num_kv_heads, s.head_dim, self.q_norm_w, self.k_norm_w,
+                                   s.qk_norm_eps, self.inv_freq, self.rotary, ctx.positions, ctx.seq_of, table,
+                                   cache.page_tokens, cache.k, cache.v, q, write_kv=owns_cache, err=ctx.err,
+                                   stream=ctx.stream)
         self.attend(ctx, q, cache, table, att)
         self.o(ctx, att, residual, T, ops.EPI_ADD_F32)
+
+    FUSE_QKV = True     # prompt portions: finish the heads in the epilogue of the q/k/v product
 
     def _tc_modes(self):
         """(prompt portions, single tokens): whether the tensor-core kernels take this geometry."""

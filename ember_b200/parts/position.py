@@ -12,6 +12,7 @@ from __future__ import annotations
 import numpy as np
 import torch
 
+from .. import ops
 from ..config.spec import ConfigError
 from .base import PositionEncoding, Runtime
 from .registry import register_part
@@ -34,6 +35,20 @@ class RotaryEmbedding(PositionEncoding):
         if self._table is None or self._table.device != rt.device:
             self._table = torch.from_numpy(self.inv_freq()).to(rt.device)
         return self._table, self.spec.rotary_dim
+
+    def cos_sin(self, ctx, rt: Runtime) -> torch.Tensor:
+        """[rotary / 4, tokens, 4] (cos, sin) pairs of the step's positions (the layout of ``ops.rope_table``), made
+        once per step and shared by the layers that use this table (fp32, the angle float(position) * inv_freq as
+        everywhere)."""
+        inv, _ = self.rotary_table(rt)
+        key = ("rope.cos_sin", inv.data_ptr())
+        got = ctx.memo.get(key)
+        if got is None:
+            half = inv.numel()
+            got = ctx.buf(f"rope.cos_sin.{half}.{inv.data_ptr()}", (half // 2, ctx.max_tokens, 4), torch.float32)
+            ops.rope_table(ctx.positions, inv, ctx.T, got, stream=ctx.stream)
+            ctx.memo[key] = got
+        return got
 
 
 class NoPosition(PositionEncoding):

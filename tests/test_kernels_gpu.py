@@ -348,3 +348,71 @@ def test_attention_fa_many_blocks(heads, kv, page, window):
         worst = ((out.float().view(T, heads, D) - want).norm(dim=-1) / want.norm(dim=-1)).max()
         assert float(worst) < 2e-2                           # every row, not only the sum over rows
         assert rel(out.float().view(T, heads, D), want) < 6e-3
+
+
+@pytest.mark.parametrize("heads,kv,page,M", [(4, 2, 16, 300), (3, 1, 64, 200), (6, 2, 32, 2100), (5, 1, 16, 2304)])
+@pytest.mark.parametrize("norm,rotate", [(True, True), (False, True), (True, False)])
+def test_gemm_tc_qkv(heads, kv, page, M, norm, rotate):
+    """The fused q/k/v product: heads finished in the epilogue (norm, rotation, cache write) against the same
+    steps computed plainly from the fp32 product.  Two runs at different depths, scattered pages; 2,100 and
+    2,304 tokens go to the kernel on pairs of SMs, the others to the single-SM kernel; 3 and 5 + 2 head slots
+    give tiles of one head, the others of two."""
+    from ember_b200 import ops
+    torch.manual_seed(heads * M + page)
+    dev, D, K = "cuda", 128, 328                       # K: no multiple of 64
+    lens = [M - 130, 130]
+    starts = [37, 1000]
+    pos = torch.cat([torch.arange(s, s + n) for s, n in zip(starts, lens)]).int().to(dev)
+    seq = torch.cat([torch.full((n,), i) for i, n in enumerate(lens)]).int().to(dev)
+    nblk = max((s + n + page - 1) // page for s, n in zip(starts, lens))
+    pages = 2 * nblk + 2
+    perm = torch.randperm(pages)[:2 * nblk].reshape(2, nblk).int().to(dev)
+    N = (heads + 2 * kv) * D
+    a = (torch.randn(M, K, device=dev) * 0.5).bfloat16()
+    w = (torch.randn(N, K, device=dev) * 0.1).bfloat16()
+    qw, kw = (1 + 0.1 * torch.randn(D, device=dev), 1 + 0.1 * torch.randn(D, device=dev)) if norm else (None, None)
+    inv = 1.0 / (10000.0 ** (torch.arange(D // 2, device=dev).float() * 2 / D))
+    assert ops.gemm_tc_qkv_usable(a, w, None, M, heads, kv, D, D if rotate else 0)
+    cs = None
+    if rotate:
+        cs = torch.empty(D // 4, M + 8, 4, device=dev)          # rows longer than the step
+        ops.rope_table(pos, inv, M, cs)
+        ang = pos.float()[None, :] * inv[:, None]                # [frequency, token]
+        got = cs[:, :M].view(D // 4, M, 2, 2).permute(0, 2, 1, 3).reshape(D // 2, M, 2)
+        assert torch.allclose(got[..., 0], torch.cos(ang), atol=2e-6) and torch.allclose(got[..., 1], torch.sin(ang), atol=2e-6)
+    x = a.float() @ w.float().t()
+    qq, kk, vv = x[:, :heads * D].view(M, heads, D), x[:, heads * D:(heads + kv) * D].view(M, kv, D), x[:, (heads + kv) * D:].view(M, kv, D)
+
+    def nrm(t, g):
+        return g * (t * torch.rsqrt((t.double() ** 2).mean(-1, keepdim=True) + 1e-5).float()) if norm else t
+
+    qq, kk = nrm(qq, qw), nrm(kk, kw)
+    if rotate:
+        qq, kk = rope_ref(qq, pos, inv, D), rope_ref(kk, pos, inv, D)
+    for write_kv in (True, False):
+        kp = torch.zeros(pages, kv, page, D, device=dev, dtype=torch.bfloat16)
+        vp = torch.zeros_like(kp)
+        q = torch.zeros(M, heads * D, device=dev, dtype=torch.bfloat16)
+        err = torch.zeros(1, dtype=torch.int32, device=dev)
+        ops.gemm_tc_qkv(a, w, M, heads, kv, qw, kw, 1e-5, cs, pos, seq, perm, page, kp, vp, q, write_kv=write_kv, err=err)
+        assert int(err.item()) == 0
+        assert rel(q.float().view(M, heads, D), qq) < 5e-3
+        worst = ((q.float().view(M, heads, D) - qq).norm(dim=-1) / qq.norm(dim=-1)).max()
+        assert float(worst) < 1.5e-2                          # every head of every token
+        if not write_kv:
+            assert float(kp.abs().max()) == 0.0 and float(vp.abs().max()) == 0.0
+            continue
+        blk = perm[seq.long(), (pos // page).long()].long()
+        slot = (pos % page).long()
+        assert rel(kp[blk, :, slot].float(), kk) < 5e-3
+        assert rel(vp[blk, :, slot].float(), vv) < 5e-3
+        written = torch.zeros(pages, page, dtype=torch.bool, device=dev)
+        written[blk, slot] = True
+        untouched = kp.permute(0, 2, 1, 3)[~written]
+        assert float(untouched.abs().max() if untouched.numel() else 0) == 0.0
+    # a page id outside the pool is recorded, not written
+    bad = perm.clone()
+    bad[0, starts[0] // page] = pages + 5
+    err = torch.zeros(1, dtype=torch.int32, device=dev)
+    ops.gemm_tc_qkv(a, w, M, heads, kv, qw, kw, 1e-5, cs, pos, seq, bad, page, kp, vp, q, err=err)
+    assert int(err.item()) == 2
