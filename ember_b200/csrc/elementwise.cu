@@ -343,8 +343,8 @@ qk_norm_rope_store_d128_kernel(
 }
 
 // The angles of a step's tokens, made once per step for the products that rotate in their epilogue (the same fp32
-// expression as the kernels above): out[i / 2][t] = (cos, sin) of float(position[t]) * inv_freq[i] for frequencies
-// i and i + 1, rows `ld` tokens long.  Token-minor, so that threads that hold neighbouring tokens read neighbouring
+// expression as the kernels above): out[i / 2][t] = (cos_i, cos_i+1, sin_i, sin_i+1) of float(position[t]) * inv_freq for
+// frequencies i and i + 1, rows `ld` tokens long.  Token-minor, so that threads that hold neighbouring tokens read neighbouring
 // 16 bytes.
 __global__ void rope_table_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq, int T, int half,
                                   int ld, float4* __restrict__ out) {
@@ -358,7 +358,7 @@ __global__ void rope_table_kernel(const int* __restrict__ positions, const float
     float s0, c0, s1, c1;
     sincosf(pos * inv_freq[2 * j], &s0, &c0);
     sincosf(pos * inv_freq[2 * j + 1], &s1, &c1);
-    out[(size_t)j * ld + t] = make_float4(c0, s0, c1, s1);
+    out[(size_t)j * ld + t] = make_float4(c0, c1, s0, s1);
 }
 
 // out[m, j] = silu(x[m, 2j]) * x[m, 2j+1] for an unfused gate/up product (interleaved rows).

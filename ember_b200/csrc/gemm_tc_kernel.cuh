@@ -25,8 +25,8 @@ struct QkvEpilogue {
     const float* q_norm_w;          // [128] or null
     const float* k_norm_w;
     float eps;
-    const float4* cos_sin;          // [32][cs_ld] (cos, sin) of position * inv_freq for frequencies 2j and 2j + 1 of token t
-                                    // at [j][t]: the lanes of a warp (neighbouring tokens) read neighbouring 16 bytes; null: no rotation
+    const float4* cos_sin;          // [32][cs_ld] (cos, cos, sin, sin) of position * inv_freq for frequencies 2j and 2j + 1 of
+                                    // token t at [j][t]: the lanes of a warp (neighbouring tokens) read neighbouring 16 bytes; null: no rotation
     int cs_ld;
     const int* positions;           // [tokens]
     const int* seq_of;              // [tokens] -> row of the block table
@@ -216,90 +216,163 @@ __device__ __forceinline__ void store_chunk_normal(const GemmTcParams& p, int m,
     }
 }
 
-// Epilogue 4 for one token row (normal orientation): `heads` head slots of 128 accumulator columns starting at
-// tensor-memory address `taddr` (this thread's lane) and at head slot `slot0`.  All of a head is in this thread's
-// lane, so the norm is a sum over 128 columns read once and the rotation pairs columns i and i + 64 of a second
-// read; the sums, the norm and the rotation are fp32 on the fp32 accumulator, rounded to bf16 once.
-// Every lane runs the tensor-memory loads (they are warp-wide); `live` says whether this row is stored.
-__device__ __forceinline__ void store_heads_normal(const GemmTcParams& p, int m, int slot0, int heads, uint32_t taddr, bool live) {
+// Packed fp32 pairs (one instruction for two lanes of arithmetic: the epilogue below shares its SM's issue slots
+// with the thread that issues the MMAs, so its instruction count is what it costs).
+__device__ __forceinline__ unsigned long long pk2(float lo, float hi) {
+    unsigned long long r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(__float_as_uint(lo)), "r"(__float_as_uint(hi)));
+    return r;
+}
+__device__ __forceinline__ void unpk2(unsigned long long v, float& lo, float& hi) {
+    uint32_t a, b;
+    asm("mov.b64 {%0, %1}, %2;" : "=r"(a), "=r"(b) : "l"(v));
+    lo = __uint_as_float(a);
+    hi = __uint_as_float(b);
+}
+__device__ __forceinline__ unsigned long long mul2(unsigned long long a, unsigned long long b) {
+    unsigned long long d;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(d) : "l"(a), "l"(b));
+    return d;
+}
+__device__ __forceinline__ unsigned long long fma2(unsigned long long a, unsigned long long b, unsigned long long c) {
+    unsigned long long d;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(d) : "l"(a), "l"(b), "l"(c));
+    return d;
+}
+
+// Epilogue 4 for one token row (normal orientation), in two steps.
+// Before the accumulator is waited for: where the row's keys and values go, and its 64 angles (32 registers of
+// (cos, cos, sin, sin) pairs), so that these loads' latency hides behind the wait; the angles serve every head of
+// the tile.
+struct QkvRow {
+    unsigned long long cs[64];      // [2j], [2j + 1] = (cos, cos), (sin, sin) of frequencies 2j, 2j + 1
+    size_t kv_off;
+    int m;
+    bool live, kv_ok, turn;
+};
+__device__ __forceinline__ void qkv_row_prepare(const GemmTcParams& p, int m, bool live, QkvRow& row) {
     const QkvEpilogue& e = p.qkv;
-    int pos = 0;
-    size_t kv_off = 0;
-    bool kv_ok = false;
-    if (live) {
-        pos = e.positions[m];
-        if (e.write_kv) {
-            const int blk = e.block_table[(size_t)e.seq_of[m] * e.max_blocks + pos / e.page];
-            if (blk < 0 || blk >= e.num_pages) {
-                if (p.err) atomicOr(p.err, EMBER_ERR_PAGE_RANGE);
-            } else {
-                kv_ok = true;
-                kv_off = ((size_t)blk * e.n_kv * e.page + (size_t)(pos % e.page)) * 128;
-            }
+    row.m = m;
+    row.live = live;
+    row.kv_ok = false;
+    row.kv_off = 0;
+    row.turn = e.cos_sin != nullptr;
+    if (live && e.write_kv) {
+        const int pos = e.positions[m];
+        const int blk = e.block_table[(size_t)e.seq_of[m] * e.max_blocks + pos / e.page];
+        if (blk < 0 || blk >= e.num_pages) {
+            if (p.err) atomicOr(p.err, EMBER_ERR_PAGE_RANGE);
+        } else {
+            row.kv_ok = true;
+            row.kv_off = ((size_t)blk * e.n_kv * e.page + (size_t)(pos % e.page)) * 128;
         }
     }
-    const float4* cs_row = e.cos_sin ? e.cos_sin + (live ? m : 0) : nullptr;
+    if (row.turn) {
+        const float4* src = e.cos_sin + (live ? m : 0);
+#pragma unroll
+        for (int j = 0; j < 32; j++) {
+            const ulonglong2 t = __ldg(reinterpret_cast<const ulonglong2*>(src + (size_t)j * e.cs_ld));
+            row.cs[2 * j] = t.x;
+            row.cs[2 * j + 1] = t.y;
+        }
+    }
+}
+// Once the accumulator is complete: `heads` head slots of 128 columns starting at tensor-memory address `taddr`
+// (this thread's lane) and at head slot `slot0`.  All of a head is in this thread's lane: the norm is a sum over
+// the 128 columns (a first pass over tensor memory), the rotation pairs columns i and i + 64 of a second pass;
+// sums, norm and rotation are fp32 on the fp32 accumulator, rounded to bf16 once.  Every lane runs the
+// tensor-memory loads (they are warp-wide); only live rows are stored.
+__device__ __forceinline__ void store_heads_normal(const GemmTcParams& p, const QkvRow& row, int slot0, int heads, uint32_t taddr) {
+    const QkvEpilogue& e = p.qkv;
     for (int h = 0; h < heads; h++) {
         const int slot = slot0 + h;
         const int kind = slot < e.n_heads ? 0 : (slot < e.n_heads + e.n_kv ? 1 : 2);       // q, k, v
-        // the whole head in registers: one round trip to tensor memory instead of one per 16 columns
-        uint32_t u[128];
-        tmem_ld64_nowait(taddr + (uint32_t)(h * 128), u);
-        tmem_ld64_nowait(taddr + (uint32_t)(h * 128 + 64), u + 64);
-        tmem_wait_ld();
-        __nv_bfloat16* dst = nullptr;
-        if (live) {
-            if (kind == 0) dst = e.q_out + ((size_t)m * e.n_heads + slot) * 128;
-            else if (kv_ok) dst = (kind == 1 ? e.k_pool : e.v_pool) + kv_off + (size_t)(slot - e.n_heads - (kind == 2 ? e.n_kv : 0)) * e.page * 128;
-        }
-        if (!dst) continue;
+        const uint32_t th = taddr + (uint32_t)(h * 128);
         const float* nw = kind == 0 ? e.q_norm_w : (kind == 1 ? e.k_norm_w : nullptr);
-        float scale = 1.0f;
-        if (nw) {
-            float s0 = 0.0f, s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
+        unsigned long long scale2 = 0;
+        if (nw) {                                                   // uniform over the block
+            unsigned long long s0 = 0, s1 = 0;                      // (+0, +0)
 #pragma unroll
-            for (int i = 0; i < 128; i += 4) {
-                const float x0 = __uint_as_float(u[i]), x1 = __uint_as_float(u[i + 1]), x2 = __uint_as_float(u[i + 2]), x3 = __uint_as_float(u[i + 3]);
-                s0 = fmaf(x0, x0, s0); s1 = fmaf(x1, x1, s1); s2 = fmaf(x2, x2, s2); s3 = fmaf(x3, x3, s3);
+            for (int half = 0; half < 2; half++) {
+                uint32_t u[64];
+                tmem_ld64_nowait(th + (uint32_t)(half * 64), u);
+                tmem_wait_ld();
+#pragma unroll
+                for (int i = 0; i < 64; i += 4) {
+                    const unsigned long long x0 = pk2(__uint_as_float(u[i]), __uint_as_float(u[i + 1]));
+                    const unsigned long long x1 = pk2(__uint_as_float(u[i + 2]), __uint_as_float(u[i + 3]));
+                    s0 = fma2(x0, x0, s0);
+                    s1 = fma2(x1, x1, s1);
+                }
             }
-            scale = 1.0f / sqrtf(((s0 + s1) + (s2 + s3)) / 128.0f + e.eps);
+            float a0, a1, b0, b1;
+            unpk2(s0, a0, a1);
+            unpk2(s1, b0, b1);
+            const float scale = 1.0f / sqrtf(((a0 + a1) + (b0 + b1)) / 128.0f + e.eps);
+            scale2 = pk2(scale, scale);
         }
-        const bool turn = kind != 2 && cs_row != nullptr;
+        __nv_bfloat16* dst = nullptr;
+        if (row.live) {
+            if (kind == 0) dst = e.q_out + ((size_t)row.m * e.n_heads + slot) * 128;
+            else if (row.kv_ok) dst = (kind == 1 ? e.k_pool : e.v_pool) + row.kv_off + (size_t)(slot - e.n_heads - (kind == 2 ? e.n_kv : 0)) * e.page * 128;
+        }
+        const bool turn = kind != 2 && row.turn;
 #pragma unroll
-        for (int c = 0; c < 8; c++) {                               // columns 8c .. 8c + 7 and their partners 64 further
-            float a[8], b[8];
+        for (int c = 0; c < 4; c++) {                               // columns 16c .. 16c + 15 and their partners 64 further
+            uint32_t ua[16], ub[16];
+            asm volatile(
+                "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+                : "=r"(ua[0]), "=r"(ua[1]), "=r"(ua[2]), "=r"(ua[3]), "=r"(ua[4]), "=r"(ua[5]), "=r"(ua[6]), "=r"(ua[7]), "=r"(ua[8]),
+                  "=r"(ua[9]), "=r"(ua[10]), "=r"(ua[11]), "=r"(ua[12]), "=r"(ua[13]), "=r"(ua[14]), "=r"(ua[15])
+                : "r"(th + (uint32_t)(c * 16)));
+            asm volatile(
+                "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15}, [%16];"
+                : "=r"(ub[0]), "=r"(ub[1]), "=r"(ub[2]), "=r"(ub[3]), "=r"(ub[4]), "=r"(ub[5]), "=r"(ub[6]), "=r"(ub[7]), "=r"(ub[8]),
+                  "=r"(ub[9]), "=r"(ub[10]), "=r"(ub[11]), "=r"(ub[12]), "=r"(ub[13]), "=r"(ub[14]), "=r"(ub[15])
+                : "r"(th + (uint32_t)(64 + c * 16)));
+            tmem_wait_ld();
+            if (!dst) continue;
+            unsigned long long a[8], b[8];
 #pragma unroll
             for (int i = 0; i < 8; i++) {
-                a[i] = __uint_as_float(u[c * 8 + i]);
-                b[i] = __uint_as_float(u[64 + c * 8 + i]);
+                a[i] = pk2(__uint_as_float(ua[2 * i]), __uint_as_float(ua[2 * i + 1]));
+                b[i] = pk2(__uint_as_float(ub[2 * i]), __uint_as_float(ub[2 * i + 1]));
             }
             if (nw) {
-                const float4 ga0 = __ldg(reinterpret_cast<const float4*>(nw + c * 8)), ga1 = __ldg(reinterpret_cast<const float4*>(nw + c * 8 + 4));
-                const float4 gb0 = __ldg(reinterpret_cast<const float4*>(nw + 64 + c * 8)), gb1 = __ldg(reinterpret_cast<const float4*>(nw + 64 + c * 8 + 4));
-                a[0] = ga0.x * (a[0] * scale); a[1] = ga0.y * (a[1] * scale); a[2] = ga0.z * (a[2] * scale); a[3] = ga0.w * (a[3] * scale);
-                a[4] = ga1.x * (a[4] * scale); a[5] = ga1.y * (a[5] * scale); a[6] = ga1.z * (a[6] * scale); a[7] = ga1.w * (a[7] * scale);
-                b[0] = gb0.x * (b[0] * scale); b[1] = gb0.y * (b[1] * scale); b[2] = gb0.z * (b[2] * scale); b[3] = gb0.w * (b[3] * scale);
-                b[4] = gb1.x * (b[4] * scale); b[5] = gb1.y * (b[5] * scale); b[6] = gb1.z * (b[6] * scale); b[7] = gb1.w * (b[7] * scale);
+#pragma unroll
+                for (int i = 0; i < 8; i += 2) {
+                    const ulonglong2 ga = __ldg(reinterpret_cast<const ulonglong2*>(nw + c * 16 + 2 * i));
+                    const ulonglong2 gb = __ldg(reinterpret_cast<const ulonglong2*>(nw + 64 + c * 16 + 2 * i));
+                    a[i] = mul2(ga.x, mul2(a[i], scale2)); a[i + 1] = mul2(ga.y, mul2(a[i + 1], scale2));
+                    b[i] = mul2(gb.x, mul2(b[i], scale2)); b[i + 1] = mul2(gb.y, mul2(b[i + 1], scale2));
+                }
             }
             if (turn) {
 #pragma unroll
-                for (int i = 0; i < 8; i += 2) {
-                    const float4 t = __ldg(cs_row + (size_t)((c * 8 + i) / 2) * e.cs_ld);      // (cos, sin) of two frequencies
-                    const float a0 = a[i] * t.x - b[i] * t.y, b0 = b[i] * t.x + a[i] * t.y;
-                    const float a1 = a[i + 1] * t.z - b[i + 1] * t.w, b1 = b[i + 1] * t.z + a[i + 1] * t.w;
-                    a[i] = a0; b[i] = b0; a[i + 1] = a1; b[i + 1] = b1;
+                for (int i = 0; i < 8; i++) {
+                    const unsigned long long cos2 = row.cs[2 * (c * 8 + i)], sin2 = row.cs[2 * (c * 8 + i) + 1];
+                    const unsigned long long nsin = sin2 ^ 0x8000000080000000ull;
+                    const unsigned long long an = fma2(a[i], cos2, mul2(b[i], nsin));      // a cos - b sin
+                    const unsigned long long bn = fma2(b[i], cos2, mul2(a[i], sin2));      // b cos + a sin
+                    a[i] = an;
+                    b[i] = bn;
                 }
             }
-            uint4 qa, qb;
-            __nv_bfloat162* ha = (__nv_bfloat162*)&qa;
-            __nv_bfloat162* hb = (__nv_bfloat162*)&qb;
+            uint4 qa[2], qb[2];
+            __nv_bfloat162* ha = (__nv_bfloat162*)qa;
+            __nv_bfloat162* hb = (__nv_bfloat162*)qb;
 #pragma unroll
-            for (int j = 0; j < 4; j++) {
-                ha[j] = __floats2bfloat162_rn(a[2 * j], a[2 * j + 1]);
-                hb[j] = __floats2bfloat162_rn(b[2 * j], b[2 * j + 1]);
+            for (int j2 = 0; j2 < 8; j2++) {
+                float lo, hi;
+                unpk2(a[j2], lo, hi);
+                ha[j2] = __floats2bfloat162_rn(lo, hi);
+                unpk2(b[j2], lo, hi);
+                hb[j2] = __floats2bfloat162_rn(lo, hi);
             }
-            *(uint4*)(dst + c * 8) = qa;
-            *(uint4*)(dst + 64 + c * 8) = qb;
+            ((uint4*)(dst + c * 16))[0] = qa[0];
+            ((uint4*)(dst + c * 16))[1] = qa[1];
+            ((uint4*)(dst + 64 + c * 16))[0] = qb[0];
+            ((uint4*)(dst + 64 + c * 16))[1] = qb[1];
         }
     }
 }
@@ -635,15 +708,31 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_rows, const __
         for (int t = blockIdx.x; t < p.total_tiles; t += gridDim.x, li++) {
             const int col_tile = t / p.row_tiles, row_tile = t - col_tile * p.row_tiles;
             const int acc = li & 1;
+            const int m = row_tile * TILE_ROWS + r;
+            QkvRow row;
+            if (p.epilogue == 4) qkv_row_prepare(p, m, ok && m < p.M, row);       // its loads travel during the wait
             if (ok) ok = mbar_wait(&tmem_full_bar[acc], (uint32_t)(li >> 1) & 1u, abort_flag);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t taddr_row = tmem_d + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * p.block_cols);
-            const int m = row_tile * TILE_ROWS + r;
             if (p.epilogue == 4) {
                 const int slot0 = col_tile * (p.block_cols >> 7);
-                store_heads_normal(p, m, slot0, min(p.block_cols >> 7, (p.N >> 7) - slot0), taddr_row, ok && m < p.M);
+                row.live = row.live && ok;
+                store_heads_normal(p, row, slot0, min(p.block_cols >> 7, (p.N >> 7) - slot0), taddr_row);
             } else {
-                for (int c0 = 0; c0 < p.block_cols; c0 += 16) {
+                // 64 columns a round trip to tensor memory (a load and its wait cost the same for 16 columns as for 64)
+                int c0 = 0;
+                for (; c0 + 64 <= p.block_cols; c0 += 64) {
+                    uint32_t u[64];
+                    tmem_ld64_nowait(taddr_row + (uint32_t)c0, u);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int q = 0; q < 4; q++) {
+                        const int n0 = col_tile * p.block_cols + c0 + q * 16;
+                        if (!ok || m >= p.M || n0 >= p.N) continue;
+                        store_chunk_normal(p, m, n0, min(16, p.N - n0), reinterpret_cast<const float*>(u + q * 16));
+                    }
+                }
+                for (; c0 < p.block_cols; c0 += 16) {
                     float v[16];
                     tmem_ld16(taddr_row + (uint32_t)c0, v);
                     const int n0 = col_tile * p.block_cols + c0;

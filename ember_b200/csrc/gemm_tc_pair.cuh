@@ -165,15 +165,31 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
         for (int t = pair; t < p.total_tiles; t += n_pairs, li++) {
             const int col_tile = t / p.row_tiles, row_tile = t - col_tile * p.row_tiles;
             const int acc = li & 1;
+            const int m = row_tile * 2 * TILE_ROWS + (int)rank * TILE_ROWS + r;
+            QkvRow row;
+            if (p.epilogue == 4) qkv_row_prepare(p, m, ok && m < p.M, row);       // its loads travel during the wait
             if (ok) ok = mbar_wait(&tmem_full_bar[acc], (uint32_t)(li >> 1) & 1u, abort_flag);
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const uint32_t taddr_row = tmem_d + ((uint32_t)(quad * 32) << 16) + (uint32_t)(acc * p.block_cols);
-            const int m = row_tile * 2 * TILE_ROWS + (int)rank * TILE_ROWS + r;
             if (p.epilogue == 4) {
                 const int slot0 = col_tile * (p.block_cols >> 7);
-                store_heads_normal(p, m, slot0, min(p.block_cols >> 7, (p.N >> 7) - slot0), taddr_row, ok && m < p.M);
+                row.live = row.live && ok;
+                store_heads_normal(p, row, slot0, min(p.block_cols >> 7, (p.N >> 7) - slot0), taddr_row);
             } else {
-                for (int c0 = 0; c0 < p.block_cols; c0 += 16) {
+                // 64 columns a round trip to tensor memory (a load and its wait cost the same for 16 columns as for 64)
+                int c0 = 0;
+                for (; c0 + 64 <= p.block_cols; c0 += 64) {
+                    uint32_t u[64];
+                    tmem_ld64_nowait(taddr_row + (uint32_t)c0, u);
+                    tmem_wait_ld();
+#pragma unroll
+                    for (int q = 0; q < 4; q++) {
+                        const int n0 = col_tile * p.block_cols + c0 + q * 16;
+                        if (!ok || m >= p.M || n0 >= p.N) continue;
+                        store_chunk_normal(p, m, n0, min(16, p.N - n0), reinterpret_cast<const float*>(u + q * 16));
+                    }
+                }
+                for (; c0 < p.block_cols; c0 += 16) {
                     float v[16];
                     tmem_ld16(taddr_row + (uint32_t)c0, v);
                     const int n0 = col_tile * p.block_cols + c0;

@@ -319,14 +319,14 @@ def gemm_tc_qkv_usable(x: torch.Tensor, w: torch.Tensor, bias, M: int, n_heads: 
 
 
 # From how many tokens on a step's q/k/v product finishes the heads itself.  Measured at the 1.7B shape, product +
-# head kernel against the fused product: 23.3 / 24.7 us at 512 tokens, 28.1 / 24.4 at 1,024, 42.4 / 37.4 at 2,048,
-# 74.8 / 57.9 at 4,096 (the longer epilogue shares its SM's issue slots with the thread that issues the MMAs, and
-# with few tiles per SM there is no next tile to hide it behind).
-QKV_FUSE_MIN_TOKENS = 1024
+# head kernel against the fused product: 18.2 / 18.8 us at 256 tokens, 19.7 / 18.8 at 512, 38.2 / 29.3 at 2,048,
+# 74.5 / 51.3 at 4,096 (below, the step is one or two tiles an SM and the longer epilogue has no next tile to
+# hide behind).
+QKV_FUSE_MIN_TOKENS = 512
 
 
 def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, T: int, out: torch.Tensor, stream: Optional[int] = None) -> None:
-    """out[i // 2, t] = (cos_i, sin_i, cos_{i+1}, sin_{i+1}) of float(positions[t]) * inv_freq[i] in fp32;
+    """out[i // 2, t] = (cos_i, cos_{i+1}, sin_i, sin_{i+1}) of float(positions[t]) * inv_freq[i] in fp32;
     ``out`` is [frequencies / 2, tokens a row, 4] (token-minor: what the rotating epilogue reads)."""
     _check(positions, "positions", torch.int32)
     _check(inv_freq, "inv_freq", torch.float32)

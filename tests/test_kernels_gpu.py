@@ -378,7 +378,7 @@ def test_gemm_tc_qkv(heads, kv, page, M, norm, rotate):
         cs = torch.empty(D // 4, M + 8, 4, device=dev)          # rows longer than the step
         ops.rope_table(pos, inv, M, cs)
         ang = pos.float()[None, :] * inv[:, None]                # [frequency, token]
-        got = cs[:, :M].view(D // 4, M, 2, 2).permute(0, 2, 1, 3).reshape(D // 2, M, 2)
+        got = cs[:, :M].view(D // 4, M, 2, 2).permute(0, 3, 1, 2).reshape(D // 2, M, 2)      # (cos, cos, sin, sin) per pair
         assert torch.allclose(got[..., 0], torch.cos(ang), atol=2e-6) and torch.allclose(got[..., 1], torch.sin(ang), atol=2e-6)
     x = a.float() @ w.float().t()
     qq, kk, vv = x[:, :heads * D].view(M, heads, D), x[:, heads * D:(heads + kv) * D].view(M, kv, D), x[:, (heads + kv) * D:].view(M, kv, D)
