@@ -41,11 +41,11 @@ class RotaryEmbedding(PositionEncoding):
         once per step and shared by the layers that use this table (fp32, the angle float(position) * inv_freq as
         everywhere)."""
         inv, _ = self.rotary_table(rt)
-        key = ("rope.cos_sin", inv.data_ptr())
+        key = ("rope.cos_sin", self.spec.rotary_dim, float(self.spec.theta))     # layers with equal frequencies share it
         got = ctx.memo.get(key)
         if got is None:
             half = inv.numel()
-            got = ctx.buf(f"rope.cos_sin.{half}.{inv.data_ptr()}", (half // 2, ctx.max_tokens, 4), torch.float32)
+            got = ctx.buf(f"rope.cos_sin.{key[1]}.{key[2]}", (half // 2, ctx.max_tokens, 4), torch.float32)
             ops.rope_table(ctx.positions, inv, ctx.T, got, stream=ctx.stream)
             ctx.memo[key] = got
         return got
