@@ -90,3 +90,37 @@ def test_long_prompt_at_the_benchmark_shape(dtype, shape_dirs):
     errs = [rel_err(got[i], ref[i]) for i in range(len(rows))]
     print(f"long prompt {dtype}: worst relative error {max(errs):.3e}")
     assert max(errs) <= TOL[dtype], errs
+
+
+def test_portions_with_and_without_the_fused_head_epilogue_agree(shape_dirs):
+    """A 700-token prompt in one step (the q/k/v product finishes the heads in its epilogue) and in portions of
+    350 and of 600 + 100 (the shorter ones take the separate head kernel): the logits at positions of every
+    portion agree with the plain implementation and with each other, whichever path wrote the cache."""
+    from ember_b200 import ops
+    from ember_b200.engine.replay import TraceReplayer
+    from ember_b200.engine.runner import ModelRunner
+    from tests.replay_helpers import rel_err
+    import tempfile
+    model_dir, _, _ = shape_dirs("0.6b")
+    rng = np.random.default_rng(5)
+    toks = rng.integers(0, SHAPES["0.6b"]["vocab_size"], size=700).tolist()
+    rows = [5, 349, 350, 599, 600, 699]
+    ref = PlainQwen3(model_dir, torch.float32).logits(toks).numpy()[rows]
+    assert ops.QKV_FUSE_MIN_TOKENS <= 600
+    results = []
+    for cuts in ([700], [350, 350], [600, 100]):
+        runner = ModelRunner.from_dir(model_dir, dtype="bfloat16", capacity_tokens=768, max_batch_tokens=768, max_requests=2)
+        steps, at = [], 0
+        for i, n in enumerate(cuts):
+            want = [r - at for r in rows if at <= r < at + n]
+            steps.append({"step": i, "entries": [{"id": "a", "tokens": toks[at:at + n], "want": want}],
+                          "end": ["a"] if at + n == len(toks) else []})
+            at += n
+        with tempfile.TemporaryDirectory() as out:
+            rp = TraceReplayer(runner, out)
+            got = np.concatenate([rp.run_step(s) for s in steps])
+        errs = [rel_err(got[i], ref[i]) for i in range(len(rows))]
+        assert max(errs) <= TOL["bfloat16"], (cuts, errs)
+        results.append(got)
+    for other in results[1:]:
+        assert max(rel_err(other[i], results[0][i]) for i in range(len(rows))) <= TOL["bfloat16"]
