@@ -346,15 +346,74 @@ EMBER_API int ember_gemm_tc(const void* A, const void* W, void* out, int ldc, in
     return 0;
 }
 
-// The fused projection of a layer's attention: [q | k | v] = A . W^T for M > 128 tokens, and straight from the
+// The fused projection of a layer's attention: [q | k | v] = A . W^T for M > 128 tokens (rotation from the angle
+// table cos_sin) or for at most 16 (rotation from the frequencies inv_freq; either may be null), and straight from the
 // accumulator every query and key head gets its RMSNorm (weights may be null) and its rotation (cos_sin, the table
 // of ember_rope_table with cs_ld tokens a row, may be null), queries go to q_out, keys and values into their cache pages.  Heads are 128 wide.  1 if these sizes are taken.
 EMBER_API int ember_gemm_tc_qkv_supported(int M, int N, int K, int n_heads, int n_kv, int head_dim) {
-    return M > 128 && K > 0 && K % 8 == 0 && head_dim == 128 && n_heads > 0 && n_kv > 0 && N == (n_heads + 2 * n_kv) * 128;
+    return M > 0 && (M <= 16 || M > 128) && K > 0 && K % 8 == 0 && head_dim == 128 && n_heads > 0 && n_kv > 0 &&
+           N == (n_heads + 2 * n_kv) * 128;
+}
+
+// The fused projection of a decode-sized step (at most 16 tokens): 128 weight rows (one head slot) x the tokens per
+// tile, the K range split over a thread-block cluster whose blocks share the tokens out and finish whole heads.
+static int launch_heads_swapped(const void* A, const void* W, GemmTcParams p, int num_sms, cudaStream_t st) {
+    p.swapped = 1;
+    p.block_cols = 16;
+    const int tiles = p.N / TILE_ROWS;
+    int splits = 1;
+    if (tiles < num_sms) {
+        splits = (num_sms + tiles - 1) / tiles;
+        if (splits > 8) splits = 8;
+        while (splits > 1 && p.num_k_blocks / splits < 2) splits--;
+    }
+    p.k_blocks_per_split = (p.num_k_blocks + splits - 1) / splits;
+    splits = (p.num_k_blocks + p.k_blocks_per_split - 1) / p.k_blocks_per_split;
+    p.cluster_splits = splits;
+    p.rows_per = TILE_ROWS;
+    p.row_tiles = tiles;
+    p.total_tiles = tiles;
+    p.tmem_cols = 32;
+    p.accum = nullptr; p.accum_ld = 0;
+    const int per = (p.block_cols + splits - 1) / splits;
+    const size_t recv_bytes = ((size_t)splits * per + 1) * TILE_ROWS * sizeof(float) + 64;     // partial sums, one head, 4 sums
+    const int stage_bytes = TILE_ROWS * TILE_K * 2 + ((p.block_cols * TILE_K * 2 + 1023) & ~1023);
+    int stages = (int)(((size_t)96 * 1024) / stage_bytes);
+    if (stages > MAX_STAGES) stages = MAX_STAGES;
+    if (stages > p.k_blocks_per_split) stages = p.k_blocks_per_split < 2 ? 2 : p.k_blocks_per_split;
+    p.stages = stages;
+    const size_t smem = (size_t)stages * stage_bytes + 1024 + 256 + recv_bytes;
+    CUtensorMap map_rows, map_cols;
+    if (!tensor_map(W, p.N, p.K, TILE_ROWS, &map_rows) || !tensor_map(A, p.M, p.K, p.block_cols, &map_cols))
+        return fail("gemm_tc: cuTensorMapEncodeTiled failed or is unavailable");
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 227 * 1024);
+        if (e != cudaSuccess) return fail("gemm_tc: cannot raise the shared-memory limit: %s", cudaGetErrorString(e));
+        cudaFuncSetAttribute(gemm_tc_kernel, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared);
+        attr_set = true;
+    }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(tiles, 1, splits);
+    cfg.blockDim = dim3(GEMM_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attrs[2];
+    attrs[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attrs[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+    attrs[1].id = cudaLaunchAttributeClusterDimension;
+    attrs[1].val.clusterDim.x = 1;
+    attrs[1].val.clusterDim.y = 1;
+    attrs[1].val.clusterDim.z = (unsigned)splits;
+    cfg.attrs = attrs;
+    cfg.numAttrs = 2;
+    cudaLaunchKernelEx(&cfg, gemm_tc_kernel, map_rows, map_cols, p);
+    return check_launch("gemm_tc_heads");
 }
 
 EMBER_API int ember_gemm_tc_qkv(const void* A, const void* W, int M, int N, int K, int n_heads, int n_kv,
                                 const float* q_norm_w, const float* k_norm_w, float eps, const void* cos_sin, int cs_ld,
+                                const float* inv_freq,
                                 const int* positions, const int* seq_of, const int* block_table, int max_blocks, int page,
                                 int num_pages, void* q_out, void* k_pool, void* v_pool, int write_kv, int num_sms,
                                 int split_mode, int* err, void* stream) {
@@ -374,10 +433,14 @@ EMBER_API int ember_gemm_tc_qkv(const void* A, const void* W, int M, int N, int 
     p.rows_per = TILE_ROWS;
     p.qkv.n_heads = n_heads; p.qkv.n_kv = n_kv; p.qkv.q_norm_w = q_norm_w; p.qkv.k_norm_w = k_norm_w; p.qkv.eps = eps;
     if (cos_sin && cs_ld < M) return fail("gemm_tc_qkv: the rotation table has %d columns for %d tokens", cs_ld, M);
+    if (M <= 16 ? (cos_sin && !inv_freq) : (inv_freq && !cos_sin))
+        return fail("gemm_tc_qkv: %d tokens rotate with %s", M, M <= 16 ? "the frequencies" : "the angle table");
+    p.qkv.inv_freq = inv_freq;
     p.qkv.cos_sin = (const float4*)cos_sin; p.qkv.cs_ld = cs_ld; p.qkv.positions = positions; p.qkv.seq_of = seq_of;
     p.qkv.block_table = block_table; p.qkv.max_blocks = max_blocks; p.qkv.page = page; p.qkv.num_pages = num_pages;
     p.qkv.q_out = (__nv_bfloat16*)q_out; p.qkv.k_pool = (__nv_bfloat16*)k_pool; p.qkv.v_pool = (__nv_bfloat16*)v_pool;
     p.qkv.write_kv = write_kv;
+    if (M <= 16) return launch_heads_swapped(A, W, p, num_sms, st);
     const int block_cols = (N % 256 == 0) ? 256 : 128;          // whole heads in a tile
     if (split_mode != 5) {
         const int max_pairs = pair_capacity(num_sms);

@@ -28,6 +28,7 @@ struct QkvEpilogue {
     const float4* cos_sin;          // [32][cs_ld] (cos, cos, sin, sin) of position * inv_freq for frequencies 2j and 2j + 1 of
                                     // token t at [j][t]: the lanes of a warp (neighbouring tokens) read neighbouring 16 bytes; null: no rotation
     int cs_ld;
+    const float* inv_freq;          // [64]: decode-sized steps (at most 16 tokens) compute their angles themselves; null: no rotation
     const int* positions;           // [tokens]
     const int* seq_of;              // [tokens] -> row of the block table
     const int* block_table;
@@ -150,6 +151,9 @@ __device__ __forceinline__ uint32_t map_to_rank(uint32_t smem_addr, uint32_t ran
 }
 __device__ __forceinline__ void st_cluster_f32x4(uint32_t addr, float a, float b, float c, float d) {
     asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "f"(a), "f"(b), "f"(c), "f"(d) : "memory");
+}
+__device__ __forceinline__ void st_cluster_f32(uint32_t addr, float a) {
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(a) : "memory");
 }
 __device__ __forceinline__ void cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
 __device__ __forceinline__ void cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
@@ -377,6 +381,106 @@ __device__ __forceinline__ void store_heads_normal(const GemmTcParams& p, const 
     }
 }
 
+// Epilogue 4 of a decode-sized step (swapped orientation: the tile's 128 accumulator rows are one head slot, its
+// columns the step's at most 16 tokens).  Block `split` of the cluster receives, from every block, the partial
+// sums of the tokens split, split + S, ...: recv[s][token / S][row].  It sums them in block order, and thread r
+// holds element r of the head: RMSNorm over the 128 elements, rotation with element r ^ 64 (the angle is
+// float(position) * inv_freq[r & 63], its sine and cosine fp32), and the head goes to the query buffer or into
+// the token's cache page.
+// What does not depend on the product -- where the first two tokens' keys and values go, their angles, this
+// thread's norm weight -- is fetched by heads_prepare before the cluster's barriers, so that the dependent loads
+// (position -> block table) and the sine and cosine are not paid after them.
+struct HeadsPrep {
+    int kind;                   // 0 q, 1 k, 2 v
+    bool norm, turn;
+    float g, freq;
+    int pos[2], blk[2];
+    float cs[2], sn[2];
+};
+__device__ __forceinline__ void heads_token(const QkvEpilogue& e, int m, const HeadsPrep& h, int& pos, int& blk, float& cs, float& sn) {
+    pos = e.positions[m];
+    blk = -1;
+    if (h.kind != 0 && e.write_kv) blk = e.block_table[(size_t)e.seq_of[m] * e.max_blocks + pos / e.page];
+    cs = 1.0f; sn = 0.0f;
+    if (h.turn) sincosf((float)pos * h.freq, &sn, &cs);
+}
+__device__ __forceinline__ void heads_prepare(const GemmTcParams& p, int slot, int split, HeadsPrep& h) {
+    const QkvEpilogue& e = p.qkv;
+    const int r = (int)threadIdx.x - 64;                   // the row this thread finishes (epilogue warps only)
+    h.kind = slot < e.n_heads ? 0 : (slot < e.n_heads + e.n_kv ? 1 : 2);
+    const float* nw = h.kind == 0 ? e.q_norm_w : (h.kind == 1 ? e.k_norm_w : nullptr);
+    h.norm = nw != nullptr;
+    h.turn = h.kind != 2 && e.inv_freq != nullptr;
+    h.g = 1.0f; h.freq = 0.0f;
+#pragma unroll
+    for (int t = 0; t < 2; t++) { h.pos[t] = 0; h.blk[t] = -1; h.cs[t] = 1.0f; h.sn[t] = 0.0f; }
+    if (r < 0) return;
+    if (nw) h.g = nw[r];
+    if (h.turn) h.freq = e.inv_freq[r & 63];
+#pragma unroll
+    for (int t = 0; t < 2; t++) {
+        const int m = split + t * p.cluster_splits;
+        if (m < p.M) heads_token(e, m, h, h.pos[t], h.blk[t], h.cs[t], h.sn[t]);
+    }
+}
+// All threads of the block call this (it synchronises); the rows are held by the four epilogue warps (threads
+// 64..191), the ones that called heads_prepare while the product ran.
+__device__ __forceinline__ void finish_heads_swapped(const GemmTcParams& p, const float* recv, int slot, int split, bool failed,
+                                                     const HeadsPrep& h) {
+    const QkvEpilogue& e = p.qkv;
+    const int S = p.cluster_splits, per = (p.block_cols + S - 1) / S;
+    float* xs = const_cast<float*>(recv) + (size_t)S * per * TILE_ROWS;      // [128] the normed head, then 4 partial sums
+    float* red = xs + TILE_ROWS;
+    const int r = (int)threadIdx.x - 64;
+    const bool row = r >= 0;
+    auto finish_one = [&](int cl, int m, int pos, int blk, float cs, float sn) {
+        float v = 0.0f;
+        if (row)
+            for (int s = 0; s < S; s++) v += recv[((size_t)s * per + cl) * TILE_ROWS + r];
+        if (h.norm) {
+            float ss = warp_sum(row ? v * v : 0.0f);
+            if ((r & 31) == 0 && row) red[r >> 5] = ss;
+            __syncthreads();
+            ss = (red[0] + red[1]) + (red[2] + red[3]);
+            v = h.g * (v * (1.0f / sqrtf(ss / 128.0f + e.eps)));
+        }
+        if (h.turn) {
+            if (row) xs[r] = v;
+            __syncthreads();
+            if (row) {
+                const float other = xs[r ^ 64];
+                v = r < 64 ? v * cs - other * sn : v * cs + other * sn;
+            }
+        }
+        __nv_bfloat16* dst = nullptr;
+        if (h.kind == 0) {
+            dst = e.q_out + ((size_t)m * e.n_heads + slot) * 128;
+        } else if (e.write_kv) {
+            if (blk < 0 || blk >= e.num_pages) {
+                if (r == 0 && p.err) atomicOr(p.err, EMBER_ERR_PAGE_RANGE);
+            } else {
+                const int kvh = slot - e.n_heads - (h.kind == 2 ? e.n_kv : 0);
+                dst = (h.kind == 1 ? e.k_pool : e.v_pool) + (((size_t)blk * e.n_kv + kvh) * e.page + (size_t)(pos % e.page)) * 128;
+            }
+        }
+        if (dst && row && !failed) dst[r] = __float2bfloat16_rn(v);
+    };
+    if (split < p.M) finish_one(0, split, h.pos[0], h.blk[0], h.cs[0], h.sn[0]);
+    if (per > 1 && split + S < p.M) {
+        __syncthreads();                                            // xs and red are reused
+        finish_one(1, split + S, h.pos[1], h.blk[1], h.cs[1], h.sn[1]);
+    }
+    for (int cl = 2; cl < per; cl++) {                              // more than two tokens a block: fetched here
+        const int m = split + cl * S;                               // uniform over the block
+        if (m >= p.M) break;
+        int pos = 0, blk = -1;
+        float cs = 1.0f, sn = 0.0f;
+        if (row) heads_token(e, m, h, pos, blk, cs, sn);
+        __syncthreads();
+        finish_one(cl, m, pos, blk, cs, sn);
+    }
+}
+
 // ------------------------------------------------------------------------------------ kernel
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_tc_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_constant__ CUtensorMap map_cols,
@@ -394,7 +498,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_consta
     volatile int* abort_flag = (volatile int*)(tmem_base_slot + 1);
     // cluster split-K: partial sums of the rows this block finishes, one slab per block of the cluster
     float* recv = (float*)((uint8_t*)full_bar + 256);            // [cluster_splits][rows_per][block_cols]
-    const bool clustered = p.cluster_splits > 1;
+    const bool heads = p.swapped && p.epilogue == 4;           // the tile is one head slot; tokens are shared out (below)
+    const bool clustered = p.cluster_splits > 1 || heads;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int row_tile = blockIdx.x, col_tile = blockIdx.y, split = blockIdx.z;
@@ -423,6 +528,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_consta
     if (clustered) cluster_arrive();        // phase 1: every block of the cluster is up before anyone writes to it
 
     pdl_launch_dependents();
+    HeadsPrep prep;
+    prep.kind = 0; prep.norm = false; prep.turn = false; prep.g = 1.0f; prep.freq = 0.0f;
+    prep.pos[0] = prep.pos[1] = 0; prep.blk[0] = prep.blk[1] = -1; prep.cs[0] = prep.cs[1] = 1.0f; prep.sn[0] = prep.sn[1] = 0.0f;
+    if (heads && warp < 2) heads_prepare(p, row_tile, split, prep);       // (the uniform fields; these warps hold no row)
     if (warp == 0) {
         // ---------------------------------------------------------------- TMA producer
         // The weight operand does not depend on earlier kernels: its first tiles are requested
@@ -481,6 +590,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_consta
     } else if (n_kb > 0) {
         // -------------------------------------------------------------------- epilogue
         const int quad = warp & 3;                  // TMEM lane quadrant this warp may read
+        if (heads) heads_prepare(p, row_tile, split, prep);       // step inputs only: fetched while the product runs
         pdl_wait();                                 // the output may still be read by earlier kernels until here
         const bool ok = mbar_wait(tmem_full_bar, 0, abort_flag);
         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -490,15 +600,32 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_consta
             cluster_wait();                         // phase 1 complete: all blocks of the cluster run
             const int r = quad * 32 + lane;
             const uint32_t taddr_row = tmem_d + ((uint32_t)(quad * 32) << 16);
-            const int owner = r / p.rows_per, rl = r - owner * p.rows_per;
-            const uint32_t dst_row = map_to_rank(smem_u32(recv + ((size_t)split * p.rows_per + rl) * p.block_cols), (uint32_t)owner);
-            for (int c0 = 0; c0 < p.block_cols; c0 += 16) {
-                float v[16];
-                tmem_ld16(taddr_row + (uint32_t)c0, v);
-                if (ok) {
+            if (heads) {
+                // token column c goes to block c % S, which then holds the whole head (all 128 rows) of its tokens:
+                // recv[split][c / S][row]
+                const int S = p.cluster_splits, per = (p.block_cols + S - 1) / S;
+                for (int c0 = 0; c0 < p.block_cols; c0 += 16) {
+                    float v[16];
+                    tmem_ld16(taddr_row + (uint32_t)c0, v);
 #pragma unroll
-                    for (int j = 0; j < 4; j++)
-                        st_cluster_f32x4(dst_row + (uint32_t)(c0 + 4 * j) * 4u, v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                    for (int j = 0; j < 16; j++) {
+                        const int c = c0 + j;
+                        if (!ok || c >= p.M) continue;
+                        const int owner = c % S, cl = c / S;
+                        st_cluster_f32(map_to_rank(smem_u32(recv + ((size_t)split * per + cl) * TILE_ROWS + r), (uint32_t)owner), v[j]);
+                    }
+                }
+            } else {
+                const int owner = r / p.rows_per, rl = r - owner * p.rows_per;
+                const uint32_t dst_row = map_to_rank(smem_u32(recv + ((size_t)split * p.rows_per + rl) * p.block_cols), (uint32_t)owner);
+                for (int c0 = 0; c0 < p.block_cols; c0 += 16) {
+                    float v[16];
+                    tmem_ld16(taddr_row + (uint32_t)c0, v);
+                    if (ok) {
+#pragma unroll
+                        for (int j = 0; j < 4; j++)
+                            st_cluster_f32x4(dst_row + (uint32_t)(c0 + 4 * j) * 4u, v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                    }
                 }
             }
         } else if (ok) {
@@ -565,7 +692,9 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_consta
         const int S = p.cluster_splits, RP = p.rows_per, C = p.block_cols;
         const int row_base = row_tile * TILE_ROWS + split * RP;       // first weight row this block finishes
         const int rows_here = max(0, min(RP, TILE_ROWS - split * RP));
-        if (p.epilogue == 3) {
+        if (heads) {
+            finish_heads_swapped(p, recv, row_tile, split, *abort_flag != 0, prep);
+        } else if (p.epilogue == 3) {
             const int pairs = rows_here >> 1;
             for (int idx = threadIdx.x; idx < pairs * C; idx += GEMM_THREADS) {
                 const int c = idx / pairs, pr = idx - c * pairs;

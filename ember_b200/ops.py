@@ -311,11 +311,11 @@ def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, M: int, epilogu
 def gemm_tc_qkv_usable(x: torch.Tensor, w: torch.Tensor, bias, M: int, n_heads: int, n_kv: int, head_dim: int,
                        rotary: int) -> bool:
     """Whether the fused projection takes this step: bf16, no bias, heads of 128 rotated whole (or not at all),
-    more than 128 tokens (the rule of ember_gemm_tc_qkv_supported)."""
+    more than 128 tokens or at most 16 (the rule of ember_gemm_tc_qkv_supported)."""
     if not gemm_tc_usable(x, w, bias, EPI_STORE):
         return False
     n, k = w.shape
-    return M > 128 and head_dim == 128 and rotary in (0, 128) and n == (n_heads + 2 * n_kv) * 128
+    return (0 < M <= 16 or M > 128) and head_dim == 128 and rotary in (0, 128) and n == (n_heads + 2 * n_kv) * 128
 
 
 # From how many tokens on a step's q/k/v product finishes the heads itself.  Measured at the 1.7B shape, product +
@@ -323,6 +323,10 @@ def gemm_tc_qkv_usable(x: torch.Tensor, w: torch.Tensor, bias, M: int, n_heads: 
 # 74.5 / 51.3 at 4,096 (below, the step is one or two tiles an SM and the longer epilogue has no next tile to
 # hide behind).
 QKV_FUSE_MIN_TOKENS = 512
+# Up to how many tokens a decode step's q/k/v product does (product + head kernel against the fused product, in a
+# graph: 8.4 / 6.2 us at 1 token, 9.1 / 7.6 at 8, 9.4 / 10.1 at 16: a block of the cluster finishes its share of
+# the tokens one after the other, and only the first two are prepared while the product runs).
+QKV_FUSE_MAX_DECODE_TOKENS = 8
 
 
 def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, T: int, out: torch.Tensor, stream: Optional[int] = None) -> None:
@@ -340,13 +344,15 @@ def rope_table(positions: torch.Tensor, inv_freq: torch.Tensor, T: int, out: tor
 
 
 def gemm_tc_qkv(a: torch.Tensor, w: torch.Tensor, M: int, n_heads: int, n_kv: int, q_norm_w: Optional[torch.Tensor],
-                k_norm_w: Optional[torch.Tensor], eps: float, cos_sin: Optional[torch.Tensor], positions: torch.Tensor,
+                k_norm_w: Optional[torch.Tensor], eps: float, cos_sin: Optional[torch.Tensor],
+                inv_freq: Optional[torch.Tensor], positions: torch.Tensor,
                 seq_of: torch.Tensor, block_table: torch.Tensor, page: int, k_pool: torch.Tensor, v_pool: torch.Tensor,
                 q_out: torch.Tensor, write_kv: bool = True, err: Optional[torch.Tensor] = None,
                 stream: Optional[int] = None, split_mode: int = 0) -> None:
     """[q | k | v] = a[:M] @ w.T on the tcgen05 tensor cores with the heads finished in the epilogue: RMSNorm and
     rotation of query and key heads in fp32 on the accumulator, queries to ``q_out``, keys and values into their
-    cache pages.  ``cos_sin`` [32, tokens a row, 4] comes from ``rope_table`` (None: no rotation).  Heads are 128 wide."""
+    cache pages.  More than 128 tokens rotate with ``cos_sin`` [32, tokens a row, 4] from ``rope_table``, at most
+    16 with the frequencies ``inv_freq`` [64] (both None: no rotation).  Heads are 128 wide."""
     _check(a, "a", torch.bfloat16)
     _check(w, "w", torch.bfloat16)
     _check(q_out, "q_out", torch.bfloat16)
@@ -355,7 +361,7 @@ def gemm_tc_qkv(a: torch.Tensor, w: torch.Tensor, M: int, n_heads: int, n_kv: in
     _check(positions, "positions", torch.int32)
     _check(seq_of, "seq_of", torch.int32)
     _check(block_table, "block_table", torch.int32)
-    for t, n in ((q_norm_w, "q_norm_w"), (k_norm_w, "k_norm_w"), (cos_sin, "cos_sin")):
+    for t, n in ((q_norm_w, "q_norm_w"), (k_norm_w, "k_norm_w"), (cos_sin, "cos_sin"), (inv_freq, "inv_freq")):
         if t is not None:
             _check(t, n, torch.float32)
     N, K = w.shape
@@ -365,11 +371,13 @@ def gemm_tc_qkv(a: torch.Tensor, w: torch.Tensor, M: int, n_heads: int, n_kv: in
         raise KernelError(f"gemm_qkv: pools {tuple(k_pool.shape)} are not [pages, {n_kv}, {page}, 128]")
     if q_out.numel() < M * n_heads * 128 or positions.numel() < M or seq_of.numel() < M:
         raise KernelError("gemm_qkv: query buffer or token arrays too small")
+    if inv_freq is not None and inv_freq.numel() != 64:
+        raise KernelError(f"gemm_qkv: {inv_freq.numel()} frequencies for heads of 128")
     if cos_sin is not None and (cos_sin.dim() != 3 or cos_sin.shape[0] != 32 or cos_sin.shape[1] < M or cos_sin.shape[2] != 4):
         raise KernelError(f"gemm_qkv: rotation table {tuple(cos_sin.shape)} is not [32, >= {M}, 4]")
     lib = _lib("gemm_tc")
     _call(lib, lib.ember_gemm_tc_qkv, _p(a), _p(w), c_int(M), c_int(N), c_int(K), c_int(n_heads), c_int(n_kv),
-          _p(q_norm_w), _p(k_norm_w), c_float(eps), _p(cos_sin), c_int(cos_sin.shape[1] if cos_sin is not None else 0), _p(positions), _p(seq_of), _p(block_table),
+          _p(q_norm_w), _p(k_norm_w), c_float(eps), _p(cos_sin), c_int(cos_sin.shape[1] if cos_sin is not None else 0), _p(inv_freq), _p(positions), _p(seq_of), _p(block_table),
           c_int(block_table.shape[-1]), c_int(page), c_int(k_pool.shape[0]), _p(q_out), _p(k_pool), _p(v_pool),
           c_int(1 if write_kv else 0), c_int(_sms(a.device)), c_int(split_mode), _p(err),
           c_void_p(stream if stream is not None else current_stream_ptr()))

@@ -87,13 +87,17 @@ class Attention(Mixer):
         q = ctx.buf("attention.q", (mt, s.q_dim), rt.dtype)
         att = ctx.buf("attention.out", (mt, s.q_dim), rt.dtype)
         table = ctx.block_table(cache.group)
-        if self.FUSE_QKV and T >= ops.QKV_FUSE_MIN_TOKENS and ops.gemm_tc_qkv_usable(x, self.qkv.weight, self.qkv.bias, T, s.num_heads, s.num_kv_heads,
-                                                    s.head_dim, self.rotary if self.inv_freq is not None else 0):
-            # a prompt portion: norm, rotation and the cache write happen in the product's epilogue
-            cos_sin = self.position.cos_sin(ctx, rt) if self.inv_freq is not None and self.rotary else None
+        rotates = self.inv_freq is not None and self.rotary > 0
+        if (self.FUSE_QKV and (T >= ops.QKV_FUSE_MIN_TOKENS or T <= ops.QKV_FUSE_MAX_DECODE_TOKENS) and
+                ops.gemm_tc_qkv_usable(x, self.qkv.weight, self.qkv.bias, T, s.num_heads, s.num_kv_heads, s.head_dim,
+                                       self.rotary if rotates else 0)):
+            # norm, rotation and the cache write happen in the product's epilogue: a prompt portion rotates with
+            # the step's angle table, a decode step of a few tokens computes its angles itself
+            cos_sin = self.position.cos_sin(ctx, rt) if rotates and T > 16 else None
             ops.gemm_tc_qkv(x, self.qkv.weight, T, s.num_heads, s.num_kv_heads, self.q_norm_w, self.k_norm_w,
-                            s.qk_norm_eps, cos_sin, ctx.positions, ctx.seq_of, table, cache.page_tokens, cache.k, cache.v,
-                            q, write_kv=owns_cache, err=ctx.err, stream=ctx.stream)
+                            s.qk_norm_eps, cos_sin, self.inv_freq if rotates and T <= 16 else None, ctx.positions,
+                            ctx.seq_of, table, cache.page_tokens, cache.k, cache.v, q, write_kv=owns_cache, err=ctx.err,
+                            stream=ctx.stream)
         else:
             self.qkv(ctx, x, qkv, T, ops.EPI_STORE)
             ops.qk_norm_rope_store(qkv, T, s.num_heads, s.num_kv_heads, s.head_dim, self.q_norm_w, self.k_norm_w,

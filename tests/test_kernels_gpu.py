@@ -350,7 +350,8 @@ def test_attention_fa_many_blocks(heads, kv, page, window):
         assert rel(out.float().view(T, heads, D), want) < 6e-3
 
 
-@pytest.mark.parametrize("heads,kv,page,M", [(4, 2, 16, 300), (3, 1, 64, 200), (6, 2, 32, 2100), (5, 1, 16, 2304)])
+@pytest.mark.parametrize("heads,kv,page,M", [(4, 2, 16, 300), (3, 1, 64, 200), (6, 2, 32, 2100), (5, 1, 16, 2304),
+                                             (16, 8, 16, 8), (4, 2, 64, 1), (3, 1, 32, 16), (40, 8, 16, 5)])
 @pytest.mark.parametrize("norm,rotate", [(True, True), (False, True), (True, False)])
 def test_gemm_tc_qkv(heads, kv, page, M, norm, rotate):
     """The fused q/k/v product: heads finished in the epilogue (norm, rotation, cache write) against the same
@@ -359,8 +360,9 @@ def test_gemm_tc_qkv(heads, kv, page, M, norm, rotate):
     give tiles of one head, the others of two."""
     from ember_b200 import ops
     torch.manual_seed(heads * M + page)
-    dev, D, K = "cuda", 128, 328                       # K: no multiple of 64
-    lens = [M - 130, 130]
+    dev, D = "cuda", 128
+    K = 136 if M == 5 else 328                         # no multiples of 64; 136: too short to split over a cluster
+    lens = [M - 130, 130] if M > 130 else [M - M // 2, M // 2]      # 1..16 tokens: the decode-sized kernel
     starts = [37, 1000]
     pos = torch.cat([torch.arange(s, s + n) for s, n in zip(starts, lens)]).int().to(dev)
     seq = torch.cat([torch.full((n,), i) for i, n in enumerate(lens)]).int().to(dev)
@@ -374,12 +376,17 @@ def test_gemm_tc_qkv(heads, kv, page, M, norm, rotate):
     inv = 1.0 / (10000.0 ** (torch.arange(D // 2, device=dev).float() * 2 / D))
     assert ops.gemm_tc_qkv_usable(a, w, None, M, heads, kv, D, D if rotate else 0)
     cs = None
-    if rotate:
+    if rotate and M <= 16:
+        fr = inv
+    elif rotate:
+        fr = None
         cs = torch.empty(D // 4, M + 8, 4, device=dev)          # rows longer than the step
         ops.rope_table(pos, inv, M, cs)
         ang = pos.float()[None, :] * inv[:, None]                # [frequency, token]
         got = cs[:, :M].view(D // 4, M, 2, 2).permute(0, 3, 1, 2).reshape(D // 2, M, 2)      # (cos, cos, sin, sin) per pair
         assert torch.allclose(got[..., 0], torch.cos(ang), atol=2e-6) and torch.allclose(got[..., 1], torch.sin(ang), atol=2e-6)
+    if not rotate:
+        fr = None
     x = a.float() @ w.float().t()
     qq, kk, vv = x[:, :heads * D].view(M, heads, D), x[:, heads * D:(heads + kv) * D].view(M, kv, D), x[:, (heads + kv) * D:].view(M, kv, D)
 
@@ -394,7 +401,7 @@ def test_gemm_tc_qkv(heads, kv, page, M, norm, rotate):
         vp = torch.zeros_like(kp)
         q = torch.zeros(M, heads * D, device=dev, dtype=torch.bfloat16)
         err = torch.zeros(1, dtype=torch.int32, device=dev)
-        ops.gemm_tc_qkv(a, w, M, heads, kv, qw, kw, 1e-5, cs, pos, seq, perm, page, kp, vp, q, write_kv=write_kv, err=err)
+        ops.gemm_tc_qkv(a, w, M, heads, kv, qw, kw, 1e-5, cs, fr, pos, seq, perm, page, kp, vp, q, write_kv=write_kv, err=err)
         assert int(err.item()) == 0
         assert rel(q.float().view(M, heads, D), qq) < 5e-3
         worst = ((q.float().view(M, heads, D) - qq).norm(dim=-1) / qq.norm(dim=-1)).max()
@@ -414,5 +421,5 @@ def test_gemm_tc_qkv(heads, kv, page, M, norm, rotate):
     bad = perm.clone()
     bad[0, starts[0] // page] = pages + 5
     err = torch.zeros(1, dtype=torch.int32, device=dev)
-    ops.gemm_tc_qkv(a, w, M, heads, kv, qw, kw, 1e-5, cs, pos, seq, bad, page, kp, vp, q, err=err)
+    ops.gemm_tc_qkv(a, w, M, heads, kv, qw, kw, 1e-5, cs, fr, pos, seq, bad, page, kp, vp, q, err=err)
     assert int(err.item()) == 2
