@@ -122,6 +122,29 @@ def test_rmsnorm(H, odt):
         assert torch.equal(g, out[rows.long()])
 
 
+@pytest.mark.parametrize("H", [512, 1024, 2048, 4096, 640])
+@pytest.mark.parametrize("odt", [torch.float32, torch.bfloat16])
+def test_rmsnorm_many_rows(H, odt):
+    """A prompt portion's worth of rows, one of them of another magnitude, and a gathered subset."""
+    from ember_b200 import ops
+    torch.manual_seed(H + 1)
+    n = 1003
+    x = torch.randn(n, H, device="cuda") * 3
+    x[17] *= 1e3                                               # one row of another magnitude
+    w = 1 + 0.1 * torch.randn(H, device="cuda")
+    out = torch.full((n + 1, H), 7.0, device="cuda", dtype=odt)
+    ops.rmsnorm(x, w, 1e-6, out, n)
+    want = w * (x * torch.rsqrt((x.double() ** 2).mean(-1, keepdim=True) + 1e-6).float())
+    assert rel(out[:n].float(), want) < (4e-3 if odt == torch.bfloat16 else 1e-6)
+    worst = ((out[:n].float() - want).norm(dim=-1) / want.norm(dim=-1)).max()
+    assert float(worst) < (6e-3 if odt == torch.bfloat16 else 2e-6)
+    assert float((out[n].float() - 7.0).abs().max()) == 0.0    # the row beyond is not touched
+    rows = torch.randperm(n, device="cuda")[:300].int()
+    g = torch.empty(300, H, device="cuda", dtype=odt)
+    ops.rmsnorm(x, w, 1e-6, g, 300, rows=rows)
+    assert torch.equal(g, out[rows.long()])
+
+
 @pytest.mark.parametrize("tdt", [torch.float32, torch.bfloat16])
 def test_embed(tdt):
     from ember_b200 import ops
