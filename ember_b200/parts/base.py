@@ -8,7 +8,8 @@ Interfaces (what a new part must provide):
 
 * ``Norm``:          ``forward(ctx, x_f32[rows, size], out[n_rows, size], n_rows, rows=None)``
 * ``PositionEncoding``: ``rotary_table(rt) -> (inv_freq_f32[rotary/2] | None, rotary_dim)``; encodings that
-  act elsewhere may instead override ``on_embedding(ctx, h)``.
+  act elsewhere may instead override ``on_embedding(ctx, h)``.  ``table_key()`` says which layers' frequencies are
+  the same (they share the step's angle table that ``cos_sin`` makes from ``rotary_table``).
 * ``Mixer``:         ``cache_need() -> CacheNeed | None`` and
   ``forward(ctx, x[T, hidden], residual_f32[T, hidden], cache: LayerCache | None, owns_cache: bool)``;
   it *adds* its result to ``residual``.
@@ -106,6 +107,26 @@ class PositionEncoding(Part):
 
     def on_embedding(self, ctx, h: torch.Tensor) -> None:
         """Hook for encodings that are added to the embedded tokens; rotary ones do nothing here."""
+
+    def table_key(self):
+        """What tells this part's frequencies from another's: layers whose keys are equal share a step's angle
+        table.  Unknown parts share nothing."""
+        return id(self)
+
+    def cos_sin(self, ctx, rt: Runtime) -> torch.Tensor:
+        """[rotary / 4, tokens, 4]: (cos, cos, sin, sin) of float(position) * inv_freq for pairs of frequencies (the
+        layout of ``ops.rope_table``), made once per step for the products that rotate in their epilogue and kept
+        in the step's memo."""
+        from .. import ops
+        inv, _ = self.rotary_table(rt)
+        key = ("rope.cos_sin", self.table_key())
+        got = ctx.memo.get(key)
+        if got is None:
+            half = inv.numel()
+            got = ctx.buf(f"rope.cos_sin.{key[1]}", (half // 2, ctx.max_tokens, 4), torch.float32)
+            ops.rope_table(ctx.positions, inv, ctx.T, got, stream=ctx.stream)
+            ctx.memo[key] = got
+        return got
 
 
 class Mixer(Part):

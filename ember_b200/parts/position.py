@@ -12,7 +12,6 @@ from __future__ import annotations
 import numpy as np
 import torch
 
-from .. import ops
 from ..config.spec import ConfigError
 from .base import PositionEncoding, Runtime
 from .registry import register_part
@@ -36,19 +35,8 @@ class RotaryEmbedding(PositionEncoding):
             self._table = torch.from_numpy(self.inv_freq()).to(rt.device)
         return self._table, self.spec.rotary_dim
 
-    def cos_sin(self, ctx, rt: Runtime) -> torch.Tensor:
-        """[rotary / 4, tokens, 4] (cos, sin) pairs of the step's positions (the layout of ``ops.rope_table``), made
-        once per step and shared by the layers that use this table (fp32, the angle float(position) * inv_freq as
-        everywhere)."""
-        inv, _ = self.rotary_table(rt)
-        key = ("rope.cos_sin", self.spec.rotary_dim, float(self.spec.theta))     # layers with equal frequencies share it
-        got = ctx.memo.get(key)
-        if got is None:
-            half = inv.numel()
-            got = ctx.buf(f"rope.cos_sin.{key[1]}.{key[2]}", (half // 2, ctx.max_tokens, 4), torch.float32)
-            ops.rope_table(ctx.positions, inv, ctx.T, got, stream=ctx.stream)
-            ctx.memo[key] = got
-        return got
+    def table_key(self):
+        return (self.spec.rotary_dim, float(self.spec.theta))        # equal frequencies: one table a step
 
 
 class NoPosition(PositionEncoding):
