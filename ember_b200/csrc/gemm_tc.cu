@@ -339,8 +339,17 @@ EMBER_API int ember_gemm_tc(const void* A, const void* W, void* out, int ldc, in
     int rc = check_launch("gemm_tc");
     if (rc) return rc;
     if (splits > 1 && p.cluster_splits <= 1 && epilogue != 2) {
-        const size_t total = (size_t)M * (epilogue == 3 ? N / 2 : N);
-        launch_kernel(gemm_tc_finalize_kernel, (unsigned)((total + 255) / 256), 256, 0, st, p.accum, p.accum_ld, out, ldc, M, N, epilogue);
+        const int n_out = epilogue == 3 ? N / 2 : N;
+        const size_t total = (size_t)M * n_out;
+        const bool by4 = n_out % 4 == 0 && ldc % 4 == 0 && p.accum_ld % 4 == 0 && ((((uintptr_t)p.accum) | ((uintptr_t)out)) & 15) == 0;
+        if (by4) {
+            const unsigned blocks = (unsigned)((total / 4 + 255) / 256);
+            if (epilogue == 3) launch_kernel(gemm_tc_finalize4_kernel<3>, blocks, 256, 0, st, p.accum, p.accum_ld, out, ldc, M, n_out);
+            else if (epilogue == 1) launch_kernel(gemm_tc_finalize4_kernel<1>, blocks, 256, 0, st, p.accum, p.accum_ld, out, ldc, M, n_out);
+            else launch_kernel(gemm_tc_finalize4_kernel<0>, blocks, 256, 0, st, p.accum, p.accum_ld, out, ldc, M, n_out);
+        } else {
+            launch_kernel(gemm_tc_finalize_kernel, (unsigned)((total + 255) / 256), 256, 0, st, p.accum, p.accum_ld, out, ldc, M, N, epilogue);
+        }
         return check_launch("gemm_tc_finalize");
     }
     return 0;
