@@ -193,7 +193,8 @@ def cmd_bench(args) -> int:
 
 
 def main(argv=None) -> int:
-    args = _parser().parse_args(argv)
+    # (intermixed: `bench -m DIR prompt=512 batch=1,8` has positionals after options)
+    args = _parser().parse_intermixed_args(argv)
     cmd = {"generate": cmd_generate, "gen": cmd_generate, "bench": cmd_bench, "info": cmd_info,
            "random": cmd_random, "replay": cmd_replay}[args.command]
     try:
