@@ -203,7 +203,10 @@ __device__ __forceinline__ void store_chunk_normal(const GemmTcParams& p, int m,
                 }
             }
         } else {
-            for (int j = 0; j < nv; j++) dst[j] = p.epilogue == 2 ? dst[j] + v[j] : v[j];
+            for (int j = 0; j < nv; j++) {
+                if (p.epilogue == 2) atomicAdd(dst + j, v[j]);          // (several units may add to one element)
+                else dst[j] = v[j];
+            }
         }
     } else {
         __nv_bfloat16* dst = (__nv_bfloat16*)p.out + (size_t)m * p.ldc + (n0 >> 1);
@@ -754,6 +757,10 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_rows, const __
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n_kb = p.num_k_blocks;
+    // With few tiles (a short prompt portion) the K range of the adding epilogue is cut: a unit is a tile and a part
+    // of K, its sums are added at the L2 like any other, and every SM has work.
+    const int k_splits = (n_kb + p.k_blocks_per_split - 1) / p.k_blocks_per_split;
+    const int units = p.total_tiles * k_splits;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < p.stages; s++) {
@@ -786,9 +793,11 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_rows, const __
             uint32_t phase = 0;                      // parity of the ring's current lap
             bool ok = true, wrapped = false;
             uint8_t* st = smem;
-            for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x) {
+            for (int u = blockIdx.x; u < units && ok; u += gridDim.x) {
+                const int t = u / k_splits, kb0 = (u - t * k_splits) * p.k_blocks_per_split;
+                const int kb1 = min(n_kb, kb0 + p.k_blocks_per_split);
                 const int col_tile = t / p.row_tiles, row_tile = t - col_tile * p.row_tiles;
-                for (int i = 0; i < n_kb; i++) {
+                for (int i = kb0; i < kb1; i++) {
                     if (wrapped) ok = mbar_wait(&empty_bar[s], phase ^ 1u, abort_flag);
                     if (!ok) break;
                     mbar_expect_tx(&full_bar[s], (uint32_t)(rows_bytes + cols_bytes));
@@ -809,19 +818,20 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_rows, const __
             const uint64_t da0 = umma_desc_sw128(smem), db0 = umma_desc_sw128(smem + rows_bytes);
             const uint64_t dstep = (uint64_t)(stage_bytes >> 4);
             uint64_t da = da0, db = db0;
-            for (int t = blockIdx.x; t < p.total_tiles && ok; t += gridDim.x, li++) {
+            for (int u = blockIdx.x; u < units && ok; u += gridDim.x, li++) {
+                const int kb0 = (u % k_splits) * p.k_blocks_per_split, kb1 = min(n_kb, kb0 + p.k_blocks_per_split);
                 const int acc = li & 1;
                 if (li >= 2) ok = mbar_wait(&tmem_empty_bar[acc], ((uint32_t)(li >> 1) & 1u) ^ 1u, abort_flag);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t d = tmem_d + (uint32_t)(acc * p.block_cols);
-                for (int i = 0; i < n_kb; i++) {
+                for (int i = kb0; i < kb1; i++) {
                     ok = mbar_wait(&full_bar[s], phase, abort_flag);
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
                     for (int k = 0; k < TILE_K / UMMA_K; k++)
-                        tcgen05_mma_bf16(d, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, (i > 0 || k > 0) ? 1u : 0u);
+                        tcgen05_mma_bf16(d, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, (i > kb0 || k > 0) ? 1u : 0u);
                     tcgen05_commit(&empty_bar[s]);
                     da += dstep; db += dstep;
                     if (++s == p.stages) { s = 0; phase ^= 1u; da = da0; db = db0; }
@@ -834,7 +844,8 @@ gemm_tc_persistent_kernel(const __grid_constant__ CUtensorMap map_rows, const __
         const int r = quad * 32 + lane;
         bool ok = true;
         int li = 0;
-        for (int t = blockIdx.x; t < p.total_tiles; t += gridDim.x, li++) {
+        for (int u = blockIdx.x; u < units; u += gridDim.x, li++) {
+            const int t = u / k_splits;
             const int col_tile = t / p.row_tiles, row_tile = t - col_tile * p.row_tiles;
             const int acc = li & 1;
             const int m = row_tile * TILE_ROWS + r;

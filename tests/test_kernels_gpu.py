@@ -26,7 +26,8 @@ def ref_epilogue(c, epilogue, prev=None):
 @pytest.mark.parametrize("M,N,K", [(1, 512, 64), (3, 1000, 96), (17, 192, 200), (64, 2048, 2048), (65, 130, 72),
                                    (128, 256, 512), (129, 1000, 264), (300, 1536, 1024), (1000, 520, 136),
                                    (8, 4096, 2048), (5, 2048, 6144), (16, 12288, 1024), (100, 640, 4096),
-                                   (2048, 4096, 512), (777, 1500, 320), (4200, 2300, 136), (130, 100, 64)])
+                                   (2048, 4096, 512), (777, 1500, 320), (4200, 2300, 136), (130, 100, 64),
+                                   (512, 2048, 6144), (260, 204, 1544)])      # few tiles, long K: the adding epilogue cuts K
 @pytest.mark.parametrize("epilogue", [0, 1, 2, 3])
 @pytest.mark.parametrize("split_mode", [0, 1, 2, 3, 4, 5])
 def test_gemm_tc(M, N, K, epilogue, split_mode):
