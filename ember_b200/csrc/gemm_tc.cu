@@ -106,6 +106,26 @@ static int best_block_cols(int M, int N, int slots, int units, double* cost_out)
     return best;
 }
 
+// The adding epilogue may cut K as well (its sums are added at the L2 whatever their number): tile width and number
+// of K parts together, by a model of the time -- waves of units over the slots, a unit costing its k-blocks at the
+// tile's MMA rate plus a fixed share for its fill and its epilogue.  (1,024 tokens, N = 2048, K = 6144: 88 tiles of
+// 192 columns over all of K took 36 us; 64 tiles of 256 columns in two parts of K take half of that.)
+static void best_tile_and_parts(int M, int N, int num_k_blocks, int slots, int units, int* block_cols, int* k_splits) {
+    const int rows = TILE_ROWS * units;
+    const int row_tiles = (M + rows - 1) / rows;
+    double best = 1e30;
+    for (int bc = 256; bc >= 192; bc -= 16) {
+        const long long tiles = (long long)row_tiles * ((N + bc - 1) / bc);
+        for (int ks = 1; ks <= 16; ks++) {
+            if (ks > 1 && num_k_blocks / ks < 8) break;
+            const int kbps = (num_k_blocks + ks - 1) / ks;
+            const long long n_units = tiles * ((num_k_blocks + kbps - 1) / kbps);
+            const double cost = (double)((n_units + slots - 1) / slots) * ((double)kbps * 2.0 * (bc + 40) + 6000.0);
+            if (cost < best * 0.999) { best = cost; *block_cols = bc; *k_splits = ks; }
+        }
+    }
+}
+
 // The pair kernel: 256-token tiles on clusters of two blocks, as many pairs as the device co-schedules.
 static int launch_pair(const void* A, const void* W, GemmTcParams p, int block_cols, int max_pairs, cudaStream_t st) {
     p.block_cols = block_cols;
@@ -113,7 +133,15 @@ static int launch_pair(const void* A, const void* W, GemmTcParams p, int block_c
     p.total_tiles = p.row_tiles * ((p.N + block_cols - 1) / block_cols);
     p.tmem_cols = 512;
     p.cluster_splits = 1;
-    p.k_blocks_per_split = p.num_k_blocks;
+    int k_splits = 1;                                  // the adding epilogue: tile width and parts of K together
+    if (p.epilogue == 2 && p.N > 128 && !getenv("EMBER_GEMM_TILE_COLS")) {
+        best_tile_and_parts(p.M, p.N, p.num_k_blocks, max_pairs, 2, &block_cols, &k_splits);
+        p.block_cols = block_cols;
+        p.total_tiles = p.row_tiles * ((p.N + block_cols - 1) / block_cols);
+    }
+    p.k_blocks_per_split = (p.num_k_blocks + k_splits - 1) / k_splits;
+    k_splits = (p.num_k_blocks + p.k_blocks_per_split - 1) / p.k_blocks_per_split;
+    const int units = p.total_tiles * k_splits;
     const int stage_bytes = pair_stage_bytes(block_cols);
     int stages = (200 * 1024) / stage_bytes;
     if (stages > MAX_STAGES) stages = MAX_STAGES;
@@ -123,7 +151,7 @@ static int launch_pair(const void* A, const void* W, GemmTcParams p, int block_c
     CUtensorMap map_rows, map_cols;
     if (!tensor_map(A, p.M, p.K, TILE_ROWS, &map_rows) || !tensor_map(W, p.N, p.K, block_cols / 2, &map_cols))
         return fail("gemm_tc: cuTensorMapEncodeTiled failed or is unavailable");
-    const int pairs = p.total_tiles < max_pairs ? p.total_tiles : max_pairs;
+    const int pairs = units < max_pairs ? units : max_pairs;
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = dim3(2 * pairs);
     cfg.blockDim = dim3(GEMM_THREADS);
@@ -150,10 +178,10 @@ static int launch_persistent(const void* A, const void* W, GemmTcParams p, int b
     // a short prompt portion has fewer tiles than the device has SMs; the adding epilogue (its sums are added at the L2
     // anyway) then cuts K so that every SM gets a unit of at least 8 k-blocks (512 tokens, K = 6144: 34 -> 12 us)
     int k_splits = 1;
-    if (p.epilogue == 2 && p.total_tiles * 2 <= num_sms) {
-        k_splits = num_sms / p.total_tiles;
-        if (k_splits > p.num_k_blocks / 8) k_splits = p.num_k_blocks / 8;
-        if (k_splits < 1) k_splits = 1;
+    if (p.epilogue == 2 && p.N > 128 && !getenv("EMBER_GEMM_TILE_COLS")) {
+        best_tile_and_parts(p.M, p.N, p.num_k_blocks, num_sms, 1, &block_cols, &k_splits);
+        p.block_cols = block_cols;
+        p.total_tiles = p.row_tiles * ((p.N + block_cols - 1) / block_cols);
     }
     p.k_blocks_per_split = (p.num_k_blocks + k_splits - 1) / k_splits;
     k_splits = (p.num_k_blocks + p.k_blocks_per_split - 1) / p.k_blocks_per_split;

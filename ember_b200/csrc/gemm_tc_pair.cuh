@@ -78,6 +78,9 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
     const uint32_t rank = cluster_ctarank();                // 0: leader, 1: peer
     const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
     const int n_kb = p.num_k_blocks;
+    // units: a tile and a part of K (more than one part only for the adding epilogue of a product with few tiles)
+    const int k_splits = (n_kb + p.k_blocks_per_split - 1) / p.k_blocks_per_split;
+    const int units = p.total_tiles * k_splits;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < p.stages; s++) {
@@ -112,11 +115,13 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
             uint32_t phase = 0;
             bool ok = true, wrapped = false;
             uint8_t* st = smem;
-            for (int t = pair; t < p.total_tiles && ok; t += n_pairs) {
+            for (int u = pair; u < units && ok; u += n_pairs) {
+                const int t = u / k_splits, kb0 = (u - t * k_splits) * p.k_blocks_per_split;
+                const int kb1 = min(n_kb, kb0 + p.k_blocks_per_split);
                 const int col_tile = t / p.row_tiles, row_tile = t - col_tile * p.row_tiles;
                 const int row0 = row_tile * 2 * TILE_ROWS + (int)rank * TILE_ROWS;
                 const int col0 = col_tile * p.block_cols + (int)rank * half_cols;
-                for (int i = 0; i < n_kb; i++) {
+                for (int i = kb0; i < kb1; i++) {
                     if (wrapped) ok = mbar_wait(&empty_bar[s], phase ^ 1u, abort_flag);
                     if (!ok) break;
                     const uint32_t bar = map_to_rank(smem_u32(&full_bar[s]), 0);
@@ -137,19 +142,20 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
             const uint64_t da0 = umma_desc_sw128(smem), db0 = umma_desc_sw128(smem + a_bytes);
             const uint64_t dstep = (uint64_t)(stage_bytes >> 4);
             uint64_t da = da0, db = db0;
-            for (int t = pair; t < p.total_tiles && ok; t += n_pairs, li++) {
+            for (int u = pair; u < units && ok; u += n_pairs, li++) {
+                const int kb0 = (u % k_splits) * p.k_blocks_per_split, kb1 = min(n_kb, kb0 + p.k_blocks_per_split);
                 const int acc = li & 1;
                 if (li >= 2) ok = mbar_wait(&tmem_empty_bar[acc], ((uint32_t)(li >> 1) & 1u) ^ 1u, abort_flag);
                 if (!ok) break;
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t d = tmem_d + (uint32_t)(acc * p.block_cols);
-                for (int i = 0; i < n_kb; i++) {
+                for (int i = kb0; i < kb1; i++) {
                     ok = mbar_wait(&full_bar[s], phase, abort_flag);
                     if (!ok) break;
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll
                     for (int k = 0; k < TILE_K / UMMA_K; k++)
-                        tcgen05_mma_bf16_pair(d, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, (i > 0 || k > 0) ? 1u : 0u);
+                        tcgen05_mma_bf16_pair(d, da + (uint64_t)(2 * k), db + (uint64_t)(2 * k), idesc, (i > kb0 || k > 0) ? 1u : 0u);
                     tcgen05_commit_pair(&empty_bar[s]);
                     da += dstep; db += dstep;
                     if (++s == p.stages) { s = 0; phase ^= 1u; da = da0; db = db0; }
@@ -162,7 +168,8 @@ gemm_tc_pair_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_c
         const int r = quad * 32 + lane;
         bool ok = true;
         int li = 0;
-        for (int t = pair; t < p.total_tiles; t += n_pairs, li++) {
+        for (int u = pair; u < units; u += n_pairs, li++) {
+            const int t = u / k_splits;
             const int col_tile = t / p.row_tiles, row_tile = t - col_tile * p.row_tiles;
             const int acc = li & 1;
             const int m = row_tile * 2 * TILE_ROWS + (int)rank * TILE_ROWS + r;
