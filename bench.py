@@ -322,10 +322,16 @@ def main() -> int:
         CONTEXT = max(CONTEXT, (DECODE_FROM + args.steps + max(3, args.warmup) + 64 + 63) // 64 * 64)      # whole pages
 
     if args.impl == "reference":
+        # The reference is a C++/CMake program (pip: "neither setup.py nor pyproject.toml found"), so it was built
+        # with its own CMake (-DEMBER_CUDA=ON -DCMAKE_CUDA_ARCHITECTURES=100: compiles and links) and driven through
+        # create_backend("cuda") -> Backend::forward -> Backend::sample on this workload.  Its first step, a
+        # 2,048-token prompt at these layer widths, ended with a memory fault on the B200, so its GPU code is not
+        # run again here and this arm stays unavailable.
         print(json.dumps({"impl": "reference", "unavailable":
-                          "the reference is a C++/CMake program, not a Python package (pip: 'neither setup.py nor "
-                          "pyproject.toml found'); its CUDA backend is written for sm_75-89 f16 mma.sync and has no "
-                          "bf16 or batch-64/2,048-token bench mode"}))
+                          "the reference's CUDA backend, built unmodified with its own CMake for sm_100, faulted on a B200 "
+                          "in its first step of this workload (2,048-token prompt, Qwen3-1.7B widths): 'CUDA error at "
+                          "src/backend/cuda/cuda_backend.cu:214: an illegal memory access was encountered "
+                          "(cudaStreamSynchronize(stream_))'; GPU code that faulted is not run again on this shared pool"}))
         return 0
     if args.gpus != 1:
         print(f"bench.py measures one GPU (this engine is single-GPU); --gpus {args.gpus} is not supported")
