@@ -27,17 +27,17 @@ import torch
 from ..sampling import device as device_sampler
 from ..sampling.params import SamplingParams
 from .batch import StepEntry
-from .runner import ModelRunner
+from .runner import DeviceError, ModelRunner
 from .scheduler import Request, Scheduler, Sequence_
 
 
 class _InFlight:
     """A launched step whose sampled ids have not been read yet."""
 
-    __slots__ = ("batch", "rows", "host", "event")
+    __slots__ = ("batch", "rows", "host", "event", "err")
 
-    def __init__(self, batch, rows, host, event):
-        self.batch, self.rows, self.host, self.event = batch, rows, host, event
+    def __init__(self, batch, rows, host, event, err=0):
+        self.batch, self.rows, self.host, self.event, self.err = batch, rows, host, event, err
 
 
 class Engine:
@@ -112,7 +112,8 @@ class Engine:
 
     def _ids_staging(self, rows: int):
         if len(self._staging) < 4:
-            self._staging.append((torch.empty(max(self.runner.max_requests, 1), dtype=torch.int32, pin_memory=True),
+            # the sampled ids and, in the last place, the kernels' error word (``ModelRunner.ids_and_err``)
+            self._staging.append((torch.empty(max(self.runner.max_requests, 1) + 1, dtype=torch.int32, pin_memory=True),
                                   torch.cuda.Event()))
         self._staging_at = (self._staging_at + 1) % len(self._staging)
         return self._staging[self._staging_at]
@@ -128,10 +129,12 @@ class Engine:
                 ids = [int(t) for t in self.sampler(logits, params, counters)]
                 if self.pipeline:
                     self.runner.set_sampled_ids(ids)
-                return _InFlight(batch, rows, ids, None)
-            ids = device_sampler.sample(logits, params, counters, out=self.runner.sampled_ids[:rows])
+                # the host sampler has read the logits, so the step is complete: its error word can be read
+                read_error = getattr(self.runner, "read_error", None)
+                return _InFlight(batch, rows, ids, None, read_error() if read_error else 0)
+            device_sampler.sample(logits, params, counters, out=self.runner.sampled_ids[:rows])
             host, event = self._ids_staging(rows)
-            host[:rows].copy_(ids, non_blocking=True)
+            host.copy_(self.runner.ids_and_err, non_blocking=True)      # ids and the error word: one small copy
             event.record()
             return _InFlight(batch, rows, host, event)
         except Exception:
@@ -142,12 +145,16 @@ class Engine:
     def _commit(self, rec: _InFlight) -> None:
         sched = self.scheduler
         sampled: List[int] = []
+        code = rec.err
         if rec.rows:
             if rec.event is not None:
                 rec.event.synchronize()
                 sampled = rec.host[:rec.rows].tolist()
+                code = int(rec.host[-1])
             else:
                 sampled = rec.host
+        if code:
+            self._device_failed(code)
         if any(seq.finished is not None for seq, _ in rec.batch):
             # a speculated step holds requests that stopped on the token before it: their share is dropped
             batch, kept, it = [], [], iter(sampled)
@@ -160,6 +167,18 @@ class Engine:
             sched.commit(batch, kept)
             return
         sched.commit(rec.batch, sampled)
+
+    def _device_failed(self, code: int) -> None:
+        """A kernel of a committed step set the error word (a token or page id out of range, a bounded wait that
+        ran out): the step's tokens cannot be trusted.  Every running request ends with an error, a speculated
+        step in flight is dropped, the runner clears the word and the scratch the aborted kernels may have left
+        dirty, and the caller gets a ``DeviceError``."""
+        self._inflight = None
+        self.scheduler.fail_running()
+        reset = getattr(self.runner, "reset_after_error", None)
+        if reset:
+            reset()
+        raise DeviceError(ModelRunner.describe_error(code))
 
     def _speculate(self, rec: _InFlight) -> Optional[_InFlight]:
         """The step after the one in flight, if the host can lay it out without that step's ids: every

@@ -61,10 +61,13 @@ class ModelRunner:
         self.storage = CacheStorage(self.cache, self.device, self.dtype)
         self.workspace = Workspace(self.device)
         self._packer = StepPacker()
-        self.err = torch.zeros(1, dtype=torch.int32, device=self.device)
-        # where a sampler may leave a step's ids for the next step to read on the device (a token
-        # -(r + 1) of a step names row r of this buffer); the address is fixed, graphs capture it
-        self.sampled_ids = torch.zeros(max(self.max_requests, 1), dtype=torch.int32, device=self.device)
+        # one small buffer holds the sampler's output and, behind it, the kernels' error word, so that the engine
+        # reads both back with the step's single device-to-host copy.  ``sampled_ids``: where a sampler may leave
+        # a step's ids for the next step to read on the device (a token -(r + 1) of a step names row r); the
+        # address is fixed, graphs capture it.  ``err``: bits set by kernels (see ``describe_error``).
+        self.ids_and_err = torch.zeros(max(self.max_requests, 1) + 1, dtype=torch.int32, device=self.device)
+        self.sampled_ids = self.ids_and_err[:-1]
+        self.err = self.ids_and_err[-1:]
         self.steps = 0
         # decode steps (one token per run) are captured into CUDA graphs, one per (runs, wanted rows,
         # context bucket); the reference does the same for its decode steps (src/backend/cuda/cuda_backend.cu:376-454)
@@ -152,7 +155,8 @@ class ModelRunner:
         ctx = StepContext(packed, self.workspace, self.device, self.max_batch_tokens, err=self.err,
                           max_context=ctx_bucket, prev_ids=self.sampled_ids)          # uploads this step's integers
         entry = self._graphs.get(key)
-        if entry is not None and entry[1] == self.workspace.version and entry[3] == ctx.ints.data_ptr():
+        if (entry is not None and entry[1] == self.workspace.version and entry[3] == ctx.ints.data_ptr()
+                and entry[5] == ops.scratch_version()):
             entry[0].replay()
             self.graph_replays += 1
             ops.add_launches(entry[4])
@@ -160,29 +164,44 @@ class ModelRunner:
         if key not in self._graph_seen:
             self._graph_seen.add(key)
             return self.model.forward(ctx, self.storage)
-        version = self.workspace.version
+        version, scratch_version = self.workspace.version, ops.scratch_version()
         n0 = ops.launch_count()
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.graph(graph):
             cap = StepContext(packed, self.workspace, self.device, self.max_batch_tokens, err=self.err,
                               max_context=ctx_bucket, upload=False, prev_ids=self.sampled_ids)
             logits = self.model.forward(cap, self.storage)
-        if self.workspace.version != version or cap.ints.data_ptr() != ctx.ints.data_ptr():
+        if (self.workspace.version != version or cap.ints.data_ptr() != ctx.ints.data_ptr()
+                or ops.scratch_version() != scratch_version):
             # a buffer was (re)allocated while capturing: the graph holds stale pointers; run eagerly
             self._graph_seen.discard(key)
             return self.model.forward(ctx, self.storage)
         if len(self._graphs) > 64:
             self._graphs.clear()
-        self._graphs[key] = (graph, version, logits, ctx.ints.data_ptr(), ops.launch_count() - n0)
+        self._graphs[key] = (graph, version, logits, ctx.ints.data_ptr(), ops.launch_count() - n0, scratch_version)
         graph.replay()
         self.graph_replays += 1
         return logits
 
+    @staticmethod
+    def describe_error(code: int) -> str:
+        what = [n for b, n in ((1, "a token id outside the vocabulary"), (2, "a page id outside the pool"),
+                               (4, "a bounded wait ran out")) if code & b]
+        return "a kernel reported: " + (", ".join(what) or f"error word {code}")
+
+    def read_error(self) -> int:
+        """The kernels' error word (synchronises)."""
+        return int(self.err.item())
+
+    def reset_after_error(self) -> None:
+        """After a reported error: clears the error word and the split-K scratch, which an aborted product may
+        have left non-zero (every later product relies on finding it zeroed)."""
+        self.err.zero_()
+        ops.zero_scratch(self.device)
+
     def check_device(self) -> None:
-        """Raises if a kernel recorded an out-of-range index (synchronises)."""
-        code = int(self.err.item())
+        """Raises if a kernel recorded an out-of-range index or a wait that ran out (synchronises)."""
+        code = self.read_error()
         if code:
-            self.err.zero_()
-            what = [n for b, n in ((1, "a token id outside the vocabulary"), (2, "a page id outside the pool"),
-                                   (4, "a bounded wait ran out")) if code & b]
-            raise DeviceError("a kernel reported: " + ", ".join(what))
+            self.reset_after_error()
+            raise DeviceError(self.describe_error(code))

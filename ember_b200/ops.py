@@ -264,13 +264,37 @@ def _sms(device) -> int:
     return n
 
 
-def _scratch(device, floats: int) -> torch.Tensor:
-    """Zero-filled fp32 scratch for split-K partial sums; the kernels leave it zeroed."""
+_scratch_version = 0
+
+
+def scratch_version() -> int:
+    """Grows whenever the split-K scratch is (re)allocated: a captured CUDA graph holds the old address and must
+    not be replayed afterwards."""
+    return _scratch_version
+
+
+def reserve_scratch(device, floats: int) -> torch.Tensor:
+    """Makes the split-K scratch at least ``floats`` long.  A ``Linear`` reserves 128 x its output width when it
+    is built, so that a loaded model never grows the scratch inside a step."""
+    global _scratch_version
+    device = torch.device(device)
     t = _tc_scratch.get(device)
     if t is None or t.numel() < floats:
-        t = torch.zeros(max(floats, 1 << 20), dtype=torch.float32, device=device)
+        t = torch.zeros(max(int(floats), 1 << 20), dtype=torch.float32, device=device)
         _tc_scratch[device] = t
+        _scratch_version += 1
     return t
+
+
+def zero_scratch(device) -> None:
+    t = _tc_scratch.get(torch.device(device))
+    if t is not None:
+        t.zero_()
+
+
+def _scratch(device, floats: int) -> torch.Tensor:
+    """Zero-filled fp32 scratch for split-K partial sums; the kernels leave it zeroed."""
+    return reserve_scratch(device, floats)
 
 
 def gemm_tc_usable(x: torch.Tensor, w: torch.Tensor, bias, epilogue: int) -> bool:

@@ -19,7 +19,10 @@ class Linear:
         self.weight = weight            # [N, K], float32 or bfloat16, on the device
         self.bias = bias                # float32 [N] or None
         self.n, self.k = weight.shape
-        self._tc = None                 # tensor-core plan, made on first use
+        if weight.is_cuda and weight.dtype == torch.bfloat16:
+            # the small-M tensor-core product sums its K parts in a shared fp32 scratch of up to 128 x N: made
+            # now, so that no step (least of all one inside a captured graph's lifetime) has to grow it
+            ops.reserve_scratch(weight.device, 128 * self.n)
 
     @classmethod
     def from_host(cls, w: torch.Tensor, rt: Runtime, bias: Optional[torch.Tensor] = None) -> "Linear":

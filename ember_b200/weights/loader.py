@@ -3,7 +3,11 @@
 A ``WeightStore`` wraps a source of named tensors (a model folder, or tensors made in
 memory).  Parts *declare* what they need (``take(name, shape)``); every problem —
 a missing tensor, a wrong shape, a tensor nobody asked for — is collected, and
-``finish()`` raises a single ``WeightError`` that lists them all.
+``finish()`` raises a single ``WeightError`` that lists them all.  Tensors nobody asked
+for are listed in that error whenever something else is wrong; when they are the only
+finding the load goes on with a warning that lists them (the reference looks tensors up
+by name and never sees the rest, src/backend/cpu/cpu_backend.cpp:50-75, and published
+files do carry extra buffers), unless the store is ``strict``.
 
 Stored precision is kept: bfloat16 stays bfloat16, float32 stays float32, float16 is
 converted to bfloat16 (the serving precision), integer tables become int32.  The
@@ -13,6 +17,7 @@ the parts' business, not the store's.
 from __future__ import annotations
 
 import fnmatch
+import warnings
 from typing import Dict, Iterable, List, Mapping, Optional, Sequence, Tuple
 
 import torch
@@ -54,6 +59,10 @@ class WeightError(ValueError):
         super().__init__("\n".join(lines))
 
 
+class UnexpectedTensorsWarning(UserWarning):
+    """The model folder holds tensors that no part of the model asked for."""
+
+
 class _DictSource:
     def __init__(self, tensors: Mapping[str, torch.Tensor]):
         self._t = dict(tensors)
@@ -79,9 +88,10 @@ _INTS = (torch.int8, torch.uint8, torch.int32, torch.int64)
 
 
 class WeightStore:
-    def __init__(self, source, description: str = "memory"):
+    def __init__(self, source, description: str = "memory", strict: bool = False):
         self._src = source
         self.description = description
+        self.strict = bool(strict)         # True: a tensor nobody asked for is an error of its own
         self._taken = set()
         self._missing: List[str] = []
         self._wrong_shape = []
@@ -90,12 +100,13 @@ class WeightStore:
 
     # -------------------------------------------------------------- constructors
     @classmethod
-    def from_dir(cls, model_dir: str) -> "WeightStore":
-        return cls(SafetensorsDir(model_dir), description=model_dir)
+    def from_dir(cls, model_dir: str, strict: bool = False) -> "WeightStore":
+        return cls(SafetensorsDir(model_dir), description=model_dir, strict=strict)
 
     @classmethod
-    def from_tensors(cls, tensors: Mapping[str, torch.Tensor], description: str = "memory") -> "WeightStore":
-        return cls(_DictSource(tensors), description=description)
+    def from_tensors(cls, tensors: Mapping[str, torch.Tensor], description: str = "memory",
+                     strict: bool = False) -> "WeightStore":
+        return cls(_DictSource(tensors), description=description, strict=strict)
 
     # ------------------------------------------------------------------- queries
     def has(self, name: str) -> bool:
@@ -132,7 +143,8 @@ class WeightStore:
         return t
 
     def finish(self) -> None:
-        """Raises ``WeightError`` if anything was missing, misshapen or left over."""
+        """Raises ``WeightError`` if anything was missing or misshapen (the error lists left-over tensors too);
+        left-over tensors alone give a warning, or the error if the store is strict."""
         unexpected = []
         for n in self._src.names():
             if n in self._taken:
@@ -140,6 +152,11 @@ class WeightStore:
             if any(fnmatch.fnmatchcase(n, p) for p in self._ignored_patterns):
                 continue
             unexpected.append(n)
+        if unexpected and not (self._missing or self._wrong_shape or self._wrong_dtype or self.strict):
+            shown = ", ".join(sorted(unexpected)[:12]) + (f", ... and {len(unexpected) - 12} more" if len(unexpected) > 12 else "")
+            warnings.warn(f"the weights in {self.description} hold {len(unexpected)} tensor(s) the model does not use: {shown}",
+                          UnexpectedTensorsWarning, stacklevel=2)
+            return
         if self._missing or self._wrong_shape or self._wrong_dtype or unexpected:
             raise WeightError(self.description, sorted(self._missing), sorted(unexpected),
                               sorted(self._wrong_shape), sorted(self._wrong_dtype))

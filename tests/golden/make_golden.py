@@ -9,8 +9,11 @@ It builds the reference's CPU library out of tree in a temporary folder, compile
 tests/golden/ref_driver.cpp against it, writes the two tiny models with this repository's
 random-weights mode (bfloat16 values, so every reader widens them exactly), and stores the
 reference's logits for whole prompts and for chunked feeding from a non-zero first block,
-plus a checksum of the weights.  tests/test_plain_golden.py compares the plain implementation
-with these numbers.
+together with the two models' tensors themselves (bfloat16 bit patterns, about 100 KB each), so that the
+comparison never depends on a random generator drawing the same numbers again.  It also stores tokens drawn
+by the reference's host sampler (src/backend/sampling_host.cpp:68-85) for a list of (logits row, parameters,
+seed, counter) cases.  tests/test_plain_golden.py compares the plain implementation and
+ember_b200/sampling/host.py with these numbers.
 """
 from __future__ import annotations
 
@@ -32,6 +35,24 @@ from ember_b200.weights import write_model_dir  # noqa: E402
 def weights_checksum(model_dir: str) -> str:
     with open(os.path.join(model_dir, "model.safetensors"), "rb") as f:
         return hashlib.sha256(f.read()).hexdigest()
+
+
+def sampler_cases(vocab: int = 1531, rows: int = 6):
+    """Logits rows with ties and clusters, and the cases drawn from them: (row, temperature, top_p, top_k,
+    min_p, seed, counter)."""
+    rng = np.random.default_rng(20240607)
+    logits = (rng.normal(size=(rows, vocab)) * 2.0).astype(np.float32)
+    logits[1, [7, 900]] = logits[1].max() + 0.5                 # a tie at the top
+    logits[2] = np.round(logits[2] * 2) / 2                     # many ties everywhere
+    logits[3, :40] += 6.0                                       # a cluster of likely tokens
+    variants = [(0.0, 1.0, 0, 0.0), (1.0, 1.0, 0, 0.0), (0.7, 0.8, 20, 0.0), (1.3, 0.7, 0, 0.0), (0.6, 1.0, 5, 0.0),
+                (1.0, 1.0, 0, 0.05), (0.9, 0.8, 20, 0.02), (1.0, 1.0, 1, 0.0), (2.0, 0.95, 100, 0.0), (0.5, 0.5, 0, 0.1)]
+    cases = []
+    for r in range(rows):
+        for vi, (t, tp, tk, mp) in enumerate(variants):
+            for rep in range(3):
+                cases.append((r, t, tp, tk, mp, 1000 + 17 * vi + rep, 5 + 31 * rep + r))
+    return logits, cases
 
 
 def main() -> None:
@@ -58,6 +79,10 @@ def main() -> None:
                         norm_std=TINY[name]["norm_std"])
         # the reference reads model_type, which to_json writes
         out[f"{name}.checksum"] = np.frombuffer(bytes.fromhex(weights_checksum(mdir)), dtype=np.uint8)
+        from ember_b200.weights import SafetensorsDir
+        sd = SafetensorsDir(mdir)
+        for tname in sd.names():                    # the tensors themselves, as bfloat16 bit patterns
+            out[f"{name}.tensor.{tname}"] = sd.get(tname).contiguous().view(torch.int16).numpy().copy()
         for pi, prompt in enumerate(tiny_prompts(name)):
             for label, first_block, chunk in (("whole", 0, 0), ("chunk7_block2", 2, 7)):
                 binf = os.path.join(work, "logits.bin")
@@ -66,6 +91,19 @@ def main() -> None:
                 rows = np.fromfile(binf, dtype=np.float32).reshape(-1, cfg.vocab_size)
                 out[f"{name}.p{pi}.{label}"] = rows
                 out[f"{name}.p{pi}.tokens"] = np.asarray(prompt, dtype=np.int32)
+    logits, cases = sampler_cases()
+    lbin, ctxt, otxt = (os.path.join(work, n) for n in ("sample_logits.bin", "sample_cases.txt", "sample_out.txt"))
+    logits.tofile(lbin)
+    with open(ctxt, "w") as f:
+        for c in cases:
+            f.write("%d %.9g %.9g %d %.9g %d %d\n" % c)
+    subprocess.check_call([driver, "sample", lbin, str(logits.shape[1]), ctxt, otxt])
+    drawn = np.loadtxt(otxt, dtype=np.int64).reshape(-1, 2)
+    assert drawn.shape[0] == len(cases)
+    out["sampler.logits"] = logits
+    out["sampler.cases"] = np.asarray(cases, dtype=np.float64)
+    out["sampler.tokens"] = drawn[:, 0].astype(np.int32)
+    out["sampler.kept"] = drawn[:, 1].astype(np.int32)
     np.savez_compressed(os.path.join(here, "qwen3_reference_logits.npz"), **out)
     print("wrote", os.path.join(here, "qwen3_reference_logits.npz"), {k: v.shape for k, v in out.items()})
 

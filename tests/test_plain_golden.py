@@ -1,6 +1,7 @@
-"""The plain implementation against the reference's own CPU backend (numbers made once by
-tests/golden/make_golden.py) and against itself in float32."""
-import hashlib
+"""The plain implementation and the host sampler against the reference's own CPU code (numbers made once by
+tests/golden/make_golden.py, with the tiny models' tensors stored beside them) and the plain implementation
+against itself in float32."""
+import json
 import os
 
 import numpy as np
@@ -18,14 +19,23 @@ def _rel(a, b):
     return float(np.linalg.norm(a - b) / max(np.linalg.norm(b), 1e-30))
 
 
+def golden_model_dir(g, name, out_dir):
+    """The model folder the golden logits were made with, rebuilt from the tensors stored beside them."""
+    from ember_b200.weights import save_file
+    from tests.tiny_configs import tiny_config
+    prefix = f"{name}.tensor."
+    tensors = {k[len(prefix):]: torch.from_numpy(g[k].copy()).view(torch.bfloat16) for k in g.files if k.startswith(prefix)}
+    os.makedirs(out_dir, exist_ok=True)
+    with open(os.path.join(out_dir, "config.json"), "w") as f:
+        json.dump(tiny_config(name).to_json(), f)
+    save_file(tensors, os.path.join(out_dir, "model.safetensors"))
+    return out_dir
+
+
 @pytest.mark.parametrize("name", GOLDEN_CONFIGS)
-def test_plain_matches_reference_cpu_backend(name, tiny_model_dirs):
+def test_plain_matches_reference_cpu_backend(name, tmp_path):
     g = np.load(GOLDEN)
-    mdir = tiny_model_dirs[name]
-    with open(os.path.join(mdir, "model.safetensors"), "rb") as f:
-        digest = hashlib.sha256(f.read()).digest()
-    if digest != bytes(g[f"{name}.checksum"]):
-        pytest.skip("this torch build draws other random weights than the ones the golden logits were made with")
+    mdir = golden_model_dir(g, name, str(tmp_path / name))
     plain = PlainQwen3(mdir, dtype=torch.float64)
     for pi, prompt in enumerate(tiny_prompts(name)):
         assert list(g[f"{name}.p{pi}.tokens"]) == prompt
@@ -38,6 +48,20 @@ def test_plain_matches_reference_cpu_backend(name, tiny_model_dirs):
         ends = [min(len(prompt), s + 7) - 1 for s in range(0, len(prompt), 7)]
         for row, e in zip(chunked, ends):
             assert _rel(logits[e], row) < 2e-6
+
+
+def test_host_sampler_draws_the_reference_tokens():
+    """ember_b200/sampling/host.py against tokens the reference's sample_host drew
+    (src/backend/sampling_host.cpp:68-85) for 180 (logits row, parameters, seed, counter) cases, and the size of
+    the kept set against its sampling_distribution."""
+    from ember_b200.sampling import SamplingParams, sample_host, sampling_distribution
+    g = np.load(GOLDEN)
+    logits, cases = g["sampler.logits"], g["sampler.cases"]
+    assert len(cases) == len(g["sampler.tokens"]) == 180
+    for (row, t, tp, tk, mp, seed, counter), tok, kept in zip(cases, g["sampler.tokens"], g["sampler.kept"]):
+        p = SamplingParams(temperature=float(t), top_p=float(tp), top_k=int(tk), min_p=float(mp), seed=int(seed))
+        assert sample_host(logits[int(row)], p, int(counter)) == int(tok), (row, t, tp, tk, mp, seed, counter)
+        assert len(sampling_distribution(logits[int(row)], p)) == int(kept)
 
 
 @pytest.mark.parametrize("name", sorted(TINY))

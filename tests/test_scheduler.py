@@ -202,3 +202,56 @@ def test_pipelined_engine_takes_new_requests_and_cancellations():
     assert a.finished == "cancelled" and list(b.output) == expected_generation([9, 8, 7, 6], 12, 977)
     assert list(a.output) == expected_generation([1, 2, 3], 40, 977)[:len(a.output)]
     assert runner.cache.used_pages() == [0]
+
+
+def test_state_slots_survive_preemption_and_reuse():
+    """The 60-requests-in-40-pages run with a fake model that is recurrent as well: every token goes, in order,
+    into its request's state slot and the slot goes into the output.  A slot shared by two requests, not zeroed
+    when a preempted request comes back, or lost, changes the tokens."""
+    rng = random.Random(11)
+    for pipeline in (False, True):
+        runner, eng = make(40 * 16, pipeline=pipeline, max_batch_tokens=256, max_prefill_chunk=40, max_seqs=16,
+                           state=True, max_requests=16)
+        reqs = []
+        for _ in range(60):
+            prompt = [rng.randrange(977) for _ in range(rng.randint(1, 120))]
+            n = rng.randint(1, 60)
+            reqs.append((prompt, n, eng.submit(Request(prompt=prompt, sampling=GREEDY, max_tokens=n, ignore_eos=True))))
+        run_all(eng, runner, [s for _, _, s in reqs])
+        eng.drain()
+        for prompt, n, s in reqs:
+            assert s.finished == "length" and s.output == expected_generation(prompt, n, 977, state=True)
+        assert eng.stats.preemptions > 0
+        # every admission zeroed its slot: first ones, those after a preemption, and tries that found no pages
+        assert runner.storage.resets >= 60 + eng.stats.preemptions
+        assert runner.cache.used_pages() == [0] and runner.cache.free_slots() == 16
+
+
+def test_a_slot_that_is_not_zeroed_is_noticed():
+    """The check of the test above can fail: with the zeroing switched off the recurrent fake model objects."""
+    runner, eng = make(64 * 16, state=True, max_requests=2, max_seqs=2)
+    eng.generate([5, 6, 7], max_tokens=3, ignore_eos=True)
+    runner.storage.reset_slot = lambda slot: None
+    with pytest.raises(AssertionError, match="not zeroed"):
+        eng.generate([8, 9], max_tokens=3, ignore_eos=True)
+
+
+def test_kernel_error_word_fails_the_running_requests():
+    """A kernel's error word (a page id out of range, a wait that ran out) reaches the engine with the step's ids:
+    the requests of that step end with an error, their pages go back, the runner is told to clean up, the caller
+    gets a DeviceError, and the engine is usable afterwards."""
+    from ember_b200.engine.runner import DeviceError
+    for pipeline in (False, True):
+        runner, eng = make(256, pipeline=pipeline)
+        a = eng.submit(Request(prompt=[1, 2, 3], sampling=GREEDY, max_tokens=50, ignore_eos=True))
+        b = eng.submit(Request(prompt=[4, 5], sampling=GREEDY, max_tokens=50, ignore_eos=True))
+        for _ in range(3):
+            assert eng.step()
+        runner.err_code = 2
+        with pytest.raises(DeviceError, match="page id outside the pool"):
+            for _ in range(3):
+                eng.step()
+        assert a.finished == "error" and b.finished == "error"
+        assert runner.resets_after_error == 1 and runner.err_code == 0
+        assert runner.cache.check() == "" and runner.cache.used_pages() == [0]
+        assert eng.generate([3, 1, 4], max_tokens=5, ignore_eos=True) == expected_generation([3, 1, 4], 5, 977)

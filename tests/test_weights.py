@@ -65,6 +65,20 @@ def test_one_error_lists_missing_unexpected_and_wrong_shapes():
         assert needle in text
 
 
+def test_extra_tensors_alone_are_a_warning_unless_strict():
+    """A folder that carries a tensor the model does not use loads, with a warning that names it (the reference
+    never sees such tensors: it looks up by name); a strict store makes it the listed error."""
+    from ember_b200.weights import UnexpectedTensorsWarning
+    spec = tiny_config("a").to_model_spec()
+    tensors = dict(random_tensors(spec, seed=4))
+    tensors["model.layers.0.self_attn.rotary_emb.inv_freq"] = torch.zeros(8)
+    with pytest.warns(UnexpectedTensorsWarning, match="rotary_emb.inv_freq"):
+        CausalLM(spec).load(WeightStore.from_tensors(tensors, "test"), CPU)
+    with pytest.raises(WeightError) as ei:
+        CausalLM(spec).load(WeightStore.from_tensors(tensors, "test", strict=True), CPU)
+    assert ei.value.unexpected == ["model.layers.0.self_attn.rotary_emb.inv_freq"] and not ei.value.missing
+
+
 def test_stored_precision_is_kept_and_tied_head_is_tolerated():
     spec = tiny_config("a").to_model_spec()           # tied
     tensors = dict(random_tensors(spec, seed=2))
