@@ -317,6 +317,67 @@ def test_attention_general(heads, kv, D, page, dt, window):
         assert rel(out.float().view(T, heads, D), want) < (6e-3 if dt == torch.bfloat16 else 3e-6)
 
 
+@pytest.mark.parametrize("page", [16, 64])
+def test_attention_long_context(page):
+    """Contexts beyond 8,192 keys at the benchmark's head geometry: a 2,048-token portion whose first query already
+    sees 8,200 cached keys (the tcgen05 kernel), and single tokens over 9,000 and 12,345 keys with the key range cut
+    into 16 splits, the most the planner makes, and into one (the TMA-fed decode kernel).  For the last query of
+    every run one key in the second page is made to stand out, for the first query of the portion the key just
+    before it, so that a far page that is skipped, fetched twice or merged with the wrong weight shows."""
+    from ember_b200 import ops
+    from ember_b200.engine.batch import StepBatch, attention_tiles
+    heads, kv, D, dt, dev = 16, 8, 128, torch.bfloat16, "cuda"
+    torch.manual_seed(page)
+    ctx_lens, new = [8200 + 2048, 9000, 12345], [2048, 1, 1]
+    S = len(ctx_lens)
+    nblk = max((c + page - 1) // page for c in ctx_lens)
+    pages = S * nblk + 5
+    perm = torch.randperm(pages)[:S * nblk].reshape(S, nblk).int()
+    kp = torch.zeros(pages, kv, page, D, dtype=dt)
+    vp = torch.zeros_like(kp)
+    ks, vs, qs = [], [], []
+    for s in range(S):
+        k = torch.randn(ctx_lens[s], kv, D) * 0.5
+        v = torch.randn(ctx_lens[s], kv, D)
+        q = torch.randn(new[s], heads, D) * 0.5
+        k[page + 3] = q[-1, ::heads // kv] * 4.0
+        if new[s] > 1:
+            k[ctx_lens[s] - new[s] - 1] = q[0, ::heads // kv] * 4.0
+        ks.append(k.to(dt).float()), vs.append(v.to(dt).float()), qs.append(q.to(dt).float())
+        for b in range(nblk):
+            lo, hi = b * page, min((b + 1) * page, ctx_lens[s])
+            if lo < hi:
+                kp[perm[s, b], :, :hi - lo] = k[lo:hi].to(dt).transpose(0, 1)
+                vp[perm[s, b], :, :hi - lo] = v[lo:hi].to(dt).transpose(0, 1)
+    T = sum(new)
+    q_all = torch.cat(qs).to(dt).to(dev).contiguous()
+    positions = np.concatenate([np.arange(c - n, c) for c, n in zip(ctx_lens, new)]).astype(np.int32)
+    batch = StepBatch(requests=list(range(S)), tokens=np.zeros(T, np.int32), positions=positions,
+                      seq_of=np.repeat(np.arange(S), new).astype(np.int32), query_start=np.cumsum([0] + new).astype(np.int32),
+                      context_len=np.asarray(ctx_lens, np.int32), block_tables=[perm.numpy()],
+                      state_slots=np.zeros(S, np.int32), logit_rows=np.zeros(0, np.int32))
+    scale = 1.0 / math.sqrt(D)
+    want = torch.cat([attention_ref(qs[s].to(dev), ks[s].to(dev), vs[s].to(dev), scale, 0) for s in range(S)])
+    err = torch.zeros(1, dtype=torch.int32, device=dev)
+    kd, vd, pd = kp.to(dev), vp.to(dev), perm.to(dev)
+    out = torch.zeros(T, heads * D, device=dev, dtype=dt)
+    multi = torch.from_numpy(attention_tiles(batch, ops.attention_fa_tile_queries(heads // kv), "multi")).to(dev)
+    ops.attention_fa(q_all.view(T, -1), kd, vd, out, heads, kv, D, multi, multi.shape[0], pd, page, 0, scale, err=err)
+    single = torch.from_numpy(attention_tiles(batch, 1, "single")).to(dev)
+    longest = max(ctx_lens)
+    for n_splits in (16, 1):
+        split_keys = ((longest + n_splits - 1) // n_splits + 63) // 64 * 64 if n_splits > 1 else 0
+        po = torch.empty(single.shape[0] * heads * n_splits * D, device=dev)
+        pml = torch.empty(single.shape[0] * heads * n_splits * 2, device=dev)
+        out[-2:] = 0
+        ops.attention_tc(q_all.view(T, -1), kd, vd, out, 1, heads, kv, D, single, single.shape[0], pd, page, 0, scale,
+                         n_splits, split_keys, po, pml, err=err)
+        assert int(err.item()) == 0
+        rows = (out.float().view(T, heads, D) - want).norm(dim=-1) / want.norm(dim=-1)
+        assert float(rows.max()) < 2e-2, (n_splits, float(rows.max()), int(rows.max(dim=-1).values.argmax()))
+        assert rel(out.float().view(T, heads, D), want) < 6e-3
+
+
 @pytest.mark.parametrize("heads,kv,page", [(16, 8, 16), (8, 1, 32), (3, 3, 64)])
 @pytest.mark.parametrize("window", [0, 700])
 def test_attention_fa_many_blocks(heads, kv, page, window):

@@ -7,7 +7,8 @@ import torch
 from ember_b200.config import Qwen3Config
 from ember_b200.weights import write_model_dir
 from tests.plain.qwen3_plain import PlainQwen3
-from tests.replay_helpers import collect, first_mismatch, max_live_tokens, trace_mixed, trace_tail_decode
+from tests.replay_helpers import (collect, first_mismatch, max_live_tokens, trace_mixed, trace_portions,
+                                  trace_tail_decode, trace_whole)
 from tests.test_replay_gpu import TOL, replay
 
 pytestmark = pytest.mark.gpu
@@ -47,19 +48,72 @@ def shape_dirs(tmp_path_factory):
     return get
 
 
+@pytest.mark.parametrize("page", [16, 64])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("mode", ["tail", "mixed"])
+@pytest.mark.parametrize("mode", ["whole", "tail", "portions", "mixed"])
 @pytest.mark.parametrize("name", sorted(SHAPES))
-def test_published_layer_sizes(name, mode, dtype, shape_dirs):
+def test_published_layer_sizes(name, mode, dtype, page, shape_dirs):
     model_dir, requests, want = shape_dirs(name)
-    steps = trace_tail_decode(requests) if mode == "tail" else trace_mixed(requests, live=3, seed=2)
-    outputs = replay(model_dir, dtype, steps, max_live_tokens(steps))
+    steps = {"whole": trace_whole, "tail": trace_tail_decode, "portions": trace_portions,
+             "mixed": lambda r: trace_mixed(r, live=3, seed=2)}[mode](requests)
+    outputs = replay(model_dir, dtype, steps, max_live_tokens(steps), page_tokens=page)
     got = collect(steps, outputs)
     for rid, toks in requests.items():
         assert sorted(got[rid]) == list(range(len(toks)))
     first, worst = first_mismatch(got, want, TOL[dtype])
-    print(f"{name} {dtype} {mode}: worst relative error {worst:.3e}")
+    print(f"{name} {dtype} {mode} page {page}: worst relative error {worst:.3e}")
     assert first is None, f"first wrong position (request, position, error): {first}; worst {worst:.3e}"
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_context_in_portions_then_token_by_token(dtype, shape_dirs):
+    """8,224 tokens at the benchmark's layer widths with the entry point's 64-token pages: four portions of 2,048
+    (each q/k/v product finishes its heads in the epilogue; every portion's attention reads the pages the earlier
+    ones wrote), then 32 single tokens over more than 8,192 keys (the key range cut into the most splits the
+    planner makes).  The last row of every portion and every decoded row against the plain implementation (the
+    reference's counterpart feeds 300 / 37 / 363 tokens from block 3: tests/test_model.cpp:124-157)."""
+    from tests.plain.qwen3_plain import linear, rmsnorm
+    from ember_b200.engine.replay import TraceReplayer
+    from ember_b200.engine.runner import ModelRunner
+    from tests.replay_helpers import rel_err
+    import tempfile
+    model_dir, _, _ = shape_dirs("1.7b")
+    rng = np.random.default_rng(21)
+    n, portion, tail = 8224, 2048, 32
+    toks = rng.integers(0, SHAPES["1.7b"]["vocab_size"], size=n).tolist()
+    plain = PlainQwen3(model_dir, torch.float32)
+    rows = [portion * (i + 1) - 1 for i in range((n - tail) // portion)] + list(range(n - tail, n))
+    h = plain.hidden_states(toks)[-1][rows]
+    ref = linear(rmsnorm(h, plain.w["model.norm.weight"], plain.cfg["eps"]), plain.w["model.embed_tokens.weight"]).numpy()
+    steps, at = [], 0
+    while at < n - tail:
+        steps.append({"step": len(steps), "entries": [{"id": "a", "tokens": toks[at:at + portion], "want": [portion - 1]}],
+                      "end": []})
+        at += portion
+    assert at == n - tail
+    for t in range(at, n):
+        steps.append({"step": len(steps), "entries": [{"id": "a", "tokens": [toks[t]], "want": [0]}],
+                      "end": ["a"] if t == n - 1 else []})
+    # the model's position limit in the test folder is 4,096; the long request needs more
+    import json, os, shutil
+    with tempfile.TemporaryDirectory() as long_dir:
+        for f in os.listdir(model_dir):
+            if f != "config.json":
+                os.symlink(os.path.join(model_dir, f), os.path.join(long_dir, f))
+        with open(os.path.join(model_dir, "config.json")) as f:
+            cfg = json.load(f)
+        cfg["max_position_embeddings"] = 16384
+        with open(os.path.join(long_dir, "config.json"), "w") as f:
+            json.dump(cfg, f)
+        runner = ModelRunner.from_dir(long_dir, dtype=dtype, capacity_tokens=n + 96, max_batch_tokens=portion,
+                                      max_requests=2, page_tokens=64)
+        with tempfile.TemporaryDirectory() as out:
+            rp = TraceReplayer(runner, out)
+            got = np.concatenate([rp.run_step(s) for s in steps])
+        runner.check_device()
+    errs = [rel_err(got[i], ref[i]) for i in range(len(rows))]
+    print(f"long context {dtype}: worst relative error {max(errs):.3e} at row {rows[int(np.argmax(errs))]}")
+    assert max(errs) <= TOL[dtype], errs
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])

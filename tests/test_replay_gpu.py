@@ -42,12 +42,12 @@ def plain_logits(tiny_model_dirs):
     return get
 
 
-def replay(model_dir, dtype, steps, capacity):
+def replay(model_dir, dtype, steps, capacity, page_tokens=16, max_batch_tokens=512):
     from ember_b200.engine.replay import TraceReplayer
     from ember_b200.engine.runner import ModelRunner
     import tempfile
-    runner = ModelRunner.from_dir(model_dir, dtype=dtype, capacity_tokens=capacity, max_batch_tokens=512,
-                                  max_requests=8)
+    runner = ModelRunner.from_dir(model_dir, dtype=dtype, capacity_tokens=capacity, max_batch_tokens=max_batch_tokens,
+                                  max_requests=8, page_tokens=page_tokens)
     with tempfile.TemporaryDirectory() as out:
         rp = TraceReplayer(runner, out)
         outputs = {}
@@ -64,24 +64,25 @@ LENGTHS = {"a": (5, 17, 33, 100), "b": (1, 31, 64, 100, 130), "c": (3, 70, 200, 
            "e": (4, 47, 97, 150), "f": (3, 24, 25, 77, 160)}
 
 
+@pytest.mark.parametrize("page", [16, 32, 64])          # 16: the reference's block; 64: what the entry point and the benchmark use
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("name", sorted(TINY))
 @pytest.mark.parametrize("mode", ["whole", "tail", "portions", "mixed"])
-def test_replay_modes(name, dtype, mode, tiny_model_dirs, plain_logits):
+def test_replay_modes(name, dtype, mode, page, tiny_model_dirs, plain_logits):
     requests = make_requests(name, LENGTHS[name], seed=5)
     if mode == "mixed":
         requests = make_requests(name, LENGTHS[name] + (70, 45, 90, 12), seed=6)
     steps = {"whole": trace_whole, "tail": trace_tail_decode, "portions": trace_portions,
              "mixed": lambda r: trace_mixed(r, live=4, seed=3)}[mode](requests)
-    capacity = max_live_tokens(steps)          # so few pages that they are used again
-    outputs = replay(tiny_model_dirs[name], dtype, steps, capacity)
+    capacity = max_live_tokens(steps)          # so few pages that they are used again (whole pages at every size)
+    outputs = replay(tiny_model_dirs[name], dtype, steps, capacity, page_tokens=page)
     got = collect(steps, outputs)
     want = plain_logits(name, requests)
     assert set(got) == set(requests)
     for rid, toks in requests.items():
         assert sorted(got[rid]) == list(range(len(toks)))
     first, worst = first_mismatch(got, want, TOL[dtype])
-    print(f"{name} {dtype} {mode}: worst relative error {worst:.3e}")
+    print(f"{name} {dtype} {mode} page {page}: worst relative error {worst:.3e}")
     assert first is None, f"first wrong position (request, position, error): {first}; worst {worst:.3e}"
 
 
