@@ -86,7 +86,7 @@ class PagePool:
 class CacheGroup:
     index: int
     need: CacheNeed
-    layers: List[int]
+    layers: List[object]           # cache ids: layer indices, or (layer, sub-id) pairs
     page_tokens: int
     pool: Optional[PagePool]       # None for kind "state"
 
@@ -124,10 +124,16 @@ class RequestCache:
         return [self._m._lib.ember_cache_first_live(self._m.core, self.handle, g) for g in range(len(self._m.groups))]
 
 
-def group_needs(needs: Mapping[int, Optional[CacheNeed]]) -> List[Tuple[CacheNeed, List[int]]]:
-    """Groups layers by equal need, in order of first appearance."""
-    out: List[Tuple[CacheNeed, List[int]]] = []
-    for layer in sorted(needs):
+def _cache_id_order(cache_id):
+    """Cache ids are layer indices, or (layer, sub-id) for a layer with several mixers: ordered by layer."""
+    return (cache_id, "") if isinstance(cache_id, int) else (cache_id[0], str(cache_id[1]))
+
+
+def group_needs(needs: Mapping[object, Optional[CacheNeed]]) -> List[Tuple[CacheNeed, List[object]]]:
+    """Groups caches (one per layer, or per mixer of a layer that has several) by equal need, in order of first
+    appearance."""
+    out: List[Tuple[CacheNeed, List[object]]] = []
+    for layer in sorted(needs, key=_cache_id_order):
         n = needs[layer]
         if n is None:
             continue
@@ -172,7 +178,7 @@ class CacheManager:
             if need.kind != "state":
                 pool = PagePool(pages[gi], _native=self._lib.ember_cache_pool(self.core, gi), _owner=self)
             self.groups.append(CacheGroup(gi, need, layers, page_tokens, pool))
-        self.layer_group: Dict[int, int] = {l: g.index for g in self.groups for l in g.layers}
+        self.layer_group: Dict[object, int] = {l: g.index for g in self.groups for l in g.layers}
         self._requests: Dict[Hashable, RequestCache] = {}
 
     def __del__(self):

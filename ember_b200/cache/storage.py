@@ -43,7 +43,8 @@ class CacheStorage:
                 self._state[g.index] = torch.zeros((len(g.layers), manager.max_requests) + tuple(g.need.state_shape),
                                                    dtype=sd, device=device)
 
-    def layer(self, layer: int) -> Optional[LayerCache]:
+    def layer(self, layer) -> Optional[LayerCache]:
+        """The cache of one mixer, by cache id (a layer index, or (layer, sub-id)); None if it owns none."""
         gi = self.manager.layer_group.get(layer)
         if gi is None:
             return None

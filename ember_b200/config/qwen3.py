@@ -202,11 +202,10 @@ class Qwen3Config:
                            activation=self.hidden_act)
         norm = RMSNormSpec(size=self.hidden_size, eps=self.rms_norm_eps)
         layers = tuple(
-            LayerSpec(mixer=attn(i), feed_forward=mlp, mixer_norm=norm, feed_forward_norm=norm,
-                      mixer_prefix=f"model.layers.{i}.self_attn.", feed_forward_prefix=f"model.layers.{i}.mlp.",
-                      mixer_norm_prefix=f"model.layers.{i}.input_layernorm.",
-                      feed_forward_norm_prefix=f"model.layers.{i}.post_attention_layernorm.",
-                      arrangement="prenorm")
+            LayerSpec.prenorm(mixer=attn(i), feed_forward=mlp, mixer_norm=norm, feed_forward_norm=norm,
+                              mixer_prefix=f"model.layers.{i}.self_attn.", feed_forward_prefix=f"model.layers.{i}.mlp.",
+                              mixer_norm_prefix=f"model.layers.{i}.input_layernorm.",
+                              feed_forward_norm_prefix=f"model.layers.{i}.post_attention_layernorm.")
             for i in range(self.num_hidden_layers))
         return ModelSpec(
             architecture=self.architecture, vocab_size=self.vocab_size, hidden_size=self.hidden_size,

@@ -97,17 +97,38 @@ class GatedMLPSpec(PartSpec):
 # ---------------------------------------------------------------------------- layers
 @dataclass(frozen=True)
 class LayerSpec:
-    """One block: which parts, how they are arranged, and where its weights live."""
+    """One block: the name of its arrangement (a registered class) and the parts that arrangement puts around the
+    residual stream, each under a *role*: ``(role, part spec, weight-name prefix)``.  Which roles exist, which
+    family each belongs to and in what order they run is the arrangement's business ("prenorm" knows
+    ``mixer_norm``, ``mixer``, ``feed_forward_norm``, ``feed_forward``); a block with four norms, with two mixers
+    or without a feed-forward is another arrangement over another set of roles, not another ``LayerSpec``."""
 
-    mixer: PartSpec
-    feed_forward: PartSpec
-    mixer_norm: PartSpec
-    feed_forward_norm: PartSpec
-    mixer_prefix: str                     # e.g. "model.layers.3.self_attn."
-    feed_forward_prefix: str              # e.g. "model.layers.3.mlp."
-    mixer_norm_prefix: str                # e.g. "model.layers.3.input_layernorm."
-    feed_forward_norm_prefix: str         # e.g. "model.layers.3.post_attention_layernorm."
-    arrangement: str = "prenorm"          # h += mixer(norm(h)); h += ffn(norm(h))
+    arrangement: str = "prenorm"
+    parts: Tuple[Tuple[str, PartSpec, str], ...] = ()
+
+    def __post_init__(self):
+        roles = [r for r, _, _ in self.parts]
+        if len(set(roles)) != len(roles):
+            raise ConfigError(f"a layer names a role twice: {roles}")
+
+    def roles(self) -> Tuple[str, ...]:
+        return tuple(r for r, _, _ in self.parts)
+
+    def part(self, role: str) -> Tuple[PartSpec, str]:
+        for r, spec, prefix in self.parts:
+            if r == role:
+                return spec, prefix
+        raise ConfigError(f"the layer has no part in the role {role!r} (it has: {', '.join(self.roles()) or 'none'})")
+
+    @classmethod
+    def prenorm(cls, mixer: PartSpec, feed_forward: PartSpec, mixer_norm: PartSpec, feed_forward_norm: PartSpec,
+                mixer_prefix: str, feed_forward_prefix: str, mixer_norm_prefix: str,
+                feed_forward_norm_prefix: str) -> "LayerSpec":
+        """h += mixer(norm(h)); h += feed_forward(norm(h)): prefixes are, for instance, "model.layers.3.self_attn.",
+        "model.layers.3.mlp.", "model.layers.3.input_layernorm.", "model.layers.3.post_attention_layernorm."."""
+        return cls("prenorm", (("mixer_norm", mixer_norm, mixer_norm_prefix), ("mixer", mixer, mixer_prefix),
+                               ("feed_forward_norm", feed_forward_norm, feed_forward_norm_prefix),
+                               ("feed_forward", feed_forward, feed_forward_prefix)))
 
 
 @dataclass(frozen=True)
@@ -141,6 +162,10 @@ class ModelSpec:
     # belong to their mixer's spec instead
     embedding_position: PartSpec = field(default_factory=NoPositionSpec)
     embedding_position_prefix: str = "model.embed_positions."
+    # h = embedding_multiplier * table[token] and logits = logit_scale * (norm(h) . head^T): 1.0 for Qwen3; other
+    # decoders scale the embedded tokens by sqrt(hidden) or the logits by a constant
+    embedding_multiplier: float = 1.0
+    logit_scale: float = 1.0
 
     def __post_init__(self):
         n = len(self.layers)

@@ -12,11 +12,11 @@ EMBER_DEFINE_LAST_ERROR
 namespace ember {
 
 // ------------------------------------------------------------------------------ embedding
-// h[t, :] = float(table[tokens[t], :]); no scaling.  A negative token -(r + 1) stands for the id that the
+// h[t, :] = scale * float(table[tokens[t], :]) (scale 1 for the reference's model: no scaling).  A negative token -(r + 1) stands for the id that the
 // sampler left in prev_ids[r]: a step can be launched before the host has read the step before it.
 template <typename TW>
 __global__ void embed_kernel(const int* __restrict__ tokens, const int* __restrict__ prev_ids, int n_prev,
-                             const TW* __restrict__ table, float* __restrict__ out, int H, int V,
+                             const TW* __restrict__ table, float* __restrict__ out, int H, int V, float scale,
                              int* __restrict__ err) {
     pdl_launch_dependents();
     pdl_wait();
@@ -30,7 +30,7 @@ __global__ void embed_kernel(const int* __restrict__ tokens, const int* __restri
         return;
     }
     const TW* row = table + (size_t)tok * H;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = to_float(row[i]);
+    for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = scale * to_float(row[i]);
 }
 
 // -------------------------------------------------------------------------------- RMSNorm
@@ -377,16 +377,16 @@ __global__ void silu_mul_interleaved_kernel(const T* __restrict__ x, T* __restri
 using namespace ember;
 
 EMBER_API int ember_embed(const int* tokens, const int* prev_ids, int n_prev, const void* table, int table_dtype,
-                          float* out, int T, int H, int V, int* err, void* stream) {
+                          float* out, int T, int H, int V, float scale, int* err, void* stream) {
     if (T <= 0) return 0;
     if (H <= 0 || V <= 0) return fail("embed: bad sizes H=%d V=%d", H, V);
     cudaStream_t st = (cudaStream_t)stream;
     const int threads = H >= 1024 ? 256 : 128;
     if (table_dtype == EMBER_F32)
-        launch_kernel(embed_kernel<float>, T, threads, 0, st, tokens, prev_ids, n_prev, (const float*)table, out, H, V, err);
+        launch_kernel(embed_kernel<float>, T, threads, 0, st, tokens, prev_ids, n_prev, (const float*)table, out, H, V, scale, err);
     else if (table_dtype == EMBER_BF16)
         launch_kernel(embed_kernel<__nv_bfloat16>, T, threads, 0, st, tokens, prev_ids, n_prev, (const __nv_bfloat16*)table, out, H, V,
-                      err);
+                      scale, err);
     else
         return fail("embed: unsupported table dtype %d", table_dtype);
     return check_launch("embed");

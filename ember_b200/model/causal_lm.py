@@ -55,6 +55,9 @@ class CausalLM:
         if self.embedding is not None:
             self.head = Linear.from_host(head, rt) if head is not None else Linear(self.embedding)
         self.final_norm.load(store, rt)
+        if s.logit_scale != 1.0:
+            # logits = scale * (norm(h) . head^T): the scale rides on the final norm's output
+            self.final_norm.scale_output(float(s.logit_scale))
         self.embedding_position.load(store, rt)
         for b in self.blocks:
             b.load(store, rt)
@@ -62,18 +65,24 @@ class CausalLM:
         return self
 
     # -------------------------------------------------------------------- cache
-    def cache_needs(self) -> Dict[int, Optional[CacheNeed]]:
-        """Need of every layer that owns a cache (a layer that only reads another's owns none)."""
+    @staticmethod
+    def cache_id(layer: int, sub: str):
+        """How the cache manager and the storage know one mixer's cache: the layer's index when the block has a
+        single mixer (sub-id ""), else (layer, sub-id)."""
+        return layer if sub == "" else (layer, sub)
+
+    def cache_needs(self) -> Dict[object, Optional[CacheNeed]]:
+        """Need of every mixer of every layer that owns a cache (a layer that only reads another's owns none),
+        as the blocks report them."""
         owners = {(e.cache_of if e.cache_of >= 0 else e.layer) for e in self.spec.schedule}
-        return {l: self.blocks[l].mixer.cache_need() for l in sorted(owners)}
+        return {self.cache_id(l, sub): need for l in sorted(owners) for sub, need in self.blocks[l].cache_needs().items()}
 
     def tile_requests(self):
-        """Attention tile shapes the mixers will ask the step context for (sent with the step's upload)."""
+        """Attention tile shapes the blocks' mixers will ask the step context for (sent with the step's upload)."""
         if not hasattr(self, "_tile_requests"):
             keys = []
             for b in self.blocks:
-                fn = getattr(b.mixer, "tile_requests", None)
-                for k in (fn() if fn else ()):
+                for k in b.tile_requests():
                     if k not in keys:
                         keys.append(k)
             self._tile_requests = tuple(keys)
@@ -83,11 +92,14 @@ class CausalLM:
     def forward(self, ctx, storage) -> Optional[torch.Tensor]:
         s, rt = self.spec, self.rt
         h = ctx.buf("model.residual", (ctx.max_tokens, s.hidden_size), torch.float32)
-        ops.embed(ctx.tokens, self.embedding, h, err=ctx.err, stream=ctx.stream, prev_ids=ctx.prev_ids)
+        ops.embed(ctx.tokens, self.embedding, h, err=ctx.err, stream=ctx.stream, prev_ids=ctx.prev_ids,
+                  scale=s.embedding_multiplier)
         self.embedding_position.on_embedding(ctx, h)          # nothing for rotary or absent encodings
         for e in s.schedule:
             owner = e.cache_of if e.cache_of >= 0 else e.layer
-            self.blocks[e.layer].forward(ctx, h, storage.layer(owner), owns_cache=(owner == e.layer))
+            block = self.blocks[e.layer]
+            caches = {sub: storage.layer(self.cache_id(owner, sub)) for sub in block.mixers}
+            block.forward(ctx, h, caches, owns_cache=(owner == e.layer))
         if ctx.R == 0:
             return None
         xn = ctx.buf_dyn("model.final_normed", ctx.R * s.hidden_size, rt.dtype).view(-1, s.hidden_size)

@@ -85,8 +85,8 @@ def _call(lib, fn, *args):
 
 # ------------------------------------------------------------------------------ elementwise
 def embed(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor, err: Optional[torch.Tensor] = None,
-          stream: Optional[int] = None, prev_ids: Optional[torch.Tensor] = None) -> None:
-    """out[t, :] = float(table[tokens[t], :]).  With ``prev_ids`` (int32, device) a token -(r + 1) is
+          stream: Optional[int] = None, prev_ids: Optional[torch.Tensor] = None, scale: float = 1.0) -> None:
+    """out[t, :] = scale * float(table[tokens[t], :]).  With ``prev_ids`` (int32, device) a token -(r + 1) is
     read as prev_ids[r]: the id the sampler wrote there in the step before."""
     _check(tokens, "tokens", torch.int32)
     if prev_ids is not None:
@@ -98,7 +98,7 @@ def embed(tokens: torch.Tensor, table: torch.Tensor, out: torch.Tensor, err: Opt
         raise KernelError(f"embed: output {tuple(out.shape)} does not fit {T} rows of width {H}")
     lib = _lib("elementwise")
     _call(lib, lib.ember_embed, _p(tokens), _p(prev_ids), c_int(prev_ids.numel() if prev_ids is not None else 0),
-          _p(table), c_int(dtype_code(table.dtype)), _p(out), c_int(T), c_int(H), c_int(V), _p(err),
+          _p(table), c_int(dtype_code(table.dtype)), _p(out), c_int(T), c_int(H), c_int(V), c_float(scale), _p(err),
           c_void_p(stream if stream is not None else current_stream_ptr()))
 
 
@@ -184,6 +184,9 @@ def gemm_simt(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, M: int, epilo
 
 
 # ------------------------------------------------------------------------------- attention
+ATTENTION_MAX_GROUP = 32     # query heads per key/value head the general attention kernel takes (its ATT_MAX_ROWS)
+
+
 def attention_tile_queries(group: int) -> int:
     """How many query tokens one tile of the general attention kernel may hold."""
     lib = _lib("attention")

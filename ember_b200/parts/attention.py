@@ -36,6 +36,12 @@ class Attention(Mixer):
             raise ConfigError(f"head_dim {s.head_dim} must be even and at most 256")
         if s.window < 0:
             raise ConfigError("window must be >= 0")
+        if s.group > ops.ATTENTION_MAX_GROUP:
+            # refused when the model is built, not at its first step: the general attention kernel (the whole
+            # float32 path, and bfloat16 geometries the tensor-core kernels do not take) holds one tile row per
+            # query head of a group
+            raise ConfigError(f"{s.group} query heads per key/value head: the attention kernels take at most "
+                              f"{ops.ATTENTION_MAX_GROUP}")
         self.position = build_part("position", s.position)
         self.scale = s.softmax_scale if s.softmax_scale is not None else 1.0 / math.sqrt(s.head_dim)
 

@@ -10,6 +10,7 @@ Interfaces (what a new part must provide):
 * ``PositionEncoding``: ``rotary_table(rt) -> (inv_freq_f32[rotary/2] | None, rotary_dim)``; encodings that
   act elsewhere may instead override ``on_embedding(ctx, h)``.  ``table_key()`` says which layers' frequencies are
   the same (they share the step's angle table that ``cos_sin`` makes from ``rotary_table``).
+* ``Norm`` may also provide ``scale_output(scale)`` (needed only as the final norm of a model with a logit scale).
 * ``Mixer``:         ``cache_need() -> CacheNeed | None`` and
   ``forward(ctx, x[T, hidden], residual_f32[T, hidden], cache: LayerCache | None, owns_cache: bool)``;
   it *adds* its result to ``residual``.
@@ -96,6 +97,11 @@ class Norm(Part):
 
     def forward(self, ctx, x: torch.Tensor, out: torch.Tensor, n_rows: int, rows: Optional[torch.Tensor] = None) -> None:
         raise NotImplementedError
+
+    def scale_output(self, scale: float) -> None:
+        """After ``load``: makes the norm's output ``scale`` times what it was (a model's logit scale is applied
+        this way to its final norm).  A norm that ends in a weight folds the factor into it."""
+        raise NotImplementedError(f"{type(self).__name__} cannot scale its output")
 
 
 class PositionEncoding(Part):

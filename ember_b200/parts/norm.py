@@ -22,6 +22,10 @@ class RMSNorm(Norm):
         w = store.take(self.prefix + "weight", (self.spec.size,))
         self.weight = rt.to_device(w, torch.float32) if w is not None else None
 
+    def scale_output(self, scale: float) -> None:
+        if self.weight is not None:
+            self.weight = self.weight * scale
+
     def forward(self, ctx, x: torch.Tensor, out: torch.Tensor, n_rows: int, rows: Optional[torch.Tensor] = None) -> None:
         ops.rmsnorm(x, self.weight, self.spec.eps, out, n_rows, rows=rows, stream=ctx.stream)
 

@@ -21,11 +21,11 @@ def test_head_dim_independent_of_hidden():
     assert c.q_dim == 192 and c.hidden_size == 96
     spec = c.to_model_spec()
     assert len(spec.layers) == 3 and [e.layer for e in spec.schedule] == [0, 1, 2]
-    a = spec.layers[1].mixer
+    a = spec.layers[1].part("mixer")[0]
     assert isinstance(a, AttentionSpec) and a.qk_norm and a.qk_norm_eps == 1e-5 and a.num_kv_heads == 1
     assert isinstance(a.position, RotarySpec) and a.position.theta == 1e6 and a.position.rotary_dim == 32
     assert isinstance(spec.final_norm, RMSNormSpec) and spec.final_norm.eps == 1e-5
-    assert not spec.tie_embeddings and spec.layers[2].mixer_prefix == "model.layers.2.self_attn."
+    assert not spec.tie_embeddings and spec.layers[2].part("mixer")[1] == "model.layers.2.self_attn."
 
 
 @pytest.mark.parametrize("patch,msg", [
@@ -84,9 +84,9 @@ def test_sliding_window_keys_give_layers_of_two_kinds():
     cfg = tiny_config("f")
     assert [cfg.layer_window(i) for i in range(3)] == [0, 24, 24]
     spec = cfg.to_model_spec()
-    assert [l.mixer.window for l in spec.layers] == [0, 24, 24]
+    assert [l.part("mixer")[0].window for l in spec.layers] == [0, 24, 24]
     assert Qwen3Config.from_json(cfg.to_json()) == cfg
     groups = CacheManager(CausalLM(spec).cache_needs(), 16, 256, 4).groups
     assert [(g.need.kind, g.layers) for g in groups] == [("full", [0]), ("window", [1, 2])]
     d = dict(TINY["f"]["json"], use_sliding_window=False)
-    assert [l.mixer.window for l in Qwen3Config.from_json(d).to_model_spec().layers] == [0, 0, 0]
+    assert [l.part("mixer")[0].window for l in Qwen3Config.from_json(d).to_model_spec().layers] == [0, 0, 0]

@@ -109,6 +109,77 @@ def test_preemption_on_the_device_keeps_the_tokens(tiny_model_dirs):
         assert o == plain.greedy(p, 30)
 
 
+@pytest.mark.parametrize("name", ["c", "f"])
+def test_preemption_on_the_device_bfloat16_at_the_entry_points_page_size(name, tiny_model_dirs):
+    """Preemption and recomputation in bfloat16 with 64-token pages: on heads of 128 (the tcgen05 kernels, "c") and
+    with a window group whose pages go back while requests run ("f").  Recomputing a request cuts its tokens into
+    other steps than the first pass did, so in bfloat16 a token may differ where two logits are close: every
+    token that was picked must be within bfloat16 reach of the plain implementation's maximum at its position,
+    and a run with pages to spare must pick tokens of the same quality."""
+    plain = PlainQwen3(tiny_model_dirs[name], torch.float64)
+    vocab = TINY[name]["json"]["vocab_size"]
+    rng = np.random.default_rng(18)
+    prompts = [rng.integers(0, vocab, size=n).tolist() for n in (70, 45, 100, 30)]
+    for tokens_of_cache, expect_preemption in ((384, True), (4096, False)):
+        llm = load(tiny_model_dirs, name, "bfloat16", kv_cache_tokens=tokens_of_cache, max_seqs=4, page_tokens=64,
+                   prefill_chunk=48)
+        outs = llm.generate(prompts, max_tokens=40, ignore_eos=True)
+        llm.runner.check_device()
+        assert (llm.stats.preemptions > 0) == expect_preemption
+        assert llm.runner.cache.check() == "" and not any(llm.runner.cache.used_pages())
+        for p, o in zip(prompts, outs):
+            assert len(o) == 40
+            logits = plain.logits(p + o).numpy()
+            for i, tok in enumerate(o):
+                row = logits[len(p) - 1 + i]
+                assert row.max() - row[tok] < 0.03 * (row.max() - row.min()), (name, tokens_of_cache, i)
+
+
+def test_state_slots_under_the_engine_with_preemption():
+    """A model whose mixers keep per-request state (a running mean in a state slot) beside attention, generated
+    from through the engine with so few pages that requests are preempted and admitted again into used slots:
+    the tokens equal those of a run that never preempts.  A slot that is not zeroed at re-admission, or shared,
+    changes the running mean and with it the tokens."""
+    from ember_b200.config import AttentionSpec, GatedMLPSpec, LayerSpec, ModelSpec, RMSNormSpec, RotarySpec, default_schedule
+    from ember_b200.engine.engine import Engine
+    from ember_b200.engine.runner import ModelRunner
+    from ember_b200.parts import register_part
+    from ember_b200.weights import WeightStore, random_tensors
+    from tests.test_parts_gpu import RunningMeanSpec, make_running_mean
+    register_part("mixer", "toy_running_mean", make_running_mean())
+    H, V = 48, 300
+    norm = RMSNormSpec(size=H, eps=1e-6)
+    attn = AttentionSpec(hidden_size=H, num_heads=3, num_kv_heads=1, head_dim=16, qk_norm=True,
+                         position=RotarySpec(head_dim=16, rotary_dim=16, theta=1e4))
+    mlp = GatedMLPSpec(hidden_size=H, intermediate_size=80)
+
+    def layer(i, mixer):
+        p = f"toy.layers.{i}."
+        return LayerSpec.prenorm(mixer=mixer, feed_forward=mlp, mixer_norm=norm, feed_forward_norm=norm,
+                                 mixer_prefix=p + "mixer.", feed_forward_prefix=p + "mlp.", mixer_norm_prefix=p + "norm_a.",
+                                 feed_forward_norm_prefix=p + "norm_b.")
+
+    spec = ModelSpec(architecture="ToyStateForCausalLM", vocab_size=V, hidden_size=H,
+                     layers=(layer(0, RunningMeanSpec(hidden_size=H)), layer(1, attn), layer(2, RunningMeanSpec(hidden_size=H))),
+                     schedule=default_schedule(3), final_norm=norm, final_norm_prefix="toy.norm.",
+                     embedding_name="toy.embed.weight", head_name="toy.head.weight", tie_embeddings=True, max_positions=512,
+                     init_std=0.3)
+    weights = dict(random_tensors(spec, seed=6, dtype=torch.float32))
+    rng = np.random.default_rng(9)
+    prompts = [rng.integers(0, V, size=n).tolist() for n in (20, 25, 30, 18, 40, 12)]
+    results = {}
+    for capacity in (96, 2048):
+        runner = ModelRunner(spec, WeightStore.from_tensors(weights), dtype="float32", capacity_tokens=capacity,
+                             max_batch_tokens=128, max_requests=4, page_tokens=16)
+        eng = Engine(runner, max_prefill_chunk=24)
+        results[capacity] = eng.generate(prompts, max_tokens=30, ignore_eos=True)
+        runner.check_device()
+        assert (eng.stats.preemptions > 0) == (capacity == 96)
+        assert runner.cache.check() == "" and runner.cache.free_slots() == 4
+    assert results[96] == results[2048]
+    assert len({tuple(o) for o in results[96]}) == len(prompts)          # the requests really differ
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_graph_replay_equals_eager_decoding(dtype, tiny_model_dirs):
     """Decode steps through captured graphs give the logits that eager steps give, while the batch

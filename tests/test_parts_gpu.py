@@ -226,7 +226,7 @@ def test_toy_mixer_with_state_is_registered_built_and_stepped():
 
     def layer(i, mixer):
         p = f"toy.layers.{i}."
-        return LayerSpec(mixer=mixer, feed_forward=mlp, mixer_norm=norm, feed_forward_norm=norm, mixer_prefix=p + "mixer.",
+        return LayerSpec.prenorm(mixer=mixer, feed_forward=mlp, mixer_norm=norm, feed_forward_norm=norm, mixer_prefix=p + "mixer.",
                          feed_forward_prefix=p + "mlp.", mixer_norm_prefix=p + "norm_a.", feed_forward_norm_prefix=p + "norm_b.")
 
     spec = ModelSpec(architecture="ToyForCausalLM", vocab_size=V, hidden_size=H,
@@ -341,7 +341,7 @@ def test_toy_routed_feed_forward_and_learned_positions():
 
     def layer(i, ff):
         p = f"toy.layers.{i}."
-        return LayerSpec(mixer=attn, feed_forward=ff, mixer_norm=norm, feed_forward_norm=norm, mixer_prefix=p + "attn.",
+        return LayerSpec.prenorm(mixer=attn, feed_forward=ff, mixer_norm=norm, feed_forward_norm=norm, mixer_prefix=p + "attn.",
                          feed_forward_prefix=p + "ff.", mixer_norm_prefix=p + "norm_a.", feed_forward_norm_prefix=p + "norm_b.")
 
     spec = ModelSpec(architecture="ToyRoutedForCausalLM", vocab_size=V, hidden_size=H,
@@ -395,3 +395,133 @@ def test_toy_routed_feed_forward_and_learned_positions():
             h = h + y
     want = plain.rmsnorm(h, w["toy.norm.weight"], 1e-5) @ w["toy.embed.weight"].t()
     assert rel(whole, want) < 1e-4
+
+
+# ------------------------------------------------- toy arrangements: four norms; two mixers in one layer
+def make_toy_arrangements():
+    from ember_b200.parts.block import Arrangement
+
+    class Sandwich(Arrangement):
+        """h += post_a(mixer(pre_a(h))); h += post_b(ffn(pre_b(h))): four norms a layer.  Mixers and feed-forwards
+        add into the buffer they are given, so the block hands them a zeroed one and norms it before adding."""
+        ROLES = {"pre_mixer_norm": "norm", "mixer": "mixer", "post_mixer_norm": "norm",
+                 "pre_feed_forward_norm": "norm", "feed_forward": "feed_forward", "post_feed_forward_norm": "norm"}
+
+        def forward(self, ctx, h, caches, owns_cache=True):
+            p, T = self.parts, ctx.T
+            x = ctx.buf("sandwich.normed", (ctx.max_tokens, h.shape[-1]), self.rt.dtype)
+            branch = ctx.buf("sandwich.branch", (ctx.max_tokens, h.shape[-1]), torch.float32)
+            normed = ctx.buf("sandwich.branch_normed", (ctx.max_tokens, h.shape[-1]), torch.float32)
+            for pre, inner, post in (("pre_mixer_norm", "mixer", "post_mixer_norm"),
+                                     ("pre_feed_forward_norm", "feed_forward", "post_feed_forward_norm")):
+                p[pre].forward(ctx, h, x, T)
+                branch.zero_()
+                if inner == "mixer":
+                    p[inner].forward(ctx, x, branch, caches[""], owns_cache)
+                else:
+                    p[inner].forward(ctx, x, branch)
+                p[post].forward(ctx, branch, normed, T)
+                h[:T] += normed[:T]
+
+    class TwoMixers(Arrangement):
+        """h += attention(norm_a(h)); h += memory(norm_m(h)); h += ffn(norm_f(h)): two mixers with caches of
+        different kinds (pages and a state slot) in one layer."""
+        ROLES = {"attention_norm": "norm", "attention": "mixer", "memory_norm": "norm", "memory": "mixer",
+                 "feed_forward_norm": "norm", "feed_forward": "feed_forward"}
+
+        def forward(self, ctx, h, caches, owns_cache=True):
+            p, T = self.parts, ctx.T
+            x = ctx.buf("two.normed", (ctx.max_tokens, h.shape[-1]), self.rt.dtype)
+            p["attention_norm"].forward(ctx, h, x, T)
+            p["attention"].forward(ctx, x, h, caches["attention"], owns_cache)
+            p["memory_norm"].forward(ctx, h, x, T)
+            p["memory"].forward(ctx, x, h, caches["memory"], owns_cache)
+            p["feed_forward_norm"].forward(ctx, h, x, T)
+            p["feed_forward"].forward(ctx, x, h)
+
+    return Sandwich, TwoMixers
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_toy_arrangements_four_norms_and_two_mixers(dtype):
+    """Arrangements defined here, registered without touching the framework's files: a layer with four norms, a
+    layer with two mixers (attention with pages beside a running mean with a state slot) and a plain pre-norm
+    layer in one model, which also scales its embedded tokens and its logits.  Whole equals portions beside
+    another request; the scales do what their definitions say."""
+    from dataclasses import replace
+    from ember_b200 import StepEntry
+    from ember_b200.config import AttentionSpec, GatedMLPSpec, LayerSpec, ModelSpec, RMSNormSpec, RotarySpec, default_schedule
+    from ember_b200.engine.runner import ModelRunner
+    from ember_b200.parts import register_part
+    from ember_b200.weights import WeightStore, random_tensors
+    Sandwich, TwoMixers = make_toy_arrangements()
+    register_part("arrangement", "toy_sandwich", Sandwich)
+    register_part("arrangement", "toy_two_mixers", TwoMixers)
+    register_part("mixer", "toy_running_mean", make_running_mean())
+    H, V = 64, 211
+    norm = RMSNormSpec(size=H, eps=1e-5)
+    attn = AttentionSpec(hidden_size=H, num_heads=4, num_kv_heads=2, head_dim=16, qk_norm=True,
+                         position=RotarySpec(head_dim=16, rotary_dim=16, theta=1e4))
+    mlp = GatedMLPSpec(hidden_size=H, intermediate_size=72)
+    mean = RunningMeanSpec(hidden_size=H)
+    sandwich = LayerSpec("toy_sandwich", (("pre_mixer_norm", norm, "t.0.n1."), ("mixer", attn, "t.0.attn."),
+                                          ("post_mixer_norm", norm, "t.0.n2."), ("pre_feed_forward_norm", norm, "t.0.n3."),
+                                          ("feed_forward", mlp, "t.0.mlp."), ("post_feed_forward_norm", norm, "t.0.n4.")))
+    two = LayerSpec("toy_two_mixers", (("attention_norm", norm, "t.1.na."), ("attention", attn, "t.1.attn."),
+                                       ("memory_norm", norm, "t.1.nm."), ("memory", mean, "t.1.mem."),
+                                       ("feed_forward_norm", norm, "t.1.nf."), ("feed_forward", mlp, "t.1.mlp.")))
+    pre = LayerSpec.prenorm(mixer=attn, feed_forward=mlp, mixer_norm=norm, feed_forward_norm=norm, mixer_prefix="t.2.attn.",
+                            feed_forward_prefix="t.2.mlp.", mixer_norm_prefix="t.2.na.", feed_forward_norm_prefix="t.2.nf.")
+    spec = ModelSpec(architecture="ToyArrangedForCausalLM", vocab_size=V, hidden_size=H, layers=(sandwich, two, pre),
+                     schedule=default_schedule(3), final_norm=norm, final_norm_prefix="t.norm.", embedding_name="t.embed.weight",
+                     head_name="t.head.weight", tie_embeddings=False, head_optional=False, max_positions=256,
+                     embedding_multiplier=3.0, logit_scale=0.5, init_std=0.1)
+    weights = dict(random_tensors(spec, seed=3, dtype=torch.float32))
+    assert {"t.0.n4.weight", "t.1.mem.mix.weight", "t.1.attn.q_proj.weight", "t.2.na.weight"} <= set(weights)
+
+    def runner(sp, w):
+        return ModelRunner(sp, WeightStore.from_tensors(w), dtype=dtype, capacity_tokens=256, max_batch_tokens=128,
+                           max_requests=4)
+
+    r = runner(spec, weights)
+    # the three attention mixers share one group of pages, the running mean has its slot: ids name (layer, sub-id)
+    assert [(g.need.kind, g.layers) for g in r.cache.groups] == [("full", [0, (1, "attention"), 2]), ("state", [(1, "memory")])]
+    rng = np.random.default_rng(5)
+    a, b = rng.integers(0, V, size=66).tolist(), rng.integers(0, V, size=29).tolist()
+    r.admit("a"), r.reserve("a", 66)
+    whole = r.step([StepEntry("a", a, tuple(range(66)))]).float().cpu().clone()
+    r.release("a")
+    r.admit("b"), r.admit("a")
+    got, at, bt = [], 0, 0
+    for n, m in ((10, 6), (1, 1), (33, 12), (2, 1), (20, 9)):
+        r.reserve("a", n), r.reserve("b", m)
+        got.append(r.step([StepEntry("b", b[bt:bt + m], ()), StepEntry("a", a[at:at + n], tuple(range(n)))]).float().cpu().clone())
+        at, bt = at + n, bt + m
+    tol = 2e-5 if dtype == "float32" else 2.5e-2
+    assert rel(torch.cat(got), whole) < tol
+    assert r.cache.check() == "" and not torch.isnan(whole).any() and whole.abs().max() > 0
+    r.check_device()
+    if dtype == "float32":
+        # logit_scale: the logits halve; embedding_multiplier: the same as a table three times as large
+        one = runner(replace(spec, logit_scale=1.0), weights)
+        one.admit("a"), one.reserve("a", 66)
+        assert rel(0.5 * one.step([StepEntry("a", a, tuple(range(66)))]).float().cpu(), whole) < 1e-6
+        w3 = dict(weights)
+        w3["t.embed.weight"] = weights["t.embed.weight"] * 3.0
+        tab = runner(replace(spec, embedding_multiplier=1.0), w3)
+        tab.admit("a"), tab.reserve("a", 66)
+        assert rel(tab.step([StepEntry("a", a, tuple(range(66)))]).float().cpu(), whole) < 1e-6
+
+
+def test_attention_refuses_a_group_the_kernels_do_not_take():
+    """More query heads per key head than the general kernel's tile holds: refused when the part is built, with
+    the limit the library itself reports."""
+    from ember_b200 import ops
+    from ember_b200.config import AttentionSpec, ConfigError
+    from ember_b200.parts import build_part
+    assert ops.attention_tile_queries(ops.ATTENTION_MAX_GROUP) >= 1
+    with pytest.raises(ops.KernelError):
+        ops.attention_tile_queries(ops.ATTENTION_MAX_GROUP + 1)
+    build_part("mixer", AttentionSpec(hidden_size=64, num_heads=32, num_kv_heads=1, head_dim=16))
+    with pytest.raises(ConfigError, match="at most 32"):
+        build_part("mixer", AttentionSpec(hidden_size=64, num_heads=66, num_kv_heads=2, head_dim=16))
