@@ -71,7 +71,9 @@ class ModelRunner:
         self.steps = 0
         # decode steps (one token per run) are captured into CUDA graphs, one per (runs, wanted rows,
         # context bucket); the reference does the same for its decode steps (src/backend/cuda/cuda_backend.cu:376-454)
-        self.cuda_graphs = bool(cuda_graphs)
+        # (only if every part of the model launches nothing but kernels that read their indices on the device:
+        # a part that reads a step's host views would have one step's values baked into the graph)
+        self.cuda_graphs = bool(cuda_graphs) and self.model.graph_safe
         self.graph_context_bucket = 512
         self.graph_max_runs = 256
         self._graphs = {}

@@ -64,6 +64,12 @@ class CausalLM:
         store.finish()
         return self
 
+    @property
+    def graph_safe(self) -> bool:
+        """Whether decode steps may be captured into CUDA graphs: every part of every block must allow it."""
+        return (all(getattr(b, "graph_safe", False) for b in self.blocks) and self.final_norm.graph_safe
+                and self.embedding_position.graph_safe)
+
     # -------------------------------------------------------------------- cache
     @staticmethod
     def cache_id(layer: int, sub: str):

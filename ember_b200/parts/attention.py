@@ -23,6 +23,8 @@ from .registry import build_part, register_part
 
 
 class Attention(Mixer):
+    graph_safe = True
+
     # keys per split and the most tokens in a step for which long key ranges are split
     SPLIT_KEYS = 256
     SPLIT_MAX_TOKENS = 256

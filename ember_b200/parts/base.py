@@ -17,7 +17,9 @@ Interfaces (what a new part must provide):
 * ``FeedForward``:   ``forward(ctx, x[T, hidden], residual_f32[T, hidden])``; it adds its result.
 
 No part knows which model it is in: sizes and constants come from its spec, weights from the
-names under the prefix it is given.
+names under the prefix it is given.  A part whose ``forward`` only launches kernels that read the step's
+indices on the device sets ``graph_safe = True``; decode steps of a model are captured into CUDA graphs only if
+every part of it says so.
 """
 from __future__ import annotations
 
@@ -77,6 +79,12 @@ class Runtime:
 
 class Part:
     family = ""
+    # Whether ``forward`` may be captured into a CUDA graph and replayed for later steps: true only if it does
+    # nothing but launch work on ``ctx.stream`` whose indices (positions, slots, block tables, run offsets) are
+    # read on the device from the step's uploaded arrays.  A part that reads the step's host views
+    # (``ctx.query_start_host``, ``ctx.state_slots_host``, ...) or synchronises bakes one step's values into the
+    # graph, so the default is False and a model with such a part decodes without graphs.
+    graph_safe = False
 
     def __init__(self, spec: PartSpec, prefix: str = ""):
         self.spec = spec

@@ -47,6 +47,12 @@ class Arrangement:
         mixer_roles = [r for r, f in self.ROLES.items() if f == "mixer" and r in self.parts]
         self.mixers: Dict[str, object] = {("" if len(mixer_roles) == 1 else r): self.parts[r] for r in mixer_roles}
 
+    @property
+    def graph_safe(self) -> bool:
+        """Whether a decode step through this block may be captured into a CUDA graph: every part must allow it
+        (an arrangement whose own ``forward`` reads host views overrides this with False)."""
+        return all(getattr(p, "graph_safe", False) for p in self.parts.values())
+
     def weight_decls(self) -> List[WeightDecl]:
         return [d for p in self.parts.values() for d in p.weight_decls()]
 

@@ -19,6 +19,8 @@ from .registry import register_part
 
 
 class GatedMLP(FeedForward):
+    graph_safe = True
+
     def __init__(self, spec, prefix: str = ""):
         super().__init__(spec, prefix)
         if spec.activation != "silu":

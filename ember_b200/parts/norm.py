@@ -15,6 +15,8 @@ from .registry import register_part
 
 
 class RMSNorm(Norm):
+    graph_safe = True
+
     def weight_decls(self) -> List[WeightDecl]:
         return [WeightDecl(self.prefix + "weight", (self.spec.size,), init="norm")]
 

@@ -18,6 +18,8 @@ from .registry import register_part
 
 
 class RotaryEmbedding(PositionEncoding):
+    graph_safe = True
+
     def __init__(self, spec, prefix: str = ""):
         super().__init__(spec, prefix)
         if spec.rotary_dim <= 0 or spec.rotary_dim % 2 or spec.rotary_dim > spec.head_dim:
@@ -40,7 +42,7 @@ class RotaryEmbedding(PositionEncoding):
 
 
 class NoPosition(PositionEncoding):
-    pass
+    graph_safe = True
 
 
 register_part("position", "rope", RotaryEmbedding)

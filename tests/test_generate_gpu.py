@@ -171,6 +171,9 @@ def test_state_slots_under_the_engine_with_preemption():
     for capacity in (96, 2048):
         runner = ModelRunner(spec, WeightStore.from_tensors(weights), dtype="float32", capacity_tokens=capacity,
                              max_batch_tokens=128, max_requests=4, page_tokens=16)
+        # the toy mixer reads the step's host views (slots, run offsets): it does not declare itself graph-safe,
+        # so the runner must not capture decode steps (a replayed graph would keep the slots of the captured step)
+        assert not runner.cuda_graphs
         eng = Engine(runner, max_prefill_chunk=24)
         results[capacity] = eng.generate(prompts, max_tokens=30, ignore_eos=True)
         runner.check_device()
