@@ -52,33 +52,35 @@ class LLM:
 
 def load(model: str, dtype: str = "bfloat16", device: str = "cuda:0", kv_cache_tokens: int = 0,
          max_batch_tokens: int = 2048, max_seqs: int = 64, prefill_chunk: int = 2048,
-         max_context: Optional[int] = None, page_tokens: int = 64, cuda_graphs: bool = True) -> LLM:
-    """Loads a model folder (config.json + safetensors).  ``kv_cache_tokens`` 0 sizes the cache
-    for ``max_seqs`` requests of the model's position limit, capped at 262,144 tokens."""
+         max_context: Optional[int] = None, page_tokens: int = 64, cuda_graphs: bool = True,
+         gpu_memory: float = 0.92, kv_cache_mib: int = 0, strict_weights: bool = False) -> LLM:
+    """Loads a model folder (config.json + safetensors).  The cache holds ``kv_cache_tokens`` tokens if given,
+    else ``kv_cache_mib`` MiB if given, else what fits once the weights are on the device when ``gpu_memory`` of
+    the device's memory may be used (the reference's --gpu-memory / --kv-cache-mib / --kv-cache-tokens,
+    tools/cli_args.hpp:57-88; src/backend/cuda/cuda_backend.cu:757-780), and never more than ``max_seqs`` requests
+    of ``max_context`` tokens could fill."""
     cfg = load_config(model)
     spec = cfg.to_model_spec()
-    if kv_cache_tokens <= 0:
-        kv_cache_tokens = min(max_seqs * spec.max_positions, 262144)
-    runner = ModelRunner(spec, WeightStore.from_dir(model), dtype=dtype, device=device,
+    runner = ModelRunner(spec, WeightStore.from_dir(model, strict=strict_weights), dtype=dtype, device=device,
                          capacity_tokens=kv_cache_tokens, max_batch_tokens=max_batch_tokens,
-                         max_requests=max_seqs, page_tokens=page_tokens, cuda_graphs=cuda_graphs)
+                         max_requests=max_seqs, page_tokens=page_tokens, cuda_graphs=cuda_graphs,
+                         memory_fraction=gpu_memory, cache_bytes=int(kv_cache_mib) << 20, max_context=max_context)
     return LLM(runner, max_prefill_chunk=prefill_chunk, max_context=max_context)
 
 
 def load_random(config, seed: int = 0, dtype: str = "bfloat16", device: str = "cuda:0", kv_cache_tokens: int = 0,
                 max_batch_tokens: int = 2048, max_seqs: int = 64, prefill_chunk: int = 2048,
                 max_context: Optional[int] = None, page_tokens: int = 64, cuda_graphs: bool = True,
-                weight_dtype=torch.bfloat16,
-                std: Optional[float] = None, norm_std: Optional[float] = None) -> LLM:
+                weight_dtype=torch.bfloat16, std: Optional[float] = None, norm_std: Optional[float] = None,
+                gpu_memory: float = 0.92, kv_cache_mib: int = 0) -> LLM:
     """Random-weights mode without a folder: the tensors are made from ``seed`` in memory
     (on the device when it is a CUDA device) and loaded as if they came from a file."""
     spec = config.to_model_spec()
     gen_device = device if torch.cuda.is_available() else "cpu"
     store = WeightStore.from_tensors(dict(random_tensors(spec, seed, weight_dtype, std, norm_std, device=gen_device)),
                                      description=f"random weights (seed {seed})")
-    if kv_cache_tokens <= 0:
-        kv_cache_tokens = min(max_seqs * spec.max_positions, 262144)
     runner = ModelRunner(spec, store, dtype=dtype, device=device, capacity_tokens=kv_cache_tokens,
                          max_batch_tokens=max_batch_tokens, max_requests=max_seqs, page_tokens=page_tokens,
-                         cuda_graphs=cuda_graphs)
+                         cuda_graphs=cuda_graphs, memory_fraction=gpu_memory, cache_bytes=int(kv_cache_mib) << 20,
+                         max_context=max_context)
     return LLM(runner, max_prefill_chunk=prefill_chunk, max_context=max_context)

@@ -25,6 +25,26 @@ class LayerCache:
     state: Optional[torch.Tensor] = None    # [slots, *state_shape]
 
 
+def cache_bytes_per_token(needs, dtype: torch.dtype) -> int:
+    """Bytes of device memory one cached token takes over all paged groups (every group's pool is made for the
+    same number of tokens): keys and values of every layer of the group.  ``needs`` is what
+    ``CausalLM.cache_needs`` returns."""
+    elem = torch.empty(0, dtype=dtype).element_size()
+    return sum(2 * n.num_kv_heads * n.head_dim * elem for n in needs.values() if n is not None and n.kind in ("full", "window"))
+
+
+def state_bytes_per_request(needs) -> int:
+    """Bytes of fixed-size state one request's slot takes over all state groups."""
+    total = 0
+    for n in needs.values():
+        if n is not None and n.kind == "state":
+            size = torch.empty(0, dtype=getattr(torch, n.state_dtype)).element_size()
+            for d in n.state_shape:
+                size *= int(d)
+            total += size
+    return total
+
+
 class CacheStorage:
     def __init__(self, manager: CacheManager, device: torch.device, dtype: torch.dtype):
         self.manager = manager

@@ -9,9 +9,10 @@
 The engine starts at token ids (there is no tokenizer here): ``-p`` takes ids separated by
 spaces or commas, ``--ids-file`` a file of them.  Options keep the reference's names where it
 has them: ``-m/--model``, ``--max-batch-tokens`` (2048), ``--max-seqs`` (64), ``--prefill-chunk``
-(2048 here, 512 there), ``--kv-cache-tokens``, ``-n/--max-tokens`` (512), ``--temp`` (0.7), ``--top-p`` (0.8),
+(2048 here, 512 there), ``--gpu-memory`` (0.92), ``--kv-cache-mib``, ``--kv-cache-tokens``, ``-n/--max-tokens`` (512), ``--temp`` (0.7), ``--top-p`` (0.8),
 ``--top-k`` (20), ``--min-p`` (0), ``--seed``, ``--greedy``, ``--no-cuda-graphs``, ``-v``.  ``--dtype`` (bfloat16 or
-float32) stands where the reference has ``--weights``.
+float32) stands where the reference has ``--weights``; ``--page-tokens`` (64; the reference's block is 16) and
+``--max-context`` are the Python entry point's options of the same names.
 """
 from __future__ import annotations
 
@@ -35,7 +36,13 @@ def _parser() -> argparse.ArgumentParser:
     ap.add_argument("--max-seqs", type=int, default=64)
     ap.add_argument("--prefill-chunk", type=int, default=2048,
                     help="most prompt tokens of one request in a step (the reference defaults to 512 for a 6 GB GPU; a B200's tensor cores want 2,048)")
-    ap.add_argument("--kv-cache-tokens", type=int, default=0)
+    ap.add_argument("--gpu-memory", type=float, default=0.92,
+                    help="share of the device's memory to use (weights + cache + buffers); sizes the cache unless one of the next two is given")
+    ap.add_argument("--kv-cache-mib", type=int, default=0, help="cache size in MiB")
+    ap.add_argument("--kv-cache-tokens", type=int, default=0, help="cache size in tokens (wins over the other two)")
+    ap.add_argument("--page-tokens", type=int, default=64, help="tokens per cache page (16, 32 or 64 for the tensor-core attention)")
+    ap.add_argument("--max-context", type=int, default=0, help="most tokens a request may reach (0: the model's position limit)")
+    ap.add_argument("--strict-weights", action="store_true", help="a tensor in the folder that the model does not use is an error")
     ap.add_argument("-n", "--max-tokens", type=int, default=512)
     ap.add_argument("--temp", "--temperature", dest="temp", type=float, default=0.7)
     ap.add_argument("--top-p", type=float, default=0.8)
@@ -65,9 +72,16 @@ def _load(args):
         raise SystemExit("error: this engine runs on a CUDA device only (--device cuda)")
     if not args.model:
         raise SystemExit("error: give a model folder with -m DIR")
-    return ember_b200.load(args.model, dtype=args.dtype, kv_cache_tokens=args.kv_cache_tokens,
-                           max_batch_tokens=args.max_batch_tokens, max_seqs=args.max_seqs,
-                           prefill_chunk=args.prefill_chunk, cuda_graphs=not args.no_cuda_graphs)
+    llm = ember_b200.load(args.model, dtype=args.dtype, kv_cache_tokens=args.kv_cache_tokens,
+                          max_batch_tokens=args.max_batch_tokens, max_seqs=args.max_seqs,
+                          prefill_chunk=args.prefill_chunk, cuda_graphs=not args.no_cuda_graphs,
+                          gpu_memory=args.gpu_memory, kv_cache_mib=args.kv_cache_mib, page_tokens=args.page_tokens,
+                          max_context=args.max_context or None, strict_weights=args.strict_weights)
+    if args.verbose:
+        r = llm.runner
+        print(f"[cache: {r.cache.capacity_tokens()} tokens in pages of {r.cache.page_tokens}, "
+              f"{r.storage.bytes() / 2**20:.0f} MiB; context limit {llm.engine.scheduler.max_context}]", file=sys.stderr)
+    return llm
 
 
 def _sampling(args):

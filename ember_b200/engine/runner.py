@@ -15,7 +15,7 @@ import torch
 
 from .. import ops
 from ..cache.manager import CacheManager
-from ..cache.storage import CacheStorage
+from ..cache.storage import CacheStorage, cache_bytes_per_token, state_bytes_per_request
 from ..config.registry import load_config
 from ..config.spec import ModelSpec
 from ..model.causal_lm import CausalLM
@@ -45,8 +45,14 @@ class DeviceError(RuntimeError):
 
 class ModelRunner:
     def __init__(self, spec: ModelSpec, store: WeightStore, dtype="bfloat16", device="cuda:0",
-                 capacity_tokens: int = 4096, max_batch_tokens: int = 2048, max_requests: int = 64,
-                 page_tokens: int = 16, cuda_graphs: bool = True):
+                 capacity_tokens: Optional[int] = 4096, max_batch_tokens: int = 2048, max_requests: int = 64,
+                 page_tokens: int = 16, cuda_graphs: bool = True, memory_fraction: float = 0.92, cache_bytes: int = 0,
+                 max_context: Optional[int] = None):
+        """``capacity_tokens``: tokens the cache holds (every paged group gets pages for that many).  None or 0
+        sizes it after the weights are on the device: from ``cache_bytes`` if given, else from the device's free
+        memory so that ``memory_fraction`` of the whole device is in use (weights, cache and buffers), as the
+        reference does (src/backend/cuda/cuda_backend.cu:757-780); never more than ``max_requests`` requests of
+        ``max_context`` tokens (default: the model's position limit) could use."""
         if not torch.cuda.is_available():
             raise DeviceError("no CUDA device: this engine runs its model on a B200 only (there is no CPU path)")
         self.device = torch.device(device)
@@ -57,6 +63,9 @@ class ModelRunner:
         self.max_batch_tokens = int(max_batch_tokens)
         self.max_requests = int(max_requests)
         self.model = CausalLM(spec).load(store, self.rt)
+        if not capacity_tokens or capacity_tokens <= 0:
+            capacity_tokens = self._capacity_from_memory(memory_fraction, cache_bytes, page_tokens,
+                                                         min(max_context or spec.max_positions, spec.max_positions))
         self.cache = CacheManager(self.model.cache_needs(), page_tokens, int(capacity_tokens), self.max_requests)
         self.storage = CacheStorage(self.cache, self.device, self.dtype)
         self.workspace = Workspace(self.device)
@@ -79,6 +88,30 @@ class ModelRunner:
         self._graphs = {}
         self._graph_seen = set()
         self.graph_replays = 0
+
+    def _capacity_from_memory(self, memory_fraction: float, cache_bytes: int, page_tokens: int, max_context: int) -> int:
+        """Tokens of cache that fit: what is free now (the weights are loaded), less the share of the device to
+        be left alone, the state slots, and room for the step's buffers (residual, activations, logits)."""
+        needs = self.model.cache_needs()
+        per_token = cache_bytes_per_token(needs, self.dtype)
+        useful = (self.max_requests * max_context + page_tokens - 1) // page_tokens * page_tokens
+        if per_token == 0:
+            return useful
+        if cache_bytes and cache_bytes > 0:
+            budget = int(cache_bytes)
+        else:
+            if not (0.0 < memory_fraction <= 1.0):
+                raise ValueError(f"memory_fraction must be in (0, 1], got {memory_fraction}")
+            torch.cuda.empty_cache()
+            free, total = torch.cuda.mem_get_info(self.device)
+            buffers = self.max_batch_tokens * self.spec.hidden_size * 64 + self.max_requests * self.spec.vocab_size * 8 \
+                + (512 << 20)
+            budget = free - int((1.0 - memory_fraction) * total) - buffers - self.max_requests * state_bytes_per_request(needs)
+        tokens = max(0, budget) // per_token // page_tokens * page_tokens
+        if tokens < 4 * page_tokens:
+            raise DeviceError(f"not enough device memory left for the cache ({max(0, budget) / 2**20:.0f} MiB; a token "
+                              f"takes {per_token} bytes)")
+        return int(min(tokens, useful))
 
     # -------------------------------------------------------------- constructors
     @classmethod
