@@ -45,7 +45,6 @@ constexpr int FA_K_STAGES = 2;        // key tiles in flight or in use (a key ti
                                       // two tiles before its values are: two stages look as far ahead as three of values)
 constexpr int FA_V_STAGES = 3;        // value tiles (free once O += P V has read them)
 constexpr int FA_THREADS = 192;
-constexpr unsigned FA_WAIT_LIMIT = 1u << 24;
 constexpr float FA_LOG2E = 1.4426950408889634f;
 
 struct FaParams {
@@ -71,32 +70,8 @@ __device__ __forceinline__ void fa_expect_tx(uint64_t* bar, uint32_t bytes) {
 __device__ __forceinline__ void fa_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(fa_s32(bar)) : "memory");
 }
-__device__ __forceinline__ bool fa_try_wait(uint64_t* bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n.reg .pred p;\n"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-        "selp.u32 %0, 1, 0, p;\n}"
-        : "=r"(ok) : "r"(fa_s32(bar)), "r"(parity) : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ bool fa_test_wait(uint64_t* bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n.reg .pred p;\n"
-        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-        "selp.u32 %0, 1, 0, p;\n}"
-        : "=r"(ok) : "r"(fa_s32(bar)), "r"(parity) : "memory");
-    return ok != 0;
-}
 __device__ __forceinline__ bool fa_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-    if (fa_test_wait(bar, parity)) return true;      // a phase that is already over costs one look, not a suspended wait
-    for (unsigned i = 0; i < FA_WAIT_LIMIT; i++) {
-        if (fa_try_wait(bar, parity)) return true;
-        if ((i & 1023u) == 1023u && *abort_flag) return false;
-    }
-    *abort_flag = 1;
-    return false;
+    return mbarrier_wait_bounded(fa_s32(bar), parity, abort_flag);      // bounded by time (common.cuh)
 }
 __device__ __forceinline__ void fa_tma_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
     asm volatile(

@@ -35,7 +35,6 @@ namespace ember {
 constexpr int KT = 64;                 // keys per shared-memory tile
 constexpr int ATC_CONSUMERS = 128;     // four warps multiply
 constexpr int ATC_THREADS = 160;       // + one warp that only fetches pages
-constexpr unsigned ATC_WAIT_LIMIT = 1u << 24;
 constexpr float LOG2E = 1.4426950408889634f;
 
 struct AttnTcParams {
@@ -83,32 +82,8 @@ __device__ __forceinline__ void atc_expect_tx(uint64_t* bar, uint32_t bytes) {
 __device__ __forceinline__ void atc_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(s32(bar)) : "memory");
 }
-__device__ __forceinline__ bool atc_try_wait(uint64_t* bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n.reg .pred p;\n"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-        "selp.u32 %0, 1, 0, p;\n}"
-        : "=r"(ok) : "r"(s32(bar)), "r"(parity) : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ bool atc_test_wait(uint64_t* bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n.reg .pred p;\n"
-        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-        "selp.u32 %0, 1, 0, p;\n}"
-        : "=r"(ok) : "r"(s32(bar)), "r"(parity) : "memory");
-    return ok != 0;
-}
 __device__ __forceinline__ bool atc_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-    if (atc_test_wait(bar, parity)) return true;      // a phase that is over costs one look, not a suspended wait
-    for (unsigned i = 0; i < ATC_WAIT_LIMIT; i++) {
-        if (atc_try_wait(bar, parity)) return true;
-        if ((i & 1023u) == 1023u && *abort_flag) return false;
-    }
-    *abort_flag = 1;
-    return false;
+    return mbarrier_wait_bounded(s32(bar), parity, abort_flag);      // bounded by time (common.cuh)
 }
 __device__ __forceinline__ void atc_tma_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
     asm volatile(

@@ -81,6 +81,56 @@ inline cudaError_t launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block
     return cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);
 }
 
+// ---- bounded waits on shared-memory barriers ------------------------------------------------------------------
+// No kernel here waits without a limit.  A wait gives up after EMBER_WAIT_LIMIT_NS of the device's global timer
+// (two seconds: far beyond any step, short enough that nobody takes the device for hung), raises the block's
+// abort flag so that every role of the block falls through to the common exit (which frees tensor memory and
+// records EMBER_ERR_WAIT_LIMIT in the device error word), and returns false.  The limit is time, not a number of
+// polls: a suspended try_wait takes an implementation-defined while, so a poll count bounds nothing in seconds.
+constexpr unsigned long long EMBER_WAIT_LIMIT_NS = 2000000000ull;
+
+__device__ __forceinline__ unsigned long long global_timer_ns() {
+    unsigned long long t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+__device__ __forceinline__ bool mbarrier_try_wait_parity(uint32_t bar_shared, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n}"
+        : "=r"(ok) : "r"(bar_shared), "r"(parity) : "memory");
+    return ok != 0;
+}
+__device__ __forceinline__ bool mbarrier_test_wait_parity(uint32_t bar_shared, uint32_t parity) {
+    uint32_t ok;
+    asm volatile(
+        "{\n.reg .pred p;\n"
+        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n}"
+        : "=r"(ok) : "r"(bar_shared), "r"(parity) : "memory");
+    return ok != 0;
+}
+// A phase that is already over is seen by one plain look (about 100 cycles; the suspending form costs about 240
+// even then).  While waiting, the abort flag and the timer are looked at every 64 polls.
+__device__ __forceinline__ bool mbarrier_wait_bounded(uint32_t bar_shared, uint32_t parity, volatile int* abort_flag,
+                                                      unsigned long long limit_ns = EMBER_WAIT_LIMIT_NS) {
+    if (mbarrier_test_wait_parity(bar_shared, parity)) return true;
+    unsigned long long start = 0;
+    for (unsigned i = 0;; i++) {
+        if (mbarrier_try_wait_parity(bar_shared, parity)) return true;
+        if ((i & 63u) == 63u) {
+            if (*abort_flag) return false;
+            const unsigned long long now = global_timer_ns();
+            if (start == 0) start = now;
+            else if (now - start > limit_ns) break;
+        }
+    }
+    *abort_flag = 1;
+    return false;
+}
+
 __device__ __forceinline__ float to_float(float x) { return x; }
 __device__ __forceinline__ float to_float(__nv_bfloat16 x) { return __bfloat162float(x); }
 

@@ -372,9 +372,36 @@ __global__ void silu_mul_interleaved_kernel(const T* __restrict__ x, T* __restri
     out[i] = from_float<T>(g / (1.0f + expf(-g)) * u);
 }
 
+// ------------------------------------------------------------------------- the bounded wait, run out on purpose
+// One thread waits, with the helper every TMA/tcgen05 kernel here uses, on a barrier that nothing ever arrives
+// at.  The wait has to give up after `limit_ns`, the kernel has to return, and the error word has to hold
+// EMBER_ERR_WAIT_LIMIT: what a test checks without any kernel hanging or faulting.
+__global__ void wait_limit_probe_kernel(unsigned long long limit_ns, int* __restrict__ err,
+                                        unsigned long long* __restrict__ waited_ns) {
+    __shared__ uint64_t bar;
+    __shared__ int abort_flag;
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"((uint32_t)__cvta_generic_to_shared(&bar)), "r"(1) : "memory");
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        const unsigned long long t0 = global_timer_ns();
+        const bool ok = mbarrier_wait_bounded((uint32_t)__cvta_generic_to_shared(&bar), 0, &abort_flag, limit_ns);
+        if (waited_ns) *waited_ns = global_timer_ns() - t0;
+        if (!ok && abort_flag && err) atomicOr(err, EMBER_ERR_WAIT_LIMIT);
+    }
+}
+
 }  // namespace ember
 
 using namespace ember;
+
+EMBER_API int ember_wait_limit_probe(unsigned long long limit_ns, int* err, unsigned long long* waited_ns, void* stream) {
+    if (limit_ns == 0 || limit_ns > 100000000ull) return fail("wait_limit_probe: the limit must be between 1 ns and 100 ms");
+    wait_limit_probe_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(limit_ns, err, waited_ns);
+    return check_launch("wait_limit_probe");
+}
 
 EMBER_API int ember_embed(const int* tokens, const int* prev_ids, int n_prev, const void* table, int table_dtype,
                           float* out, int T, int H, int V, float scale, int* err, void* stream) {

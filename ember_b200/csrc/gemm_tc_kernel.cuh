@@ -15,7 +15,6 @@ constexpr int TILE_K = 64;         // bf16 elements per stage along K = one 128-
 constexpr int UMMA_K = 16;
 constexpr int GEMM_THREADS = 192;
 constexpr int MAX_STAGES = 8;
-constexpr unsigned WAIT_LIMIT = 1u << 24;
 
 // Epilogue 4: the output columns are head slots of 128 (query heads, then key heads, then value heads); instead of
 // being stored as they are, a token's query and key heads get their RMSNorm and rotation and go to the query
@@ -72,39 +71,9 @@ __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
 __device__ __forceinline__ void mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(smem_u32(bar)), "r"(bytes) : "memory");
 }
-__device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n.reg .pred p;\n"
-        "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-        "selp.u32 %0, 1, 0, p;\n}"
-        : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-__device__ __forceinline__ bool mbar_test_wait(uint64_t* bar, uint32_t parity) {
-    uint32_t ok;
-    asm volatile(
-        "{\n.reg .pred p;\n"
-        "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-        "selp.u32 %0, 1, 0, p;\n}"
-        : "=r"(ok)
-        : "r"(smem_u32(bar)), "r"(parity)
-        : "memory");
-    return ok != 0;
-}
-// Bounded wait; returns false (and raises the abort flag) if the limit is reached.  A phase that is already
-// over is seen by one plain look (about 100 cycles); the suspending form costs about 240 even then, and the
-// single issuing thread of a tile pays it once per k-block.
+// Bounded wait (common.cuh): returns false, with the abort flag raised, once the time limit is reached.
 __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
-    if (mbar_test_wait(bar, parity)) return true;
-    for (unsigned i = 0; i < WAIT_LIMIT; i++) {
-        if (mbar_try_wait(bar, parity)) return true;
-        if ((i & 1023u) == 1023u && *abort_flag) return false;
-    }
-    *abort_flag = 1;
-    return false;
+    return mbarrier_wait_bounded(smem_u32(bar), parity, abort_flag);
 }
 __device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, uint64_t* bar, int x, int y) {
     asm volatile(

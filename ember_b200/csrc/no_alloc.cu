@@ -68,7 +68,11 @@ EMBER_API int ember_gemm_tc_noalloc(const void* A, const void* W, void* out, int
     if ((long long)M * N > (long long)EMBER_NOALLOC_SCRATCH_FLOATS)
         return fail("gemm_tc_noalloc: M*N = %lld exceeds the built-in scratch of %d floats", (long long)M * N,
                     EMBER_NOALLOC_SCRATCH_FLOATS);
+    if (A == nullptr || W == nullptr || out == nullptr) return fail("gemm_tc_noalloc: A, W and out must not be null");
     if ((((uintptr_t)A) & 15) || (((uintptr_t)W) & 15)) return fail("gemm_tc_noalloc: operands must be 16-byte aligned");
+    const int out_width = epilogue == 3 ? N / 2 : N;
+    if (ldc < out_width)
+        return fail("gemm_tc_noalloc: ldc=%d is shorter than the %d values a row of the output holds", ldc, out_width);
     float* scratch = nullptr;
     if (int rc = scratch_pointer(&scratch)) return rc;
     cudaStream_t st = (cudaStream_t)stream;

@@ -13,7 +13,9 @@
  * What it computes: out = epilogue(A[M,K] . W[N,K]^T) with bf16 operands and fp32 accumulation,
  * for the small-M ("decode") orientation of the tcgen05 kernel, M <= 128.  Epilogues: 0 store
  * bf16, 1 store fp32, 2 add into fp32 `out`, 3 silu(gate) * up over interleaved rows -> bf16.
- * `ldc` is the row stride of `out` in elements.  Inputs and outputs are the caller's.
+ * `ldc` is the row stride of `out` in elements (at least N, or N / 2 for epilogue 3; a shorter one
+ * is refused, as are null pointers).  Inputs and outputs are the caller's; `err` may be null or
+ * point to one device int that collects error bits.
  *
  * Limits: M <= 128, K a multiple of 8, and M * N <= EMBER_NOALLOC_SCRATCH_FLOATS (1,048,576
  * floats = 4 MiB of fp32 scratch).  Larger sizes are refused with an error; nothing is truncated.

@@ -88,6 +88,8 @@ class ModelRunner:
         self._graphs = {}
         self._graph_seen = set()
         self.graph_replays = 0
+        self._capture_row: Optional[int] = None
+        self._captured: Optional[torch.Tensor] = None
 
     def _capacity_from_memory(self, memory_fraction: float, cache_bytes: int, page_tokens: int, max_context: int) -> int:
         """Tokens of cache that fit: what is free now (the weights are loaded), less the share of the device to
@@ -138,12 +140,30 @@ class ModelRunner:
     def cached_tokens(self, request: Hashable) -> int:
         return self.cache.get(request).tokens
 
+    # ----------------------------------------------------------------- debugging
+    def set_capture_hidden(self, on: bool, row: int = -1) -> None:
+        """Debugging aid (the reference's Backend::set_capture_hidden, src/backend/backend.hpp:119-122): while on,
+        every step records the residual stream of one of its tokens (``row`` among the step's tokens; -1 = the
+        last) after the embedding and after every run of the layer schedule, so that a drift against another
+        implementation can be traced to the layer where it starts.  Such steps run without CUDA graphs."""
+        self._capture_row = int(row) if on else None
+        if on and self._captured is None:
+            self._captured = torch.zeros(len(self.spec.schedule) + 1, self.spec.hidden_size, dtype=torch.float32,
+                                         device=self.device)
+
+    def captured_hidden(self) -> torch.Tensor:
+        """[runs of the schedule + 1, hidden] float32 on the host: the residual of the captured token of the last
+        step after the embedding (row 0) and after each layer run."""
+        if self._captured is None:
+            raise RuntimeError("nothing was captured: call set_capture_hidden(True) before the step")
+        return self._captured.cpu()
+
     # ---------------------------------------------------------------------- step
     def step(self, entries: Sequence[StepEntry], n_prev: int = 0) -> Optional[torch.Tensor]:
         """Runs the entries as one batch; returns logits [wanted rows, vocab] fp32 on the device
         (a view of a scratch buffer, valid until the next step), or None if nothing is wanted.
         With ``n_prev`` > 0 a token -(r + 1), r < n_prev, is read on the device from ``sampled_ids[r]``."""
-        graphable = self.cuda_graphs and 0 < len(entries) <= self.graph_max_runs and \
+        graphable = self.cuda_graphs and self._capture_row is None and 0 < len(entries) <= self.graph_max_runs and \
             all(len(e.tokens) == 1 for e in entries)
         min_widths, ctx_bucket = None, None
         if graphable:
@@ -175,6 +195,8 @@ class ModelRunner:
         else:
             ctx = StepContext(batch, self.workspace, self.device, self.max_batch_tokens, err=self.err,
                               tile_sizes=self.model.tile_requests(), prev_ids=self.sampled_ids)
+            if self._capture_row is not None:
+                ctx.capture_hidden = (self._capture_row, self._captured)
             logits = self.model.forward(ctx, self.storage)
         lens = batch.context_len.tolist()
         for s, req in enumerate(batch.requests):

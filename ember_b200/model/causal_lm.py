@@ -101,11 +101,17 @@ class CausalLM:
         ops.embed(ctx.tokens, self.embedding, h, err=ctx.err, stream=ctx.stream, prev_ids=ctx.prev_ids,
                   scale=s.embedding_multiplier)
         self.embedding_position.on_embedding(ctx, h)          # nothing for rotary or absent encodings
-        for e in s.schedule:
+        capture = getattr(ctx, "capture_hidden", None)        # (row, buffer [runs of the schedule + 1, hidden]) or None
+        if capture is not None:
+            row = capture[0] if capture[0] >= 0 else ctx.T + capture[0]
+            capture[1][0].copy_(h[row])
+        for i, e in enumerate(s.schedule):
             owner = e.cache_of if e.cache_of >= 0 else e.layer
             block = self.blocks[e.layer]
             caches = {sub: storage.layer(self.cache_id(owner, sub)) for sub in block.mixers}
             block.forward(ctx, h, caches, owns_cache=(owner == e.layer))
+            if capture is not None:
+                capture[1][i + 1].copy_(h[row])
         if ctx.R == 0:
             return None
         xn = ctx.buf_dyn("model.final_normed", ctx.R * s.hidden_size, rt.dtype).view(-1, s.hidden_size)

@@ -149,6 +149,17 @@ def qk_norm_rope_store(qkv: torch.Tensor, T: int, n_heads: int, n_kv: int, head_
           c_int(1 if write_kv else 0), _p(err), c_void_p(stream if stream is not None else current_stream_ptr()))
 
 
+def wait_limit_probe(limit_ns: int, err: torch.Tensor, waited_ns: torch.Tensor, stream: Optional[int] = None) -> None:
+    """Runs the kernels' bounded barrier wait on a barrier nobody arrives at, with a limit of ``limit_ns`` (at most
+    100 ms): the wait gives up, the kernel returns, ``err`` gets the wait-limit bit and ``waited_ns`` (int64[1])
+    how long the wait lasted.  For tests of the error path; nothing hangs."""
+    _check(err, "err", torch.int32)
+    _check(waited_ns, "waited_ns", torch.int64)
+    lib = _lib("elementwise")
+    _call(lib, lib.ember_wait_limit_probe, ctypes.c_ulonglong(int(limit_ns)), _p(err), _p(waited_ns),
+          c_void_p(stream if stream is not None else current_stream_ptr()))
+
+
 def silu_mul_interleaved(x: torch.Tensor, out: torch.Tensor, n_out: int, stream: Optional[int] = None) -> None:
     _check(x, "x")
     _check(out, "out", x.dtype)

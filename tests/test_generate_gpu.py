@@ -240,3 +240,34 @@ def test_pipelined_engine_equals_synchronous_engine(dtype, tiny_model_dirs):
                 assert s == (f[:f.index(stop)] if stop in f else f)
         assert results[True] == results[False]
     llm.runner.check_device()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_captured_residuals_follow_the_plain_layers(dtype, tiny_model_dirs):
+    """The residual of a step's last token after the embedding and after every layer (the debugging aid of the
+    reference's backend, src/backend/backend.hpp:119-122) against the plain implementation's hidden states:
+    a prompt portion, then a single token (which would otherwise go through a graph)."""
+    from ember_b200 import StepEntry
+    name = "b"
+    plain = PlainQwen3(tiny_model_dirs[name], torch.float64)
+    toks = np.random.default_rng(3).integers(0, 1000, size=41).tolist()
+    want = plain.hidden_states(toks)                        # [layers + 1] of [T, hidden]
+    llm = load(tiny_model_dirs, name, dtype)
+    r = llm.runner
+    with pytest.raises(RuntimeError):
+        r.captured_hidden()
+    r.set_capture_hidden(True)
+    r.admit("x"), r.reserve("x", 40)
+    r.step([StepEntry("x", toks[:40], (39,))])
+    got = r.captured_hidden()
+    assert got.shape == (len(want), want[0].shape[1])
+    tol = 2e-5 if dtype == "float32" else 2.5e-2
+    for l, h in enumerate(want):
+        assert float((got[l].double() - h[39]).norm() / h[39].norm()) < tol, l
+    r.reserve("x", 1)
+    r.step([StepEntry("x", toks[40:], (0,))])
+    got = r.captured_hidden()
+    for l, h in enumerate(want):
+        assert float((got[l].double() - h[40]).norm() / h[40].norm()) < tol, l
+    r.set_capture_hidden(False)
+    assert r.graph_replays == 0

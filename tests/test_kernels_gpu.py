@@ -508,3 +508,25 @@ def test_gemm_tc_qkv(heads, kv, page, M, norm, rotate):
     err = torch.zeros(1, dtype=torch.int32, device=dev)
     ops.gemm_tc_qkv(a, w, M, heads, kv, qw, kw, 1e-5, cs, fr, pos, seq, bad, page, kp, vp, q, err=err)
     assert int(err.item()) == 2
+
+
+def test_bounded_wait_runs_out_and_returns():
+    """The wait every TMA / tcgen05 kernel uses, on a barrier nobody arrives at, with a limit of one millisecond:
+    the kernel returns, the error word holds the wait-limit bit, the wait lasted about the limit (not a poll
+    count's worth of unknown time), the runner turns the word into a DeviceError, and the device works afterwards."""
+    from ember_b200 import ops
+    from ember_b200.engine.runner import ModelRunner
+    dev = "cuda"
+    err = torch.zeros(1, dtype=torch.int32, device=dev)
+    waited = torch.zeros(1, dtype=torch.int64, device=dev)
+    ops.wait_limit_probe(1_000_000, err, waited)
+    torch.cuda.synchronize()
+    assert int(err.item()) == 4                                   # EMBER_ERR_WAIT_LIMIT
+    assert 1_000_000 <= int(waited.item()) < 50_000_000
+    assert "a bounded wait ran out" in ModelRunner.describe_error(int(err.item()))
+    with pytest.raises(ops.KernelError):
+        ops.wait_limit_probe(10_000_000_000, err, waited)          # a limit a test should not ask for
+    x = torch.randn(4, 64, device=dev)
+    out = torch.empty(4, 64, device=dev)
+    ops.rmsnorm(x, torch.ones(64, device=dev), 1e-6, out, 4)
+    assert torch.isfinite(out).all()

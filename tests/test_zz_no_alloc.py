@@ -83,3 +83,14 @@ def test_noalloc_refuses_what_does_not_fit():
     big = torch.zeros(200, 64, device="cuda", dtype=torch.bfloat16)
     rc, msg = call_noalloc(lib, big, w[:64].contiguous(), out, 200, 0, err)
     assert rc != 0 and "up to 128 rows" in msg
+    # a row stride shorter than the output's width would write past the caller's rows: refused, like a null output
+    from ctypes import c_int, c_void_p
+    small_w = w[:256].contiguous()
+    narrow = torch.zeros(8, 128, device="cuda", dtype=torch.bfloat16)
+    fn = lib.ember_gemm_tc_noalloc
+    rc = fn(c_void_p(a.data_ptr()), c_void_p(small_w.data_ptr()), c_void_p(narrow.data_ptr()), c_int(128), c_int(8),
+            c_int(256), c_int(64), c_int(0), c_void_p(err.data_ptr()), c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert rc != 0 and "shorter than" in lib.ember_last_error().decode()
+    rc = fn(c_void_p(a.data_ptr()), c_void_p(small_w.data_ptr()), c_void_p(0), c_int(256), c_int(8), c_int(256), c_int(64),
+            c_int(0), c_void_p(err.data_ptr()), c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert rc != 0 and "must not be null" in lib.ember_last_error().decode()
