@@ -5,12 +5,19 @@
 
 Prints ONE JSON line.  ``value`` is decoded tokens a second at the default batch (8), timed on
 the device with CUDA events around K decode steps of the step function plus the sampler (the
-weights alone, 3.4 GB, exceed the 126 MB L2, so nothing is flushed between steps); ``e2e`` is
+weights alone, 3.4 GB, exceed the 126 MB L2, so nothing is flushed between steps); the K-step
+region is repeated until about a second has been timed and the median is reported.  ``e2e`` is
 the same through the Python entry point (``Engine.step``: host token ids in through pinned
-memory, sampled ids back to the host, every step) by wall clock; ``prefill`` is one request of
-2,048 tokens in one step; ``points`` holds decode at batch 1 and 64; ``roofline`` divides the
-bytes a decode step has to read (every weight once, and the cache of the live requests) by its
-time.  A "step" is one decode step.
+memory, sampled ids back to the host, every step) by wall clock, with the bytes each step really
+copied; ``prefill`` is one request of 2,048 tokens in one step; ``points`` holds decode at batch
+1 and 64 (``points_e2e`` the same end to end); ``roofline`` divides the bytes a decode step has
+to read (every weight once, and the cache of the live requests) by its time.  A "step" is one
+decode step.
+
+Other workloads of the same engine, one JSON line each (not part of the default run):
+
+    python bench.py --workload serving-8b    # Qwen3-8B shape: 64 requests, prompts U[128, 2048], 512-token portions, 256 tokens each
+    python bench.py --workload qwen3-32b     # Qwen3-32B shape: 2,048-token prefill, decode at batch 1 and 8 to 4,096, cache from free memory
 """
 from __future__ import annotations
 
@@ -30,6 +37,10 @@ QWEN3_1P7B = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", vocab_
                   intermediate_size=6144, num_hidden_layers=28, num_attention_heads=16, num_key_value_heads=8,
                   head_dim=128, rope_theta=1000000.0, rms_norm_eps=1e-6, tie_word_embeddings=True,
                   max_position_embeddings=40960)
+QWEN3_8B = dict(QWEN3_1P7B, hidden_size=4096, intermediate_size=12288, num_hidden_layers=36, num_attention_heads=32,
+                num_key_value_heads=8, tie_word_embeddings=False)
+QWEN3_32B = dict(QWEN3_1P7B, hidden_size=5120, intermediate_size=25600, num_hidden_layers=64, num_attention_heads=64,
+                 num_key_value_heads=8, tie_word_embeddings=False)
 CONTEXT = 4096          # decode runs up to this many positions
 DECODE_FROM = 3072      # the timed decode steps start here (the middle of 2,048 -> 4,096)
 PREFILL_TOKENS = 2048
@@ -145,8 +156,10 @@ def fill_cache(llm, batch, context):
     return ids
 
 
-def time_decode(llm, batch, steps, warmup, context):
-    """K decode steps of the step function + sampler on the device; returns (ms per step, launches per step)."""
+def time_decode(llm, batch, steps, warmup, context, min_total_ms=1000.0, max_steps=900):
+    """K decode steps of the step function + sampler on the device, timed with CUDA events; the K-step region is
+    repeated (at least 3 times, until ``min_total_ms`` has been timed, within ``max_steps`` positions) and the
+    median taken.  Returns (ms per step, launches per step, repeats, mean context of the timed steps)."""
     import torch
     from ember_b200 import SamplingParams, StepEntry, ops
     from ember_b200.sampling import device as dsampler
@@ -163,30 +176,41 @@ def time_decode(llm, batch, steps, warmup, context):
         logits = r.step(entries)
         dsampler.sample(logits, params, [context + i] * batch, out=out)
 
+    def region(first):
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for i in range(steps):
+            one(first + i)
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / steps
+
     for i in range(warmup):
         one(i)
     torch.cuda.synchronize()
     n0 = ops.launch_count()
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    e0.record()
-    for i in range(steps):
-        one(warmup + i)
-    e1.record()
-    torch.cuda.synchronize()
-    ms = e0.elapsed_time(e1) / steps
+    times = [region(warmup)]
     launches = (ops.launch_count() - n0) / steps
+    done = warmup + steps
+    while done + steps <= max_steps and (len(times) < 3 or sum(times) * steps < min_total_ms):
+        times.append(region(done))
+        done += steps
     r.check_device()
     for rid in ids:
         r.release(rid)
-    return ms, launches
+    mean_context = context + warmup + (done - warmup) / 2.0
+    return statistics.median(times), launches, len(times), mean_context
 
 
-def time_e2e(llm, batch, steps, warmup, context):
-    """The same decode through Engine.step: host ids in (pinned staging), sampled ids out, each step."""
+def time_e2e(llm, batch, steps, warmup, context, min_total_ms=500.0, max_steps=900):
+    """The same decode through Engine.step: host ids in (pinned staging), sampled ids out, each step, by wall
+    clock; K-step regions repeated and the median taken.  Also the bytes a step copied each way, counted where
+    the copies are made (``ember_b200.transfers``)."""
     import torch
-    from ember_b200 import Request, SamplingParams
-    eng, r = llm.engine, llm.runner
-    vocab = r.spec.vocab_size
+    from ember_b200 import Request, SamplingParams, transfers
+    eng = llm.engine
+    vocab = llm.runner.spec.vocab_size
     # requests whose prompts are already cached: prefill them for real through the engine
     import random
     rng = random.Random(1234)
@@ -197,20 +221,24 @@ def time_e2e(llm, batch, steps, warmup, context):
         eng.step()
     for _ in range(warmup):
         eng.step()
-    torch.cuda.synchronize()
-    t0 = time.perf_counter()
-    for _ in range(steps):
-        eng.step()
-    torch.cuda.synchronize()
-    dt = time.perf_counter() - t0
+    times, done = [], warmup
+    h0, d0 = transfers.snapshot()
+    while done + steps <= max_steps and (len(times) < 3 or sum(times) * steps < min_total_ms):
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(steps):
+            eng.step()
+        torch.cuda.synchronize()
+        times.append((time.perf_counter() - t0) * 1000.0 / steps)
+        done += steps
+    h1, d1 = transfers.snapshot()
+    n = steps * len(times)
     for s in seqs:
         s.cancelled = True
     eng.step()
-    # bytes per step: the packed int32 arrays of a decode step (tokens, positions, run index, starts, lengths,
-    # slots, rows, block table) and the sampler's parameter rows in; sampled ids out
-    blocks = (context + steps + warmup + 15) // 16
-    ints = 3 * batch + (batch + 1) + 3 * batch + batch * blocks
-    return dt * 1000.0 / steps, ints * 4 + 32 * batch, 4 * batch
+    eng.drain()
+    llm.runner.check_device()
+    return statistics.median(times), (h1 - h0) // n, (d1 - d0) // n
 
 
 def time_prefill(llm, tokens, reps, warmup):
@@ -294,6 +322,137 @@ def breakdown(cfg, n_layers, batch) -> int:
     return 0
 
 
+def workload_serving_8b(args, pk) -> int:
+    """BASELINE's fourth configuration: the Qwen3-8B shape, 64 requests with random-id prompts of lengths uniform in
+    [128, 2048], continuous batching with 512-token prompt portions, 256 decoded tokens each, through ``Engine``
+    (host ids in, host ids out).  The cache is sized from the device's free memory."""
+    import random
+    import torch
+    import ember_b200
+    from ember_b200 import Request, SamplingParams
+    from ember_b200.config import Qwen3Config
+    cfg = Qwen3Config.from_json(dict(QWEN3_8B, num_hidden_layers=args.layers or QWEN3_8B["num_hidden_layers"]))
+    n_layers = cfg.num_hidden_layers
+    wbytes, kv_per_token, _ = model_bytes_and_flops(cfg, n_layers)
+    n_req, gen, chunk = 64, 256, 512
+    with ClockSampler() as clocks:
+        llm = ember_b200.load_random(cfg, seed=0, dtype="bfloat16", kv_cache_tokens=0, page_tokens=PAGE_TOKENS,
+                                     max_batch_tokens=2048, max_seqs=64, prefill_chunk=chunk, max_context=4096)
+        eng, vocab = llm.engine, cfg.vocab_size
+        rng = random.Random(1234)
+        greedy = SamplingParams(temperature=0.0)
+
+        def submit(n, lo, hi, ntok):
+            return [eng.submit(Request(prompt=[rng.randrange(1000, min(100000, vocab)) for _ in range(rng.randint(lo, hi))],
+                                       sampling=greedy, max_tokens=ntok, ignore_eos=True)) for _ in range(n)]
+
+        def run(seqs, trace=None):
+            sched = eng.scheduler
+            torch.cuda.synchronize()
+            t0 = time.perf_counter()
+            while any(s.finished is None for s in seqs):
+                before = sched.stats.prompt_tokens + sched.stats.generated_tokens
+                if not eng.step():
+                    break
+                if trace is not None:      # (tokens this commit accounted for, tokens cached by the running requests, how many run)
+                    trace.append((sched.stats.prompt_tokens + sched.stats.generated_tokens - before,
+                                  sum(q.computed for q in sched.running), len(sched.running)))
+            eng.drain()
+            torch.cuda.synchronize()
+            return time.perf_counter() - t0
+
+        run(submit(8, 128, 600, 8))                                   # warm-up: every kernel shape of the mix once
+        s0 = eng.stats.steps
+        seqs = submit(n_req, 128, 2048, gen)
+        prompt_tokens = sum(q.prompt_len for q in seqs)
+        trace = []
+        dt = run(seqs, trace)
+        llm.runner.check_device()
+    steps = eng.stats.steps - s0
+    generated = sum(len(q.output) for q in seqs)
+    # the roofline of each step: the slower of reading (weights once + the running requests' cache) and computing
+    # (2 flops per weight per token + attention over the cached tokens), summed over the steps
+    H, D, nh = cfg.hidden_size, cfg.head_dim, cfg.num_attention_heads
+    per_layer = H * (cfg.q_dim + 2 * cfg.kv_dim) + cfg.q_dim * H + 3 * H * cfg.intermediate_size
+    bound_s, read_bytes, flops = 0.0, 0.0, 0.0
+    for toks, live, running in trace:
+        b = wbytes + live * kv_per_token
+        # every token attends to about the mean cached length of the running requests
+        f = 2.0 * max(toks, 1) * n_layers * per_layer + 2.0 * cfg.vocab_size * H * min(max(toks, 1), 64) \
+            + 4.0 * n_layers * nh * D * (live / max(running, 1)) * max(toks, 1)
+        bound_s += max(b / (pk["hbm_gbs"] * 1e9), f / (pk["bf16_tflops_sustained"] * 1e12))
+        read_bytes += b
+        flops += f
+    out = {"metric": "continuous batching: generated tok/s, 64 requests, prompts U[128,2048], 512-token portions, 256 tokens each (Qwen3-8B shape)",
+           "value": round(generated / dt, 1), "unit": "tokens/s", "n_gpus": 1, "steps": steps, "warmup": 1,
+           "ms_per_step": round(dt * 1000.0 / max(steps, 1), 4), "higher_is_better": True, "dtype": "bf16", "impl": "ours",
+           "data": "synthetic (random weights from a seed, random token ids)",
+           "config": {"model": "Qwen3-8B shape", "requests": n_req, "prompt_tokens": prompt_tokens, "generated_tokens": generated,
+                      "prefill_chunk": chunk, "max_batch_tokens": 2048, "max_seqs": 64, "layers": n_layers,
+                      "layers_of_config": QWEN3_8B["num_hidden_layers"], "hidden": H, "intermediate": cfg.intermediate_size,
+                      "heads": nh, "kv_heads": cfg.num_key_value_heads, "vocab": cfg.vocab_size, "page_tokens": PAGE_TOKENS,
+                      "cache_tokens": llm.runner.cache.capacity_tokens(), "peaks": pk["source"]},
+           "e2e": {"value": round(generated / dt, 1), "unit": "tokens/s", "total_tokens_per_s": round((generated + prompt_tokens) / dt, 1),
+                   "seconds": round(dt, 3), "note": "this workload is end to end by construction (Engine.step, host ids in and out)"},
+           "preemptions": eng.stats.preemptions,
+           "roofline": {"bound": "per step, the slower of hbm and tensor", "frac": round(bound_s / dt, 4),
+                        "hbm_frac": round(read_bytes / dt / 1e9 / pk["hbm_gbs"], 4),
+                        "tensor_frac": round(flops / dt / 1e12 / pk["bf16_tflops_sustained"], 4)},
+           "clocks": clocks.summary()}
+    print(json.dumps(out))
+    return 0
+
+
+def workload_qwen3_32b(args, pk) -> int:
+    """BASELINE's fifth configuration: the Qwen3-32B shape (65.5 GB of bf16 weights), a 2,048-token prefill, decode
+    at batch 1 and 8 from context 3,072 towards 4,096, the cache sized from the memory the weights leave."""
+    global CONTEXT
+    import torch
+    import ember_b200
+    from ember_b200.config import Qwen3Config
+    cfg = Qwen3Config.from_json(dict(QWEN3_32B, num_hidden_layers=args.layers or QWEN3_32B["num_hidden_layers"]))
+    n_layers = cfg.num_hidden_layers
+    wbytes, kv_per_token, prefill_flops = model_bytes_and_flops(cfg, n_layers)
+    warmup = max(3, args.warmup)
+    with ClockSampler() as clocks:
+        t0 = time.perf_counter()
+        llm = ember_b200.load_random(cfg, seed=0, dtype="bfloat16", kv_cache_tokens=0, page_tokens=PAGE_TOKENS,
+                                     max_batch_tokens=2048, max_seqs=64, prefill_chunk=2048, gpu_memory=0.92)
+        torch.cuda.synchronize()
+        load_s = time.perf_counter() - t0
+        r = llm.runner
+        free, total = torch.cuda.mem_get_info()
+        pms = time_prefill(llm, PREFILL_TOKENS, reps=3, warmup=2)
+        points, fracs = {}, {}
+        for b in (1, 8):
+            ms, _, _, ctx = time_decode(llm, b, args.steps, warmup, DECODE_FROM, min_total_ms=1500.0,
+                                        max_steps=CONTEXT - DECODE_FROM - 8)
+            points[f"decode_b{b}"] = round(b * 1000.0 / ms, 1)
+            fracs[f"decode_b{b}"] = round((wbytes + b * ctx * kv_per_token) / (ms * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
+            if b == 8:
+                ms8, ctx8 = ms, ctx
+    fl = prefill_flops(PREFILL_TOKENS)
+    step_bytes = wbytes + 8 * ctx8 * kv_per_token
+    out = {"metric": "decode tok/s at batch 1/8; prefill tok/s at 2,048 tokens (Qwen3-32B)", "value": points["decode_b8"],
+           "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup, "ms_per_step": round(ms8, 4),
+           "higher_is_better": True, "dtype": "bf16", "impl": "ours",
+           "data": "synthetic (random weights from a seed, random token ids)",
+           "config": {"model": "Qwen3-32B shape", "global_batch": 8, "seq_len": CONTEXT, "decode_from": DECODE_FROM,
+                      "layers": n_layers, "layers_of_config": QWEN3_32B["num_hidden_layers"], "hidden": cfg.hidden_size,
+                      "intermediate": cfg.intermediate_size, "heads": cfg.num_attention_heads,
+                      "kv_heads": cfg.num_key_value_heads, "vocab": cfg.vocab_size, "page_tokens": PAGE_TOKENS,
+                      "gpu_memory": 0.92, "cache_tokens": r.cache.capacity_tokens(),
+                      "cache_gib": round(r.storage.bytes() / 2**30, 1), "device_free_gib_after": round(free / 2**30, 1),
+                      "load_seconds": round(load_s, 1), "peaks": pk["source"]},
+           "roofline": {"bound": "hbm", "achieved": round(step_bytes / (ms8 * 1e-3) / 1e9, 1), "peak": pk["hbm_gbs"],
+                        "unit": "GB/s", "frac": fracs["decode_b8"], "bytes_per_step": int(step_bytes)},
+           "prefill": {"value": round(PREFILL_TOKENS / (pms * 1e-3), 1), "tokens": PREFILL_TOKENS, "ms": round(pms, 3),
+                       "frac": round(fl / (pms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4), "tflops": round(fl / (pms * 1e-3) / 1e12, 1)},
+           "points": points, "points_hbm_frac": fracs, "clocks": clocks.summary()}
+    print(json.dumps(out))
+    return 0
+
+
 def main() -> int:
     global PAGE_TOKENS, CONTEXT, DECODE_FROM
     ap = argparse.ArgumentParser()
@@ -309,6 +468,9 @@ def main() -> int:
                     help="profiling aid: device time per kernel of three decode steps and one 2,048-token prefill step "
                          "(kernels serialised: EMBER_PDL=0 and no CUDA graphs are set by this flag)")
     ap.add_argument("--page-tokens", type=int, default=PAGE_TOKENS, choices=[16, 32, 64], help="tokens per cache page")
+    ap.add_argument("--workload", default="default", choices=["default", "serving-8b", "qwen3-32b"],
+                    help="default: the Qwen3-1.7B line the contract asks for; the others are BASELINE's fourth and fifth "
+                         "configurations, one JSON line each")
     ap.add_argument("--prefill-tokens", type=int, default=PREFILL_TOKENS,
                     help="with --only-prefill: another prompt length (the reported line stays at 2,048)")
     ap.add_argument("--decode-from", type=int, default=DECODE_FROM,
@@ -345,6 +507,10 @@ def main() -> int:
     pk = peaks()
     wbytes, kv_per_token, prefill_flops = model_bytes_and_flops(cfg, n_layers)
 
+    if args.workload == "serving-8b":
+        return workload_serving_8b(args, pk)
+    if args.workload == "qwen3-32b":
+        return workload_qwen3_32b(args, pk)
     if args.breakdown:
         return breakdown(cfg, n_layers, args.batch)
     if args.only_prefill:
@@ -356,57 +522,75 @@ def main() -> int:
                                       "ms": round(pms, 3), "tflops": round(fl / (pms * 1e-3) / 1e12, 1), "layers": n_layers}}))
         return 0
 
-    llm = build_llm(cfg, n_layers, max(args.batch, 1))
-    with ClockSampler() as clocks:
-        ms, launches = time_decode(llm, args.batch, args.steps, warmup, DECODE_FROM)
-    # (the end-to-end loop prefills its prompts through the engine; at other context lengths than the default's the
-    # first requests would be done decoding before the last has its prompt in, so it is measured at the default only)
-    e2e_ms, h2d, d2h = time_e2e(llm, args.batch, args.steps, warmup, DECODE_FROM) if custom_context is None else (None, 0, 0)
-    value = args.batch * 1000.0 / ms
-    ctx_mid = DECODE_FROM + warmup + args.steps / 2
-    step_bytes = wbytes + args.batch * ctx_mid * kv_per_token
-    achieved = step_bytes / (ms * 1e-3) / 1e9
-
-    out = {
-        "metric": "decode tok/s at batch 1/8/64; prefill tok/s at 2,048 tokens (Qwen3-1.7B)",
-        "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup,
-        "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "bf16", "data": "synthetic (random weights from a seed, random token ids)", "impl": "ours",
-        "config": {"model": "Qwen3-1.7B shape", "global_batch": args.batch, "seq_len": CONTEXT,
-                   "decode_from": DECODE_FROM, "layers": n_layers, "layers_of_config": cfg.num_hidden_layers,
-                   "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
-                   "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
-                   "tied": cfg.tie_word_embeddings, "page_tokens": PAGE_TOKENS, "parallelism": "single GPU",
-                   "l2": "inputs larger than L2 (3.4 GB of weights per step); no flush",
-                   "peaks": pk["source"]},
-        "clocks": clocks.summary(),
-        "e2e": ({"value": round(args.batch * 1000.0 / e2e_ms, 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms, 4),
-                 "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h} if e2e_ms is not None else
-                {"skipped": "measured at the default context only"}),
-        "gpu_launches": int(round(launches * args.steps)),
-        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
-                     "frac": round(achieved / pk["hbm_gbs"], 4), "bytes_per_step": int(step_bytes)},
-    }
-    del llm
-    torch.cuda.empty_cache()
-
-    if not args.skip_points:
-        llm = build_llm(cfg, n_layers, 1)
-        pms = time_prefill(llm, PREFILL_TOKENS, reps=5, warmup=3)
-        fl = prefill_flops(PREFILL_TOKENS)
-        out["prefill"] = {"value": round(PREFILL_TOKENS / (pms * 1e-3), 1), "tokens": PREFILL_TOKENS, "ms": round(pms, 3),
-                          "frac": round(fl / (pms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4), "tflops": round(fl / (pms * 1e-3) / 1e12, 1)}
-        points = {}
-        ms1, _ = time_decode(llm, 1, args.steps, warmup, DECODE_FROM)
-        points["decode_b1"] = round(1000.0 / ms1, 1)
+    room = CONTEXT - DECODE_FROM - 8                 # positions left for timed steps before the context limit
+    with ClockSampler() as clocks_all:
+        llm = build_llm(cfg, n_layers, max(args.batch, 1))
+        with ClockSampler() as clocks:
+            ms, launches, repeats, mean_ctx = time_decode(llm, args.batch, args.steps, warmup, DECODE_FROM, max_steps=min(900, room))
+        # (the end-to-end loop prefills its prompts through the engine; at other context lengths than the default's
+        # the first requests would be done decoding before the last has its prompt in, so it is measured at the
+        # default only)
+        e2e_ms, h2d, d2h = time_e2e(llm, args.batch, args.steps, warmup, DECODE_FROM) if custom_context is None else (None, 0, 0)
+        value = args.batch * 1000.0 / ms
+        step_bytes = wbytes + args.batch * mean_ctx * kv_per_token
+        achieved = step_bytes / (ms * 1e-3) / 1e9
+        head_clocks = clocks.summary()
+        out = {
+            "metric": "decode tok/s at batch 1/8/64; prefill tok/s at 2,048 tokens (Qwen3-1.7B)",
+            "value": round(value, 1), "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup,
+            "ms_per_step": round(ms, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic (random weights from a seed, random token ids)", "impl": "ours",
+            "config": {"model": "Qwen3-1.7B shape", "global_batch": args.batch, "seq_len": CONTEXT,
+                       "decode_from": DECODE_FROM, "layers": n_layers, "layers_of_config": cfg.num_hidden_layers,
+                       "hidden": cfg.hidden_size, "heads": cfg.num_attention_heads, "kv_heads": cfg.num_key_value_heads,
+                       "head_dim": cfg.head_dim, "intermediate": cfg.intermediate_size, "vocab": cfg.vocab_size,
+                       "tied": cfg.tie_word_embeddings, "page_tokens": PAGE_TOKENS, "parallelism": "single GPU",
+                       "l2": "inputs larger than L2 (3.4 GB of weights per step); no flush",
+                       "timing": f"median of {repeats} regions of {args.steps} steps, CUDA events",
+                       "peaks": pk["source"]},
+            "clocks": head_clocks,
+            "e2e": ({"value": round(args.batch * 1000.0 / e2e_ms, 1), "unit": "tokens/s", "ms_per_step": round(e2e_ms, 4),
+                     "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": int(d2h)} if e2e_ms is not None else
+                    {"skipped": "measured at the default context only"}),
+            "gpu_launches": int(round(launches * args.steps)),
+            "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"], "unit": "GB/s",
+                         "frac": round(achieved / pk["hbm_gbs"], 4), "bytes_per_step": int(step_bytes)},
+        }
+        if head_clocks.get("sm_mhz"):
+            # time x clock: lets a run at boost clocks be compared with one under the power cap
+            out["ms_per_step_x_ghz"] = round(ms * head_clocks["sm_mhz"] / 1000.0, 4)
         del llm
         torch.cuda.empty_cache()
-        llm = build_llm(cfg, n_layers, 64)
-        ms64, _ = time_decode(llm, 64, max(8, args.steps // 2), warmup, DECODE_FROM)
-        points["decode_b64"] = round(64 * 1000.0 / ms64, 1)
-        points["decode_b8"] = round(value, 1)
-        out["points"] = points
-        del llm
+
+        if not args.skip_points:
+            llm = build_llm(cfg, n_layers, 1)
+            pms = time_prefill(llm, PREFILL_TOKENS, reps=5, warmup=3)
+            fl = prefill_flops(PREFILL_TOKENS)
+            out["prefill"] = {"value": round(PREFILL_TOKENS / (pms * 1e-3), 1), "tokens": PREFILL_TOKENS, "ms": round(pms, 3),
+                              "frac": round(fl / (pms * 1e-3) / (pk["bf16_tflops"] * 1e12), 4), "tflops": round(fl / (pms * 1e-3) / 1e12, 1)}
+            points, points_e2e, fracs = {}, {}, {}
+            ms1, _, _, ctx1 = time_decode(llm, 1, args.steps, warmup, DECODE_FROM, max_steps=min(900, room))
+            points["decode_b1"] = round(1000.0 / ms1, 1)
+            fracs["decode_b1"] = round((wbytes + ctx1 * kv_per_token) / (ms1 * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
+            if custom_context is None:
+                points_e2e["decode_b1"] = round(1000.0 / time_e2e(llm, 1, args.steps, warmup, DECODE_FROM)[0], 1)
+            del llm
+            torch.cuda.empty_cache()
+            llm = build_llm(cfg, n_layers, 64)
+            ms64, _, _, ctx64 = time_decode(llm, 64, max(8, args.steps // 2), warmup, DECODE_FROM, max_steps=min(900, room))
+            points["decode_b64"] = round(64 * 1000.0 / ms64, 1)
+            fracs["decode_b64"] = round((wbytes + 64 * ctx64 * kv_per_token) / (ms64 * 1e-3) / 1e9 / pk["hbm_gbs"], 4)
+            if custom_context is None:
+                points_e2e["decode_b64"] = round(64 * 1000.0 / time_e2e(llm, 64, max(8, args.steps // 2), warmup, DECODE_FROM)[0], 1)
+            points["decode_b8"] = round(value, 1)
+            fracs["decode_b8"] = out["roofline"]["frac"]
+            if e2e_ms is not None:
+                points_e2e["decode_b8"] = out["e2e"]["value"]
+            out["points"] = points
+            out["points_e2e"] = points_e2e
+            out["points_hbm_frac"] = fracs
+            del llm
+    out["clocks_all_points"] = clocks_all.summary()
     print(json.dumps(out))
     return 0
 

@@ -21,7 +21,7 @@ from .engine.engine import Engine
 from .engine.runner import ModelRunner
 from .sampling.params import SamplingParams
 from .weights.loader import WeightStore
-from .weights.random_init import random_tensors
+from .weights.random_init import RandomSource
 
 
 class LLM:
@@ -77,8 +77,9 @@ def load_random(config, seed: int = 0, dtype: str = "bfloat16", device: str = "c
     (on the device when it is a CUDA device) and loaded as if they came from a file."""
     spec = config.to_model_spec()
     gen_device = device if torch.cuda.is_available() else "cpu"
-    store = WeightStore.from_tensors(dict(random_tensors(spec, seed, weight_dtype, std, norm_std, device=gen_device)),
-                                     description=f"random weights (seed {seed})")
+    # tensors are made one at a time as the parts take them: a 65 GB model is never held twice
+    store = WeightStore(RandomSource(spec, seed, weight_dtype, std, norm_std, device=gen_device),
+                        description=f"random weights (seed {seed})")
     runner = ModelRunner(spec, store, dtype=dtype, device=device, capacity_tokens=kv_cache_tokens,
                          max_batch_tokens=max_batch_tokens, max_requests=max_seqs, page_tokens=page_tokens,
                          cuda_graphs=cuda_graphs, memory_fraction=gpu_memory, cache_bytes=int(kv_cache_mib) << 20,

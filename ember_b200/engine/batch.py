@@ -14,6 +14,7 @@ from typing import Dict, Hashable, List, Optional, Sequence, Tuple
 import numpy as np
 import torch
 
+from .. import transfers
 from ..cache.manager import CacheManager
 
 
@@ -279,6 +280,7 @@ class StepContext:
                     hn[o:o + p.size] = p
         self.ints[:self._total].copy_(host[:self._total], non_blocking=True)
         event.record()
+        transfers.add_h2d(4 * self._total)
 
     def _view(self, i: int, shape=None) -> torch.Tensor:
         v = self.ints[self._offs[i]:self._offs[i] + self._sizes[i]]

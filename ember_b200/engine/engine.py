@@ -24,6 +24,7 @@ from typing import Dict, List, Optional, Sequence, Union
 
 import torch
 
+from .. import transfers
 from ..sampling import device as device_sampler
 from ..sampling.params import SamplingParams
 from .batch import StepEntry
@@ -136,6 +137,7 @@ class Engine:
             host, event = self._ids_staging(rows)
             host.copy_(self.runner.ids_and_err, non_blocking=True)      # ids and the error word: one small copy
             event.record()
+            transfers.add_d2h(4 * host.numel())
             return _InFlight(batch, rows, host, event)
         except Exception:
             self._inflight = None

@@ -7,7 +7,7 @@ from typing import Optional, Sequence
 import numpy as np
 import torch
 
-from .. import ops
+from .. import ops, transfers
 from .params import SamplingParams
 
 _ROW = struct.Struct("<fiffQQ")   # temperature, top_k, top_p, min_p, seed, counter: 32 bytes
@@ -71,5 +71,6 @@ def sample(logits: torch.Tensor, params: Sequence[SamplingParams], counters: Seq
     host[:rows * _ROW.size].copy_(torch.from_numpy(pack_params(params, counters)))
     dev[:rows * _ROW.size].copy_(host[:rows * _ROW.size], non_blocking=True)
     event.record()
+    transfers.add_h2d(rows * _ROW.size)
     ops.sample(logits, dev, out, rows)
     return out

@@ -271,3 +271,39 @@ def test_captured_residuals_follow_the_plain_layers(dtype, tiny_model_dirs):
         assert float((got[l].double() - h[40]).norm() / h[40].norm()) < tol, l
     r.set_capture_hidden(False)
     assert r.graph_replays == 0
+
+
+def test_bfloat16_logits_alone_and_in_a_batch_of_ten(tiny_model_dirs):
+    """In bfloat16 a step of up to 8 tokens (and a portion of 512 or more) norms and rotates the heads on the fp32
+    accumulator in the q/k/v product's epilogue, while a step of 9 to 511 tokens rounds the product to bfloat16
+    first and finishes the heads in a kernel of its own.  The keys a request caches and its logits therefore
+    differ by a rounding with the company it keeps; they must stay within bfloat16's tolerance of the plain
+    implementation, and of each other, either way."""
+    from ember_b200 import StepEntry
+    name = "c"                                     # heads of 128: the fused epilogue applies
+    plain = PlainQwen3(tiny_model_dirs[name], torch.float64)
+    rng = np.random.default_rng(33)
+    vocab = TINY[name]["json"]["vocab_size"]
+    seqs = [rng.integers(0, vocab, size=40).tolist() for _ in range(10)]
+    want = plain.logits(seqs[0]).numpy()
+
+    def decode(n_requests):
+        llm = load(tiny_model_dirs, name, "bfloat16", max_seqs=16, kv_cache_tokens=2048)
+        r = llm.runner
+        for i in range(n_requests):
+            r.admit(i), r.reserve(i, 20)
+        r.step([StepEntry(i, seqs[i][:20], ()) for i in range(n_requests)])
+        rows = []
+        for t in range(20, 40):                     # single tokens: 1 run a step (fused) or 10 (separate kernel)
+            for i in range(n_requests):
+                assert r.reserve(i, 1)
+            lg = r.step([StepEntry(i, [seqs[i][t]], (0,)) for i in range(n_requests)])
+            rows.append(lg[0].float().cpu().numpy().copy())
+        r.check_device()
+        return np.stack(rows)
+
+    alone, together = decode(1), decode(10)
+    rel = lambda a, b: float(np.linalg.norm(a - b) / np.linalg.norm(b))          # noqa: E731
+    assert max(rel(alone[i], want[20 + i]) for i in range(20)) < 2.5e-2
+    assert max(rel(together[i], want[20 + i]) for i in range(20)) < 2.5e-2
+    assert max(rel(together[i], alone[i]) for i in range(20)) < 2.5e-2
