@@ -294,6 +294,21 @@ EMBER_API int ember_gemm_tc(const void* A, const void* W, void* out, int ldc, in
             if (splits > 8) splits = 8;
             while (splits > 1 && p.num_k_blocks / splits < 2) splits--;
         }
+    } else if (p.swapped && split_mode >= 16) {
+        splits = split_mode - 16;                      // tuning and tests: this many parts of K, summed with atomics
+        if (splits < 1) splits = 1;
+        while (splits > 1 && p.num_k_blocks / splits < 2) splits--;
+    } else if (p.swapped && p.block_cols > 16) {
+        // Token tiles of 17 to 128: two such blocks fit on an SM, the stream reaches the memory's rate once about
+        // that many blocks are in flight, and every further part of K costs atomics and a wider finalize pass.  So:
+        // as many parts as keep tiles x parts within two blocks an SM, at least four k-blocks each.  Measured at 64
+        // tokens (us; parts in brackets): 1.7B widths q/k/v 12.6 (8), O 7.7 (8), gate/up 18.1 (3), down 10.5 (16),
+        // head 137 (1); 8B widths 18.6 (6), 11.9 (8), 43.0 (1), 22.3 (8), 232 (1).  (Counting waves over the SMs
+        // alone gave the head 16 parts, 364 us, and the 8B gate/up 3 parts, 51 us.)
+        splits = 2 * num_sms / (tiles > 0 ? tiles : 1);
+        if (splits > 16) splits = 16;
+        if (splits > p.num_k_blocks / 4) splits = p.num_k_blocks / 4;
+        if (splits < 1) splits = 1;
     } else if (p.swapped) {
         // minimise the number of waves over the SMs; a larger split must pay for itself
         double best = 1e30;
