@@ -285,16 +285,21 @@ EMBER_API int ember_gemm_tc(const void* A, const void* W, void* out, int ldc, in
     // The split count depends on N and K only.
     const int tiles = row_tiles * col_tiles;
     const bool store_epilogue = epilogue != 2;
-    const bool use_cluster = split_mode == 2 || (split_mode == 0 && p.block_cols <= 16 && store_epilogue);
+    const bool use_cluster = split_mode == 2 || split_mode >= 32 || (split_mode == 0 && p.block_cols <= 16 && store_epilogue);
     int splits = 1;
-    if (p.swapped && use_cluster) {
+    if (p.swapped && use_cluster && split_mode >= 32) {
+        splits = split_mode - 32;                      // tuning and tests: a cluster of this many blocks
+        if (splits > 8) splits = 8;
+        if (splits < 1) splits = 1;
+        while (splits > 1 && p.num_k_blocks / splits < 2) splits--;
+    } else if (p.swapped && use_cluster) {
         // fill the SMs once: clusters of up to 8 blocks, at least 2 k-blocks each
         if (tiles < num_sms) {
             splits = (num_sms + tiles - 1) / tiles;
             if (splits > 8) splits = 8;
             while (splits > 1 && p.num_k_blocks / splits < 2) splits--;
         }
-    } else if (p.swapped && split_mode >= 16) {
+    } else if (p.swapped && split_mode >= 16 && split_mode < 32) {
         splits = split_mode - 16;                      // tuning and tests: this many parts of K, summed with atomics
         if (splits < 1) splits = 1;
         while (splits > 1 && p.num_k_blocks / splits < 2) splits--;
