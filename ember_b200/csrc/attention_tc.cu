@@ -415,6 +415,16 @@ __global__ void attention_tc_combine_kernel(const float* __restrict__ part_o, co
     const int tile = (int)(th / n_heads), head = (int)(th % n_heads);
     const size_t oh = (size_t)tiles[tile * 4 + 1] * n_heads + head;        // the tile's single token row
     const float* ml = part_ml + th * n_splits * 2;
+    // Up to 16 splits (what the planner makes): a thread's partial sums are requested now, so that they travel
+    // while the first warp forms the weights (one trip to memory behind the dependency instead of two).
+    constexpr int EARLY = 16;
+    const bool early = n_splits <= EARLY && (int)threadIdx.x < D;
+    float a[EARLY];
+    if (early) {
+        const float* po = part_o + th * n_splits * D + threadIdx.x;
+#pragma unroll
+        for (int s = 0; s < EARLY; s++) a[s] = s < n_splits ? po[(size_t)s * D] : 0.0f;
+    }
     if (threadIdx.x < 32) {
         // one warp: lanes take the splits (in rounds of 32), the sums run in ascending order of the split
         float M = -INFINITY;
@@ -435,7 +445,14 @@ __global__ void attention_tc_combine_kernel(const float* __restrict__ part_o, co
     }
     __syncthreads();
     const float inv = inv_s;
-    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+    if (early) {
+        float o = 0.0f;
+#pragma unroll
+        for (int s = 0; s < EARLY; s++)
+            if (s < n_splits) o = fmaf(a[s], w_s[s], o);                   // ascending, as below
+        out[oh * D + threadIdx.x] = __float2bfloat16_rn(o * inv);
+    }
+    for (int d = (int)threadIdx.x + (early ? (int)blockDim.x : 0); d < D; d += blockDim.x) {
         const float* po = part_o + th * n_splits * D + d;
         float o = 0.0f;
         int s = 0;
