@@ -50,6 +50,7 @@ struct AttnTcParams {
     float scale_log2;         // softmax scale * log2(e)
     int n_splits, split_keys;
     int n_tiles;
+    int cluster_merge;        // the splits of a tile are a thread-block cluster and are merged in its first block's shared memory
     int* err;
 };
 
@@ -91,6 +92,17 @@ __device__ __forceinline__ void atc_tma_2d(void* dst, const CUtensorMap* map, ui
         ::"r"(s32(dst)), "l"((uint64_t)map), "r"(s32(bar)), "r"(x), "r"(y) : "memory");
 }
 
+__device__ __forceinline__ uint32_t atc_map_to_rank(uint32_t smem_addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void atc_st_cluster(uint32_t addr, float v) {
+    asm volatile("st.shared::cluster.f32 [%0], %1;" ::"r"(addr), "f"(v) : "memory");
+}
+__device__ __forceinline__ void atc_cluster_arrive() { asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory"); }
+__device__ __forceinline__ void atc_cluster_wait() { asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory"); }
+
 // Byte offset of (row, 16-byte chunk) inside a [rows][64 bf16] half-tile with the 128-byte swizzle.
 __device__ __forceinline__ uint32_t swz(int row, int chunk) { return (uint32_t)(row * 128 + ((chunk ^ (row & 7)) << 4)); }
 
@@ -116,6 +128,10 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
     uint64_t* full_bar = (uint64_t*)(v_s + NSTAGE * TILE_BYTES);
     uint64_t* empty_bar = full_bar + NSTAGE;
     volatile int* abort_flag = (volatile int*)(empty_bar + NSTAGE);
+    // cluster merge (decode): what every split of the tile hands to the first one: [splits][rows][D] sums, then
+    // [splits][rows][2] maxima (log2 units) and denominators.  A region of its own: it is written by the other
+    // blocks while this one may still be multiplying.
+    float* recv = reinterpret_cast<float*>((reinterpret_cast<uintptr_t>(abort_flag + 1) + 15) & ~(uintptr_t)15);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int g8 = lane >> 2, t4 = lane & 3;
@@ -145,6 +161,8 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
         asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
     }
 
+    const bool merge_in_cluster = DECODE && p.cluster_merge && p.n_splits > 1;
+    if (merge_in_cluster) atc_cluster_arrive();     // phase 1: every block of the cluster runs before anyone writes to it
     pdl_launch_dependents();
     pdl_wait();       // queries and the newest keys are written by the kernel before this one
 
@@ -372,6 +390,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
         rb[0] = o[j][2]; rb[1] = o[j][3];
     }
     __syncthreads();
+    if (merge_in_cluster) atc_cluster_wait();
+    const uint32_t recv_o0 = atc_map_to_rank(s32(recv), 0);
+    const uint32_t recv_ml0 = recv_o0 + (uint32_t)(p.n_splits * rows * D) * 4u;
     for (int idx = threadIdx.x; idx < rows * D; idx += ATC_THREADS) {
         const int r = idx / D, d = idx - r * D;
         float M = -INFINITY;
@@ -389,6 +410,12 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
         // nq == 1: row r is head r of the group
         if (p.n_splits <= 1) {
             p.out[((size_t)row0 * p.n_heads + kvh * G + r) * D + d] = __float2bfloat16_rn(L > 0.0f ? acc / L : 0.0f);
+        } else if (merge_in_cluster) {
+            atc_st_cluster(recv_o0 + (uint32_t)((split * rows + r) * D + d) * 4u, acc);
+            if (d == 0) {
+                atc_st_cluster(recv_ml0 + (uint32_t)((split * rows + r) * 2) * 4u, M);
+                atc_st_cluster(recv_ml0 + (uint32_t)((split * rows + r) * 2 + 1) * 4u, L);
+            }
         } else {
             const size_t ph = (size_t)tile * p.n_heads + kvh * G + r;      // partials are indexed by tile
             p.part_o[(ph * p.n_splits + split) * D + d] = acc;
@@ -396,6 +423,28 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
                 p.part_ml[(ph * p.n_splits + split) * 2 + 0] = M == -INFINITY ? -INFINITY : M * (1.0f / LOG2E);
                 p.part_ml[(ph * p.n_splits + split) * 2 + 1] = L;
             }
+        }
+    }
+    if (merge_in_cluster) {
+        // ---- the tile's first block merges the splits in ascending order (the arithmetic of the merge kernel)
+        atc_cluster_arrive();                       // phase 2: every split's results are written ...
+        atc_cluster_wait();                         // ... and visible
+        if (split != 0) return;
+        const float* ro = recv;
+        const float* rml = recv + (size_t)p.n_splits * rows * D;
+        for (int idx = threadIdx.x; idx < rows * D; idx += ATC_THREADS) {
+            const int r = idx / D, d = idx - r * D;
+            float M = -INFINITY;
+            for (int sp = 0; sp < p.n_splits; sp++) M = fmaxf(M, rml[(sp * rows + r) * 2]);
+            float L = 0.0f, acc = 0.0f;
+            for (int sp = 0; sp < p.n_splits; sp++) {
+                const float ms = rml[(sp * rows + r) * 2];
+                if (ms == -INFINITY) continue;
+                const float f = exp2f(ms - M);
+                L += rml[(sp * rows + r) * 2 + 1] * f;
+                acc = fmaf(ro[((size_t)sp * rows + r) * D + d], f, acc);
+            }
+            p.out[((size_t)row0 * p.n_heads + kvh * G + r) * D + d] = __float2bfloat16_rn(L > 0.0f ? acc * (1.0f / L) : 0.0f);
         }
     }
 }
@@ -540,8 +589,12 @@ EMBER_API int ember_attention_tc(const void* q, const void* k_pool, const void* 
     if (!ember_attention_tc_supported(D, G, page, mode))
         return fail("attention_tc: head size %d, group %d, page %d are not taken in mode %d", D, G, page, mode);
     if (mode == 0 && n_splits != 1) return fail("attention_tc: prompt portions are not split");
-    if (n_splits < 1 || (n_splits > 1 && (split_keys <= 0 || split_keys % KT || !part_o || !part_ml)))
+    // splits without buffers for their partial results: the splits of a tile form a thread-block cluster (at most 8
+    // blocks) and are merged in shared memory
+    const bool cluster_merge = n_splits > 1 && !part_o && !part_ml;
+    if (n_splits < 1 || (n_splits > 1 && (split_keys <= 0 || split_keys % KT || (!cluster_merge && (!part_o || !part_ml)))))
         return fail("attention_tc: bad split configuration (%d splits of %d keys)", n_splits, split_keys);
+    if (cluster_merge && n_splits > 8) return fail("attention_tc: %d splits are too many for a cluster (at most 8)", n_splits);
     if (n_splits > 8192 || n_kv > 65535) return fail("attention_tc: grid too large");
     CUtensorMap mk, mv;
     const long long total_rows = (long long)num_pages * n_kv * page;
@@ -552,24 +605,41 @@ EMBER_API int ember_attention_tc(const void* q, const void* k_pool, const void* 
     p.tiles = tiles; p.block_table = block_table; p.max_blocks = max_blocks; p.page = page; p.num_pages = num_pages;
     p.n_heads = n_heads; p.n_kv = n_kv; p.window = window; p.scale_log2 = scale * LOG2E;
     p.n_splits = n_splits; p.split_keys = split_keys; p.n_tiles = n_tiles; p.err = err;
+    p.cluster_merge = cluster_merge ? 1 : 0;
     cudaStream_t st = (cudaStream_t)stream;
     const size_t tile_bytes = (size_t)(D / 64) * KT * 128;
     const size_t q_bytes = ((size_t)(D / 64) * (mode == 1 ? 16 : 64) * 128 + 1023) & ~(size_t)1023;
-    const size_t smem = q_bytes + (size_t)(mode == 1 ? 3 : 2) * 2 * tile_bytes + 1024 + 128;
+    const size_t recv_bytes = cluster_merge ? (size_t)n_splits * G * (D + 2) * sizeof(float) + 16 : 0;
+    const size_t smem = q_bytes + (size_t)(mode == 1 ? 3 : 2) * 2 * tile_bytes + 1024 + 128 + recv_bytes;
     dim3 grid(n_tiles, n_kv, n_splits);
     auto run = [&](auto kernel) -> int {
         cudaError_t e = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
         if (e != cudaSuccess) return fail("attention_tc: shared memory %zu: %s", smem, cudaGetErrorString(e));
         // ask for the largest shared-memory carve-out so that two blocks fit on an SM
         cudaFuncSetAttribute(kernel, cudaFuncAttributePreferredSharedMemoryCarveout, (int)cudaSharedmemCarveoutMaxShared);
-        launch_kernel(kernel, grid, ATC_THREADS, smem, st, mk, mv, p);
-        return check_launch("attention_tc");
+        if (!cluster_merge) {
+            launch_kernel(kernel, grid, ATC_THREADS, smem, st, mk, mv, p);
+            return check_launch("attention_tc");
+        }
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = grid;
+        cfg.blockDim = dim3(ATC_THREADS);
+        cfg.dynamicSmemBytes = smem;
+        cfg.stream = st;
+        cudaLaunchAttribute attrs[2];
+        attrs[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attrs[0].val.programmaticStreamSerializationAllowed = pdl_enabled() ? 1 : 0;
+        attrs[1].id = cudaLaunchAttributeClusterDimension;
+        attrs[1].val.clusterDim.x = 1; attrs[1].val.clusterDim.y = 1; attrs[1].val.clusterDim.z = (unsigned)n_splits;
+        cfg.attrs = attrs; cfg.numAttrs = 2;
+        cudaLaunchKernelEx(&cfg, kernel, mk, mv, p);
+        return check_launch("attention_tc (cluster)");
     };
     int rc;
     if (D == 128) rc = mode == 1 ? run(attention_tc_kernel<2, true>) : run(attention_tc_kernel<2, false>);
     else rc = mode == 1 ? run(attention_tc_kernel<1, true>) : run(attention_tc_kernel<1, false>);
     if (rc) return rc;
-    if (n_splits > 1) {
+    if (n_splits > 1 && !cluster_merge) {
         launch_kernel(attention_tc_combine_kernel, (unsigned)((size_t)n_tiles * n_heads), D, (size_t)(n_splits + 1) * sizeof(float), st,
                       (const float*)part_o,
                       (const float*)part_ml, (__nv_bfloat16*)out, tiles, n_heads, n_splits, D);

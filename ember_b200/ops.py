@@ -223,7 +223,7 @@ def attention(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, out: 
         raise KernelError(f"attention: pools {tuple(k_pool.shape)} are not [pages, {n_kv}, {page}, {head_dim}]")
     if q.numel() < T * n_heads * head_dim or out.numel() < T * n_heads * head_dim:
         raise KernelError("attention: q/out too small for the step")
-    if n_splits > 1:
+    if n_splits > 1 and (part_o is not None or part_ml is not None or n_splits > ATTENTION_CLUSTER_SPLITS):
         _check(part_o, "part_o", torch.float32)
         _check(part_ml, "part_ml", torch.float32)
         if part_o.numel() < T * n_heads * n_splits * head_dim or part_ml.numel() < T * n_heads * n_splits * 2:
@@ -434,6 +434,9 @@ def attention_tc_supported(head_dim: int, group: int, page_tokens: int, mode: in
     return group <= 16 if mode == 1 else group <= 64
 
 
+ATTENTION_CLUSTER_SPLITS = 8     # key splits of a decode tile that one thread-block cluster can merge
+
+
 def attention_tc_tile_queries(group: int) -> int:
     return 64 // group if 1 <= group <= 64 else 0
 
@@ -475,7 +478,9 @@ def attention_tc(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, ou
                  part_o: Optional[torch.Tensor] = None, part_ml: Optional[torch.Tensor] = None,
                  err: Optional[torch.Tensor] = None, stream: Optional[int] = None) -> None:
     """bf16 attention over the paged cache on tensor cores (TMA-fed).  ``mode`` 0 takes tiles of
-    prompt portions, 1 takes single-token tiles and may split their key range."""
+    prompt portions, 1 takes single-token tiles and may split their key range: with ``part_o`` / ``part_ml`` the
+    splits' partial results go through those buffers and a second kernel merges them; without them (at most 8
+    splits) the splits of a tile are a thread-block cluster and are merged in shared memory."""
     _check(q, "q", torch.bfloat16)
     _check(out, "out", torch.bfloat16)
     _check(k_pool, "k_pool", torch.bfloat16)
@@ -484,7 +489,7 @@ def attention_tc(q: torch.Tensor, k_pool: torch.Tensor, v_pool: torch.Tensor, ou
     _check(block_table, "block_table", torch.int32)
     if k_pool.dim() != 4 or tuple(k_pool.shape[1:]) != (n_kv, page, head_dim) or v_pool.shape != k_pool.shape:
         raise KernelError(f"attention: pools {tuple(k_pool.shape)} are not [pages, {n_kv}, {page}, {head_dim}]")
-    if n_splits > 1:
+    if n_splits > 1 and (part_o is not None or part_ml is not None or n_splits > ATTENTION_CLUSTER_SPLITS):
         _check(part_o, "part_o", torch.float32)
         _check(part_ml, "part_ml", torch.float32)
         if part_o.numel() < n_tiles * n_heads * n_splits * head_dim or part_ml.numel() < n_tiles * n_heads * n_splits * 2:

@@ -116,6 +116,9 @@ class Attention(Mixer):
         self.o(ctx, att, residual, T, ops.EPI_ADD_F32)
 
     FUSE_QKV = True     # prompt portions: finish the heads in the epilogue of the q/k/v product
+    CLUSTER_MERGE = True            # tests switch it off to compare with the merge kernel
+    MERGE_KERNEL_US = 3.0           # what the merge kernel costs a decode step per layer beyond the attention kernel
+    CACHE_BYTES_PER_US = 6.4e6      # the rate at which the decode kernel streams the cache when the SMs are full
 
     def _tc_modes(self):
         """(prompt portions, single tokens): whether the tensor-core kernels take this geometry."""
@@ -171,18 +174,33 @@ class Attention(Mixer):
                 # layer with 1 / 2 / 4 splits: 64 requests 122 / 130 / 134, 24 requests 52 / 60 / 58, 16 requests
                 # 40 / 37 / 41, 8 requests - / 22.6 / 22.5, one request 19 (2) / 12.8 (4) / 10.1 (8).  Splits are
                 # anchored at key 0, so with a window the early ones are empty.
+                # Up to 8 splits of a tile can be a thread-block cluster that merges in shared memory; more go
+                # through buffers and the merge kernel, which costs a step about MERGE_KERNEL_US a layer (batch 8,
+                # 3 splits: 1.895 -> 1.805 ms a step; one request at 3,072: 12 splits through buffers 1.351 ms, 8 in a
+                # cluster 1.305 ms; at 32,768 the 16 splits through buffers win, 28.5 against 42.9 us a layer).
                 live = ctx.max_context if s.window <= 0 else min(ctx.max_context, s.window + 64)
                 sms = ops.num_sms(q.device)
                 blocks = n * s.num_kv_heads
-                live_splits, best = 1, None
-                for cand in range(1, max(1, min(16, (live + 255) // 256)) + 1):
-                    cost = max(1.0, sms / float(blocks * cand)) * (1.0 + 0.04 * (cand - 1))
-                    if best is None or cost < best - 1e-9:
-                        live_splits, best = cand, cost
+                stream_us = n * live * s.num_kv_heads * s.head_dim * 4 / self.CACHE_BYTES_PER_US      # keys and values, bf16
+
+                def plan(most):
+                    splits, best = 1, None
+                    for cand in range(1, max(1, min(most, (live + 255) // 256)) + 1):
+                        cost = max(1.0, sms / float(blocks * cand)) * (1.0 + 0.04 * (cand - 1))
+                        if best is None or cost < best - 1e-9:
+                            splits, best = cand, cost
+                    return splits, best * stream_us
+
+                live_splits, est = plan(16)
+                in_cluster = False
+                if self.CLUSTER_MERGE and ctx.max_context <= live:          # (with a window the early splits are empty: too many)
+                    c_splits, c_est = plan(ops.ATTENTION_CLUSTER_SPLITS)
+                    if c_est <= est + self.MERGE_KERNEL_US:
+                        live_splits, in_cluster = c_splits, True
                 split_keys = ((live + live_splits - 1) // live_splits + 63) // 64 * 64
                 n_splits = (ctx.max_context + split_keys - 1) // split_keys
                 part_o = part_ml = None
-                if n_splits > 1:
+                if n_splits > 1 and not (in_cluster and n_splits <= ops.ATTENTION_CLUSTER_SPLITS):
                     part_o = ctx.buf_dyn("attention.part_o", n * s.num_heads * n_splits * s.head_dim, torch.float32)
                     part_ml = ctx.buf_dyn("attention.part_ml", n * s.num_heads * n_splits * 2, torch.float32)
                 ops.attention_tc(q, cache.k, cache.v, out, 1, *args, tiles, n, table, cache.page_tokens, s.window,

@@ -284,9 +284,11 @@ def test_attention_general(heads, kv, D, page, dt, window):
         single = torch.from_numpy(attention_tiles(batch, 1, "single")).to(dev)
         ops.attention_tc(q_all.view(T, -1), kp.to(dev), vp.to(dev), out, 0, heads, kv, D, multi, multi.shape[0],
                          perm.to(dev), page, window, scale, err=err)
-        for n_splits, split_keys in ((1, 0), (4, 192), (11, 64)):
-            po = torch.empty(single.shape[0] * heads * n_splits * D, device=dev)
-            pml = torch.empty(single.shape[0] * heads * n_splits * 2, device=dev)
+        # splits merged by a second kernel through buffers, or (no buffers, at most 8) inside a cluster
+        for n_splits, split_keys, buffers in ((1, 0, True), (4, 192, True), (11, 64, True), (4, 192, False), (8, 128, False),
+                                              (3, 320, False)):
+            po = torch.empty(single.shape[0] * heads * n_splits * D, device=dev) if buffers else None
+            pml = torch.empty(single.shape[0] * heads * n_splits * 2, device=dev) if buffers else None
             out[-2:] = 0
             ops.attention_tc(q_all.view(T, -1), kp.to(dev), vp.to(dev), out, 1, heads, kv, D, single, single.shape[0],
                              perm.to(dev), page, window, scale, n_splits, split_keys, po, pml, err=err)
@@ -365,10 +367,10 @@ def test_attention_long_context(page):
     ops.attention_fa(q_all.view(T, -1), kd, vd, out, heads, kv, D, multi, multi.shape[0], pd, page, 0, scale, err=err)
     single = torch.from_numpy(attention_tiles(batch, 1, "single")).to(dev)
     longest = max(ctx_lens)
-    for n_splits in (16, 1):
+    for n_splits, buffers in ((16, True), (1, True), (8, False), (5, False)):
         split_keys = ((longest + n_splits - 1) // n_splits + 63) // 64 * 64 if n_splits > 1 else 0
-        po = torch.empty(single.shape[0] * heads * n_splits * D, device=dev)
-        pml = torch.empty(single.shape[0] * heads * n_splits * 2, device=dev)
+        po = torch.empty(single.shape[0] * heads * n_splits * D, device=dev) if buffers else None
+        pml = torch.empty(single.shape[0] * heads * n_splits * 2, device=dev) if buffers else None
         out[-2:] = 0
         ops.attention_tc(q_all.view(T, -1), kd, vd, out, 1, heads, kv, D, single, single.shape[0], pd, page, 0, scale,
                          n_splits, split_keys, po, pml, err=err)
