@@ -22,6 +22,39 @@ from .linear import Linear
 from .registry import build_part, register_part
 
 
+def plan_decode_splits(n_tokens: int, max_context: int, window: int, num_kv_heads: int, head_dim: int, sms: int,
+                       cluster_splits: int, merge_kernel_us: float, cache_bytes_per_us: float):
+    """How the key ranges of a decode step's single-token tiles are cut: ``(n_splits, split_keys, in_cluster)``.
+
+    Splits are fixed ranges of ``split_keys`` keys (a multiple of 64) anchored at key 0 that cover ``max_context``;
+    the number of *live* ones (those a window leaves non-empty) is chosen by a model of the kernel's time: the bytes
+    of cache over the device's rate, stretched by idle SMs (blocks = tokens x key heads x splits against ``sms``)
+    and by 4 % per further split.  ``in_cluster``: the splits of a tile are a thread-block cluster that merges in
+    shared memory (at most ``cluster_splits``; 0 forbids it), chosen when the best such plan is estimated no slower
+    than the best plan of up to 16 splits plus what the merge kernel costs."""
+    live = max_context if window <= 0 else min(max_context, window + 64)
+    blocks = max(1, n_tokens * num_kv_heads)
+    stream_us = n_tokens * live * num_kv_heads * head_dim * 4 / cache_bytes_per_us         # keys and values, bf16
+
+    def plan(most):
+        splits, best = 1, None
+        for cand in range(1, max(1, min(most, (live + 255) // 256)) + 1):
+            cost = max(1.0, sms / float(blocks * cand)) * (1.0 + 0.04 * (cand - 1))
+            if best is None or cost < best - 1e-9:
+                splits, best = cand, cost
+        return splits, best * stream_us
+
+    live_splits, est = plan(16)
+    in_cluster = False
+    if cluster_splits > 1 and max_context <= live:          # (with a window the early splits are empty: too many)
+        c_splits, c_est = plan(cluster_splits)
+        if c_est <= est + merge_kernel_us:
+            live_splits, in_cluster = c_splits, True
+    split_keys = ((live + live_splits - 1) // live_splits + 63) // 64 * 64
+    n_splits = (max_context + split_keys - 1) // split_keys
+    return n_splits, split_keys, in_cluster and 1 < n_splits <= cluster_splits
+
+
 class Attention(Mixer):
     graph_safe = True
 
@@ -178,29 +211,11 @@ class Attention(Mixer):
                 # through buffers and the merge kernel, which costs a step about MERGE_KERNEL_US a layer (batch 8,
                 # 3 splits: 1.895 -> 1.805 ms a step; one request at 3,072: 12 splits through buffers 1.351 ms, 8 in a
                 # cluster 1.305 ms; at 32,768 the 16 splits through buffers win, 28.5 against 42.9 us a layer).
-                live = ctx.max_context if s.window <= 0 else min(ctx.max_context, s.window + 64)
-                sms = ops.num_sms(q.device)
-                blocks = n * s.num_kv_heads
-                stream_us = n * live * s.num_kv_heads * s.head_dim * 4 / self.CACHE_BYTES_PER_US      # keys and values, bf16
-
-                def plan(most):
-                    splits, best = 1, None
-                    for cand in range(1, max(1, min(most, (live + 255) // 256)) + 1):
-                        cost = max(1.0, sms / float(blocks * cand)) * (1.0 + 0.04 * (cand - 1))
-                        if best is None or cost < best - 1e-9:
-                            splits, best = cand, cost
-                    return splits, best * stream_us
-
-                live_splits, est = plan(16)
-                in_cluster = False
-                if self.CLUSTER_MERGE and ctx.max_context <= live:          # (with a window the early splits are empty: too many)
-                    c_splits, c_est = plan(ops.ATTENTION_CLUSTER_SPLITS)
-                    if c_est <= est + self.MERGE_KERNEL_US:
-                        live_splits, in_cluster = c_splits, True
-                split_keys = ((live + live_splits - 1) // live_splits + 63) // 64 * 64
-                n_splits = (ctx.max_context + split_keys - 1) // split_keys
+                n_splits, split_keys, in_cluster = plan_decode_splits(
+                    n, ctx.max_context, s.window, s.num_kv_heads, s.head_dim, ops.num_sms(q.device),
+                    ops.ATTENTION_CLUSTER_SPLITS if self.CLUSTER_MERGE else 0, self.MERGE_KERNEL_US, self.CACHE_BYTES_PER_US)
                 part_o = part_ml = None
-                if n_splits > 1 and not (in_cluster and n_splits <= ops.ATTENTION_CLUSTER_SPLITS):
+                if n_splits > 1 and not in_cluster:
                     part_o = ctx.buf_dyn("attention.part_o", n * s.num_heads * n_splits * s.head_dim, torch.float32)
                     part_ml = ctx.buf_dyn("attention.part_ml", n * s.num_heads * n_splits * 2, torch.float32)
                 ops.attention_tc(q, cache.k, cache.v, out, 1, *args, tiles, n, table, cache.page_tokens, s.window,

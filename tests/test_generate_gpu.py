@@ -307,3 +307,41 @@ def test_bfloat16_logits_alone_and_in_a_batch_of_ten(tiny_model_dirs):
     assert max(rel(alone[i], want[20 + i]) for i in range(20)) < 2.5e-2
     assert max(rel(together[i], want[20 + i]) for i in range(20)) < 2.5e-2
     assert max(rel(together[i], alone[i]) for i in range(20)) < 2.5e-2
+
+
+@pytest.mark.parametrize("name", ["c", "d"])
+def test_decode_key_splits_merged_in_a_cluster_or_by_the_merge_kernel(name, tiny_model_dirs, monkeypatch):
+    """Single tokens after 300 to 500 keys: the planner cuts the keys in two.  Whether the two blocks of a tile
+    merge in shared memory as a cluster or through buffers and the merge kernel, the logits follow the plain
+    implementation and differ from each other by the merge's rounding only."""
+    from ember_b200 import StepEntry
+    from ember_b200.parts.attention import Attention
+    plain = PlainQwen3(tiny_model_dirs[name], torch.float64)
+    rng = np.random.default_rng(77)
+    vocab = TINY[name]["json"]["vocab_size"]
+    seqs = [rng.integers(0, vocab, size=n).tolist() for n in (330, 470, 505)]
+    want = [plain.logits(s).numpy() for s in seqs]
+
+    def decode(in_cluster):
+        monkeypatch.setattr(Attention, "CLUSTER_MERGE", in_cluster)
+        llm = load(tiny_model_dirs, name, "bfloat16", max_seqs=4, kv_cache_tokens=2048, max_batch_tokens=2048)
+        r = llm.runner
+        for i, s in enumerate(seqs):
+            r.admit(i), r.reserve(i, len(s) - 6)
+        r.step([StepEntry(i, s[:-6], ()) for i, s in enumerate(seqs)])
+        rows = []
+        for t in range(6, 0, -1):
+            for i in range(len(seqs)):
+                assert r.reserve(i, 1)
+            lg = r.step([StepEntry(i, [s[-t]], (0,)) for i, s in enumerate(seqs)])
+            rows.append(lg.float().cpu().numpy().copy())
+        r.check_device()
+        return np.stack(rows)                      # [6 steps, 3 requests, vocab]
+
+    a, b = decode(True), decode(False)
+    rel = lambda x, y: float(np.linalg.norm(x - y) / np.linalg.norm(y))          # noqa: E731
+    for step in range(6):
+        for i, s in enumerate(seqs):
+            ref = want[i][len(s) - 6 + step]
+            assert rel(a[step, i], ref) < 2.5e-2 and rel(b[step, i], ref) < 2.5e-2
+            assert rel(a[step, i], b[step, i]) < 5e-3

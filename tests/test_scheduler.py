@@ -255,3 +255,23 @@ def test_kernel_error_word_fails_the_running_requests():
         assert runner.resets_after_error == 1 and runner.err_code == 0
         assert runner.cache.check() == "" and runner.cache.used_pages() == [0]
         assert eng.generate([3, 1, 4], max_tokens=5, ignore_eos=True) == expected_generation([3, 1, 4], 5, 977)
+
+
+def test_decode_split_planner_covers_the_context_and_keeps_clusters_small():
+    """The decode attention's split plan (a pure function of the step's sizes): the splits cover the context in
+    multiples of 64 keys, a cluster never has more blocks than it may, a full device is not split, one request with
+    a few thousand keys merges in a cluster and one with 32,768 goes through the buffers."""
+    from ember_b200.parts.attention import plan_decode_splits
+    for n in (1, 2, 3, 8, 17, 64, 200):
+        for ctx in (1, 63, 64, 65, 300, 1024, 3072, 3200, 8192, 32768, 100000):
+            for window in (0, 128, 4096):
+                for cl in (0, 8):
+                    ns, sk, inc = plan_decode_splits(n, ctx, window, 8, 128, 148, cl, 3.0, 6.4e6)
+                    assert ns >= 1 and sk % 64 == 0 and ns * sk >= ctx and (ns - 1) * sk < ctx
+                    assert not inc or (cl and 1 < ns <= cl)
+                    assert cl or not inc
+    assert plan_decode_splits(64, 3072, 0, 8, 128, 148, 8, 3.0, 6.4e6)[0] == 1
+    assert plan_decode_splits(1, 3072, 0, 8, 128, 148, 8, 3.0, 6.4e6) == (8, 384, True)
+    ns, sk, inc = plan_decode_splits(1, 32768, 0, 8, 128, 148, 8, 3.0, 6.4e6)
+    assert ns == 16 and not inc
+    assert plan_decode_splits(8, 3072, 0, 8, 128, 148, 8, 3.0, 6.4e6)[2]
