@@ -600,11 +600,66 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap map_rows, const __grid_consta
                     }
                 }
             }
-        } else if (ok) {
+        } else {
             const int r = quad * 32 + lane;         // accumulator row of this thread
             const uint32_t taddr_row = tmem_d + ((uint32_t)(quad * 32) << 16);
             const bool splitk = gridDim.z > 1;
-            for (int c0 = 0; c0 < p.block_cols; c0 += 16) {
+            // Swapped orientation, K not cut, more than 16 tokens: a thread holds one weight row, so a token's outputs
+            // from this tile are spread over the block's threads and stored one by one they are 2-byte stores 32 bytes
+            // a warp (at 128 tokens that was 14 of the 8B gate/up's 54 us).  The tile is turned in shared memory instead
+            // (the stages are free: every MMA has finished) and goes out as whole 16-byte pieces of token rows.
+            const int elt = p.epilogue == 1 ? 4 : 2;
+            const int out_cols = p.epilogue == 3 ? TILE_ROWS / 2 : TILE_ROWS;       // outputs a token gets from this tile
+            const int row_bytes = out_cols * elt;
+            const bool turned = p.swapped && !splitk && p.epilogue != 2 && p.block_cols > 16 &&
+                                (row_tile + 1) * TILE_ROWS <= p.N &&
+                                (size_t)p.block_cols * row_bytes <= (size_t)p.stages * stage_bytes &&
+                                (reinterpret_cast<uintptr_t>(p.out) & 15) == 0 && ((size_t)p.ldc * elt) % 16 == 0;
+            // (the turned tile has a barrier of the four epilogue warps in it: they go through it together or not at
+            // all, whatever each of them saw of a wait that ran out)
+            bool go = ok;
+            if (turned) {
+                uint32_t all;
+                asm volatile(
+                    "{\n.reg .pred p, q;\n"
+                    "setp.ne.u32 p, %1, 0;\n"
+                    "bar.red.and.pred q, 1, 128, p;\n"
+                    "selp.u32 %0, 1, 0, q;\n}"
+                    : "=r"(all) : "r"((uint32_t)ok) : "memory");
+                go = all != 0;
+            }
+            if (turned && go) {
+                uint8_t* turn = smem;                // [token][outputs of this tile]
+                auto put = [&](int c, float x) {     // this thread's weight row, token column c
+                    uint8_t* row = turn + (size_t)c * row_bytes;
+                    if (p.epilogue == 3) {
+                        const float other = __shfl_xor_sync(0xffffffffu, x, 1);             // gate rows are even, up rows odd
+                        if ((lane & 1) == 0) reinterpret_cast<__nv_bfloat16*>(row)[r >> 1] = __float2bfloat16_rn(silu_mul(x, other));
+                    } else if (p.epilogue == 0) {
+                        reinterpret_cast<__nv_bfloat16*>(row)[r] = __float2bfloat16_rn(x);
+                    } else {
+                        reinterpret_cast<float*>(row)[r] = x;
+                    }
+                };
+                // (64 columns a round trip to tensor memory, as the prefill epilogues read, gained nothing here)
+                for (int c0 = 0; c0 < p.block_cols; c0 += 16) {
+                    float v[16];
+                    tmem_ld16(taddr_row + (uint32_t)c0, v);
+#pragma unroll
+                    for (int j = 0; j < 16; j++) put(c0 + j, v[j]);
+                }
+                asm volatile("bar.sync 1, 128;" ::: "memory");      // the four epilogue warps
+                const int m0 = col_tile * p.block_cols;
+                const int tokens = min(p.block_cols, p.M - m0);
+                const int pieces = row_bytes >> 4;
+                uint8_t* out0 = reinterpret_cast<uint8_t*>(p.out) + (size_t)(row_tile * out_cols) * elt;
+                for (int idx = (int)threadIdx.x - 64; idx < tokens * pieces; idx += GEMM_THREADS - 64) {
+                    const int c = idx / pieces, o = idx - c * pieces;
+                    *reinterpret_cast<uint4*>(out0 + (size_t)(m0 + c) * p.ldc * elt + (size_t)o * 16) =
+                        *reinterpret_cast<const uint4*>(turn + (size_t)c * row_bytes + (size_t)o * 16);
+                }
+            }
+            for (int c0 = (turned || !go) ? p.block_cols : 0; c0 < p.block_cols; c0 += 16) {
                 float v[16];
                 tmem_ld16(taddr_row + (uint32_t)c0, v);
                 if (!p.swapped) {

@@ -51,6 +51,29 @@ def test_gemm_tc(M, N, K, epilogue, split_mode):
         assert float(ops._tc_scratch[a.device].abs().max()) == 0.0
 
 
+@pytest.mark.parametrize("M,N,K", [(17, 2048, 264), (64, 2048, 2048), (128, 24576, 128), (100, 640, 264), (33, 1000, 72),
+                                   (128, 1160, 136), (70, 20000, 64)])
+@pytest.mark.parametrize("epilogue", [0, 1, 3])
+def test_gemm_tc_whole_k_more_than_16_tokens(M, N, K, epilogue):
+    """17 to 128 tokens with K in one part (forced with split_mode 17, and what the planner picks for a matrix of
+    more tiles than SMs): the block turns its tile in shared memory and stores whole pieces of token rows.  1,000
+    and 1,160 weight rows end inside a tile (that tile is stored element by element), 1,000 outputs a row are
+    no multiple of 16 bytes for the gated epilogue."""
+    from ember_b200 import ops
+    torch.manual_seed(M + N + K + epilogue)
+    a = (torch.randn(M, K, device="cuda") * 0.5).bfloat16()
+    w = (torch.randn(N, K, device="cuda") * 0.5).bfloat16()
+    n_out = N // 2 if epilogue == 3 else N
+    want = ref_epilogue(a.float() @ w.float().t(), epilogue)
+    for mode in (17, 0):
+        out = torch.full((M + 1, n_out), 7.0, device="cuda", dtype=torch.float32 if epilogue == 1 else torch.bfloat16)
+        err = torch.zeros(1, dtype=torch.int32, device="cuda")
+        ops.gemm_tc(a, w, out, M, epilogue, err=err, split_mode=mode)
+        assert int(err.item()) == 0
+        assert rel(out[:M].float(), want) < (5e-3 if epilogue in (0, 3) else 1e-5)
+        assert float((out[M].float() - 7.0).abs().max()) == 0.0          # the row after the step's tokens is not touched
+
+
 @pytest.mark.parametrize("cols", [64, 208, 240])
 @pytest.mark.parametrize("split_mode", [4, 5])
 def test_gemm_tc_tile_widths(cols, split_mode, monkeypatch):
