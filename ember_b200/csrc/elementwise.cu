@@ -245,10 +245,13 @@ __device__ __forceinline__ void store8<__nv_bfloat16>(__nv_bfloat16* p, const fl
 
 constexpr int ROPE128_WARPS = 4;
 
-template <typename T>
+// TI: what the projection is read as; T: queries and cache.  CLEAR (TI float only): the rows are the fp32 sums a
+// product with a cut K range left in its zeroed scratch; every element is read once and set back to zero here,
+// which stands in for that product's own pass that would round the sums, store them and clear the scratch.
+template <typename TI, typename T, bool CLEAR>
 __global__ void __launch_bounds__(ROPE128_WARPS * 32)
 qk_norm_rope_store_d128_kernel(
-    const T* __restrict__ qkv, int ld, int n_heads, int n_kv,
+    TI* __restrict__ qkv, int ld, int n_heads, int n_kv,
     const float* __restrict__ q_norm_w, const float* __restrict__ k_norm_w, float eps,
     const float* __restrict__ inv_freq, int rotate,
     const int* __restrict__ positions, const int* __restrict__ seq_of,
@@ -290,7 +293,7 @@ qk_norm_rope_store_d128_kernel(
     // where this token's keys and values go: page blk, place pos % page (per key head: + kvh * page * D)
     const size_t kv_base = blk >= 0 ? ((size_t)blk * n_kv * page + (size_t)(pos % page)) * D + e0 : 0;
     const size_t kv_head = (size_t)page * D;
-    const T* src_row = qkv + (size_t)t * ld + e0;
+    TI* src_row = qkv + (size_t)t * ld + e0;
     T* q_row = q_out + (size_t)t * n_heads * D + e0;
     const bool kv_ok = write_kv && blk >= 0;
     // a warp takes two heads per turn; blockIdx.y splits the heads between blocks when a step has few tokens
@@ -299,8 +302,12 @@ qk_norm_rope_store_d128_kernel(
         const int kind = slot < n_heads ? 0 : (slot < n_heads + n_kv ? 1 : 2);  // q, k, v
         const bool act = slot < slots && (kind == 0 || kv_ok);
         float x[8];
-        if (act) {
-            load8<T>(src_row + (size_t)slot * D, x);
+        if (act || (CLEAR && slot < slots)) {
+            load8<TI>(src_row + (size_t)slot * D, x);
+            if constexpr (CLEAR) {              // (the only instance that writes to its input)
+                const float zero[8] = {0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f, 0.0f};
+                store8<TI>(src_row + (size_t)slot * D, zero);
+            }
         } else {
 #pragma unroll
             for (int j = 0; j < 8; j++) x[j] = 0.0f;
@@ -479,12 +486,12 @@ EMBER_API int ember_qk_norm_rope_store(const void* qkv, int dtype, int T, int ld
         if (gy < 1) gy = 1;
         dim3 g128(T, gy);
         if (dtype == EMBER_F32)
-            launch_kernel(qk_norm_rope_store_d128_kernel<float>, g128, ROPE128_WARPS * 32, 0, st,
-                (const float*)qkv, ld, n_heads, n_kv, q_norm_w, k_norm_w, eps, inv_freq, rotate ? 1 : 0, positions, seq_of,
+            launch_kernel(qk_norm_rope_store_d128_kernel<float, float, false>, g128, ROPE128_WARPS * 32, 0, st,
+                (float*)const_cast<void*>(qkv), ld, n_heads, n_kv, q_norm_w, k_norm_w, eps, inv_freq, rotate ? 1 : 0, positions, seq_of,
                 block_table, max_blocks, page, num_pages, (float*)q_out, (float*)k_pool, (float*)v_pool, write_kv, err);
         else
-            launch_kernel(qk_norm_rope_store_d128_kernel<__nv_bfloat16>, g128, ROPE128_WARPS * 32, 0, st,
-                (const __nv_bfloat16*)qkv, ld, n_heads, n_kv, q_norm_w, k_norm_w, eps, inv_freq, rotate ? 1 : 0, positions,
+            launch_kernel(qk_norm_rope_store_d128_kernel<__nv_bfloat16, __nv_bfloat16, false>, g128, ROPE128_WARPS * 32, 0, st,
+                (__nv_bfloat16*)const_cast<void*>(qkv), ld, n_heads, n_kv, q_norm_w, k_norm_w, eps, inv_freq, rotate ? 1 : 0, positions,
                 seq_of, block_table, max_blocks, page, num_pages, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool,
                 (__nv_bfloat16*)v_pool, write_kv, err);
         return check_launch("qk_norm_rope_store");
@@ -501,6 +508,35 @@ EMBER_API int ember_qk_norm_rope_store(const void* qkv, int dtype, int T, int ld
     else
         return fail("qk_norm_rope_store: unsupported dtype %d", dtype);
     return check_launch("qk_norm_rope_store");
+}
+
+// The same on the fp32 sums of a q/k/v product (rows of `ld` floats, heads of 128, queries and cache bf16): the
+// sums are read and set back to zero.  1 / 0 from the first function: whether this geometry is taken.
+EMBER_API int ember_qk_norm_rope_store_sums_supported(int D, int rotary, int ld) {
+    return D == 128 && (rotary == 0 || rotary == 128) && ld % 8 == 0;
+}
+EMBER_API int ember_qk_norm_rope_store_sums(float* sums, int T, int ld, int n_heads, int n_kv,
+                                            const float* q_norm_w, const float* k_norm_w, float eps,
+                                            const float* inv_freq, int rotary, const int* positions, const int* seq_of,
+                                            const int* block_table, int max_blocks, int page, int num_pages,
+                                            void* q_out, void* k_pool, void* v_pool, int write_kv, int* err, void* stream) {
+    if (T <= 0) return 0;
+    const bool rotate = inv_freq != nullptr && rotary > 0;
+    if (!ember_qk_norm_rope_store_sums_supported(128, rotate ? rotary : 0, ld) || n_heads <= 0 || n_kv <= 0 ||
+        ld < (n_heads + 2 * n_kv) * 128)
+        return fail("qk_norm_rope_store_sums: %d/%d heads of 128 in rows of %d floats, rotation %d are not taken", n_heads, n_kv, ld, rotary);
+    if (page <= 0 || max_blocks <= 0 || num_pages <= 0) return fail("qk_norm_rope_store_sums: bad cache geometry");
+    if (((uintptr_t)sums | (uintptr_t)q_out | (uintptr_t)k_pool | (uintptr_t)v_pool | (uintptr_t)q_norm_w | (uintptr_t)k_norm_w) & 15)
+        return fail("qk_norm_rope_store_sums: operands must be 16-byte aligned");
+    const int slots = n_heads + 2 * n_kv;
+    int gy = (592 + T - 1) / T;
+    const int gy_max = (slots + 2 * ROPE128_WARPS - 1) / (2 * ROPE128_WARPS);
+    if (gy > gy_max) gy = gy_max;
+    if (gy < 1) gy = 1;
+    launch_kernel(qk_norm_rope_store_d128_kernel<float, __nv_bfloat16, true>, dim3(T, gy), ROPE128_WARPS * 32, 0, (cudaStream_t)stream,
+        sums, ld, n_heads, n_kv, q_norm_w, k_norm_w, eps, inv_freq, rotate ? 1 : 0, positions, seq_of,
+        block_table, max_blocks, page, num_pages, (__nv_bfloat16*)q_out, (__nv_bfloat16*)k_pool, (__nv_bfloat16*)v_pool, write_kv, err);
+    return check_launch("qk_norm_rope_store_sums");
 }
 
 EMBER_API int ember_rope_table(const int* positions, const float* inv_freq, int T, int half, int ld, void* out, void* stream) {

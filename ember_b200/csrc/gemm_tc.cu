@@ -221,6 +221,7 @@ EMBER_API int ember_gemm_tc_supported(int M, int N, int K, int epilogue) {
     if (M <= 0 || N <= 0 || K <= 0) return 0;
     if (K % 8) return 0;                       // TMA needs 16-byte row pitch
     if (epilogue == 3 && (N & 1)) return 0;
+    if (epilogue == 5 && M > 128) return 0;    // the sums stay in the scratch of the small-M product
     return 1;
 }
 
@@ -231,9 +232,17 @@ EMBER_API long long ember_gemm_tc_scratch_floats(int max_tokens_swapped, int N) 
 
 // C = A . W^T with the fused epilogue.  `scratch` is a zero-filled fp32 buffer of at least
 // min(M, 128) * N floats (used only when the K range is split; it is left zeroed).
+// Epilogue 5 (at most 128 tokens): the fp32 sums are left in `scratch` as [M, N] for a consumer that reads them and
+// sets them back to zero (`out` is not used); it saves the pass that rounds, stores and clears.
 EMBER_API int ember_gemm_tc(const void* A, const void* W, void* out, int ldc, int M, int N, int K, int epilogue,
                             float* scratch, long long scratch_floats, int num_sms, int split_mode, int* err, void* stream) {
     if (M <= 0 || N <= 0) return 0;
+    const bool sums = epilogue == 5;
+    if (sums) {
+        if (M > 128 || !scratch || scratch_floats < (long long)M * N)
+            return fail("gemm_tc: sums in scratch need at most 128 tokens and %lld floats of scratch, got M=%d and %lld", (long long)M * N, M, scratch_floats);
+        out = scratch; ldc = N; epilogue = 1;          // with K in one part the sums are stored like any fp32 result
+    }
     if (!ember_gemm_tc_supported(M, N, K, epilogue))
         return fail("gemm_tc: sizes M=%d N=%d K=%d (epilogue %d) are not taken; K must be a multiple of 8", M, N, K, epilogue);
     if ((((uintptr_t)A) & 15) || (((uintptr_t)W) & 15)) return fail("gemm_tc: operands must be 16-byte aligned");
@@ -396,7 +405,7 @@ EMBER_API int ember_gemm_tc(const void* A, const void* W, void* out, int ldc, in
     cudaLaunchKernelEx(&cfg, gemm_tc_kernel, map_rows, map_cols, p);
     int rc = check_launch("gemm_tc");
     if (rc) return rc;
-    if (splits > 1 && p.cluster_splits <= 1 && epilogue != 2) {
+    if (splits > 1 && p.cluster_splits <= 1 && epilogue != 2 && !sums) {
         const int n_out = epilogue == 3 ? N / 2 : N;
         const size_t total = (size_t)M * n_out;
         const bool by4 = n_out % 4 == 0 && ldc % 4 == 0 && p.accum_ld % 4 == 0 && ((((uintptr_t)p.accum) | ((uintptr_t)out)) & 15) == 0;

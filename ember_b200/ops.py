@@ -16,6 +16,7 @@ from .csrc import build
 
 F32, BF16 = 0, 1
 EPI_STORE, EPI_STORE_F32, EPI_ADD_F32, EPI_SILU_MUL = 0, 1, 2, 3
+EPI_SUMS = 5      # tensor-core product of at most 128 tokens: the fp32 sums stay in the split-K scratch
 
 
 class KernelError(RuntimeError):
@@ -147,6 +148,44 @@ def qk_norm_rope_store(qkv: torch.Tensor, T: int, n_heads: int, n_kv: int, head_
           c_int(rotary if inv_freq is not None else 0), _p(positions), _p(seq_of), _p(block_table),
           c_int(block_table.shape[-1]), c_int(page), c_int(k_pool.shape[0]), _p(q_out), _p(k_pool), _p(v_pool),
           c_int(1 if write_kv else 0), _p(err), c_void_p(stream if stream is not None else current_stream_ptr()))
+
+
+def qk_norm_rope_store_sums_usable(head_dim: int, rotary: int, width: int) -> bool:
+    """Whether the head kernel can take a product's fp32 sums (heads of 128 rotated whole or not at all)."""
+    return head_dim == 128 and rotary in (0, 128) and width % 8 == 0
+
+
+def qk_norm_rope_store_sums(sums: torch.Tensor, T: int, n_heads: int, n_kv: int, q_norm_w: Optional[torch.Tensor],
+                            k_norm_w: Optional[torch.Tensor], eps: float, inv_freq: Optional[torch.Tensor],
+                            positions: torch.Tensor, seq_of: torch.Tensor, block_table: torch.Tensor, page: int,
+                            k_pool: torch.Tensor, v_pool: torch.Tensor, q_out: torch.Tensor, write_kv: bool = True,
+                            err: Optional[torch.Tensor] = None, stream: Optional[int] = None) -> None:
+    """``qk_norm_rope_store`` on the fp32 sums [T, (n_heads + 2 n_kv) * 128] a product left in its scratch
+    (``gemm_tc`` with ``EPI_SUMS``): queries and cache are bf16, and every sum read is set back to zero."""
+    _check(sums, "sums", torch.float32)
+    _check(q_out, "q_out", torch.bfloat16)
+    _check(k_pool, "k_pool", torch.bfloat16)
+    _check(v_pool, "v_pool", torch.bfloat16)
+    _check(positions, "positions", torch.int32)
+    _check(seq_of, "seq_of", torch.int32)
+    _check(block_table, "block_table", torch.int32)
+    for w, n in ((q_norm_w, "q_norm_w"), (k_norm_w, "k_norm_w"), (inv_freq, "inv_freq")):
+        if w is not None:
+            _check(w, n, torch.float32)
+    if sums.dim() != 2 or sums.shape[0] < T or sums.shape[1] != (n_heads + 2 * n_kv) * 128:
+        raise KernelError(f"qk_norm_rope_store_sums: sums {tuple(sums.shape)} for {T} tokens and {n_heads}/{n_kv} heads of 128")
+    if k_pool.dim() != 4 or tuple(k_pool.shape[1:]) != (n_kv, page, 128) or v_pool.shape != k_pool.shape:
+        raise KernelError(f"qk_norm_rope_store_sums: pools {tuple(k_pool.shape)} are not [pages, {n_kv}, {page}, 128]")
+    if inv_freq is not None and inv_freq.numel() != 64:
+        raise KernelError(f"qk_norm_rope_store_sums: {inv_freq.numel()} frequencies for heads of 128")
+    if q_out.numel() < T * n_heads * 128 or positions.numel() < T or seq_of.numel() < T:
+        raise KernelError("qk_norm_rope_store_sums: query buffer or token arrays too small")
+    lib = _lib("elementwise")
+    _call(lib, lib.ember_qk_norm_rope_store_sums, _p(sums), c_int(T), c_int(sums.shape[1]), c_int(n_heads), c_int(n_kv),
+          _p(q_norm_w), _p(k_norm_w), c_float(eps), _p(inv_freq), c_int(128 if inv_freq is not None else 0), _p(positions),
+          _p(seq_of), _p(block_table), c_int(block_table.shape[-1]), c_int(page), c_int(k_pool.shape[0]), _p(q_out),
+          _p(k_pool), _p(v_pool), c_int(1 if write_kv else 0), _p(err),
+          c_void_p(stream if stream is not None else current_stream_ptr()))
 
 
 def wait_limit_probe(limit_ns: int, err: torch.Tensor, waited_ns: torch.Tensor, stream: Optional[int] = None) -> None:
@@ -322,16 +361,27 @@ def gemm_tc_usable(x: torch.Tensor, w: torch.Tensor, bias, epilogue: int) -> boo
 
 def gemm_tc(a: torch.Tensor, w: torch.Tensor, out: torch.Tensor, M: int, epilogue: int = EPI_STORE,
             err: Optional[torch.Tensor] = None, stream: Optional[int] = None, split_mode: int = 0) -> None:
-    """out (+)= a[:M] @ w.T on the tcgen05 tensor cores (bf16 in, fp32 accumulate).
+    """out (+)= a[:M] @ w.T on the tcgen05 tensor cores (bf16 in, fp32 accumulate).  With ``EPI_SUMS`` (``out`` None,
+    at most 128 tokens) the fp32 sums are left in the split-K scratch and returned as a view [M, N]: whoever reads
+    them sets them back to zero (``qk_norm_rope_store_sums``).
     ``split_mode``: how split-K partial sums are combined (0 automatic, 1 atomics, 2 cluster); 3 runs
     prefill-sized products one tile per block instead of persistently, 4 on pairs of SMs whenever the device
     takes them, 5 never on pairs (for tests and tuning)."""
     _check(a, "a", torch.bfloat16)
     _check(w, "w", torch.bfloat16)
-    _check(out, "out")
     N, K = w.shape
     if a.shape[-1] != K:
         raise KernelError(f"gemm: activations of width {a.shape[-1]} against weights {tuple(w.shape)}")
+    if epilogue == EPI_SUMS:
+        if out is not None or not 0 < M <= 128 or a.numel() < M * K:
+            raise KernelError(f"gemm: the sums of M={M} tokens stay in the scratch only for 1..128 tokens and without an output")
+        scratch = _scratch(a.device, M * N)
+        lib = _lib("gemm_tc")
+        _call(lib, lib.ember_gemm_tc, _p(a), _p(w), c_void_p(0), c_int(N), c_int(M), c_int(N), c_int(K), c_int(epilogue),
+              _p(scratch), c_longlong(scratch.numel()), c_int(_sms(a.device)), c_int(split_mode), _p(err),
+              c_void_p(stream if stream is not None else current_stream_ptr()))
+        return scratch[:M * N].view(M, N)
+    _check(out, "out")
     n_out = N // 2 if epilogue == EPI_SILU_MUL else N
     want = torch.bfloat16 if epilogue in (EPI_STORE, EPI_SILU_MUL) else torch.float32
     if out.dtype != want:

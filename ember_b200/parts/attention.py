@@ -139,6 +139,15 @@ class Attention(Mixer):
                             s.qk_norm_eps, cos_sin, self.inv_freq if rotates and T <= 16 else None, ctx.positions,
                             ctx.seq_of, table, cache.page_tokens, cache.k, cache.v, q, write_kv=owns_cache, err=ctx.err,
                             stream=ctx.stream)
+        elif (self.SUMS_TO_HEADS and 16 < T <= 128 and ops.gemm_tc_usable(x, self.qkv.weight, self.qkv.bias, ops.EPI_STORE)
+              and ops.qk_norm_rope_store_sums_usable(s.head_dim, self.rotary if rotates else 0, self.qkv.n)):
+            # 17 to 128 tokens: the product cuts K and adds its parts into a zeroed fp32 scratch; the head kernel
+            # reads the sums there (and clears them) instead of a bf16 copy that a pass of its own would have to make
+            sums = ops.gemm_tc(x, self.qkv.weight, None, T, ops.EPI_SUMS, err=ctx.err, stream=ctx.stream)
+            ops.qk_norm_rope_store_sums(sums, T, s.num_heads, s.num_kv_heads, self.q_norm_w, self.k_norm_w, s.qk_norm_eps,
+                                        self.inv_freq if rotates else None, ctx.positions, ctx.seq_of, table,
+                                        cache.page_tokens, cache.k, cache.v, q, write_kv=owns_cache, err=ctx.err,
+                                        stream=ctx.stream)
         else:
             self.qkv(ctx, x, qkv, T, ops.EPI_STORE)
             ops.qk_norm_rope_store(qkv, T, s.num_heads, s.num_kv_heads, s.head_dim, self.q_norm_w, self.k_norm_w,
@@ -149,6 +158,7 @@ class Attention(Mixer):
         self.o(ctx, att, residual, T, ops.EPI_ADD_F32)
 
     FUSE_QKV = True     # prompt portions: finish the heads in the epilogue of the q/k/v product
+    SUMS_TO_HEADS = True     # 17 to 128 tokens: the head kernel reads the product's fp32 sums (tests switch it off)
     CLUSTER_MERGE = True            # tests switch it off to compare with the merge kernel
     MERGE_KERNEL_US = 3.0           # what the merge kernel costs a decode step per layer beyond the attention kernel
     CACHE_BYTES_PER_US = 6.4e6      # the rate at which the decode kernel streams the cache when the SMs are full

@@ -535,6 +535,59 @@ def test_gemm_tc_qkv(heads, kv, page, M, norm, rotate):
     assert int(err.item()) == 2
 
 
+@pytest.mark.parametrize("heads,kv,page,M,K", [(16, 8, 64, 64, 2048), (4, 2, 16, 17, 328), (3, 1, 32, 128, 136), (40, 8, 16, 100, 512),
+                                               (32, 8, 64, 33, 4096)])
+@pytest.mark.parametrize("norm,rotate", [(True, True), (False, True), (True, False)])
+def test_qkv_sums_to_heads(heads, kv, page, M, K, norm, rotate):
+    """17 to 128 tokens: the q/k/v product leaves its fp32 sums in the scratch (K cut into parts added with atomics,
+    or one part stored), the head kernel reads them there, norms, rotates, writes queries and cache, and sets every
+    sum back to zero."""
+    from ember_b200 import ops
+    torch.manual_seed(heads * M + page + K)
+    dev, D = "cuda", 128
+    lens = [M - M // 3, M // 3]
+    starts = [5, 700]
+    pos = torch.cat([torch.arange(s, s + n) for s, n in zip(starts, lens)]).int().to(dev)
+    seq = torch.cat([torch.full((n,), i) for i, n in enumerate(lens)]).int().to(dev)
+    nblk = max((s + n + page - 1) // page for s, n in zip(starts, lens))
+    pages = 2 * nblk + 2
+    perm = torch.randperm(pages)[:2 * nblk].reshape(2, nblk).int().to(dev)
+    N = (heads + 2 * kv) * D
+    a = (torch.randn(M, K, device=dev) * 0.5).bfloat16()
+    w = (torch.randn(N, K, device=dev) * 0.1).bfloat16()
+    qw, kw = (1 + 0.1 * torch.randn(D, device=dev), 1 + 0.1 * torch.randn(D, device=dev)) if norm else (None, None)
+    inv = 1.0 / (10000.0 ** (torch.arange(D // 2, device=dev).float() * 2 / D))
+    x = a.float() @ w.float().t()
+    qq, kk, vv = x[:, :heads * D].view(M, heads, D), x[:, heads * D:(heads + kv) * D].view(M, kv, D), x[:, (heads + kv) * D:].view(M, kv, D)
+
+    def nrm(t, g):
+        return g * (t * torch.rsqrt((t.double() ** 2).mean(-1, keepdim=True) + 1e-5).float()) if norm else t
+
+    qq, kk = nrm(qq, qw), nrm(kk, kw)
+    if rotate:
+        qq, kk = rope_ref(qq, pos, inv, D), rope_ref(kk, pos, inv, D)
+    assert ops.qk_norm_rope_store_sums_usable(D, D if rotate else 0, N)
+    for write_kv in (True, False):
+        kp = torch.zeros(pages, kv, page, D, device=dev, dtype=torch.bfloat16)
+        vp = torch.zeros_like(kp)
+        q = torch.zeros(M, heads * D, device=dev, dtype=torch.bfloat16)
+        err = torch.zeros(1, dtype=torch.int32, device=dev)
+        sums = ops.gemm_tc(a, w, None, M, ops.EPI_SUMS, err=err)
+        assert rel(sums, x) < 1e-5                       # fp32 sums of the bf16 operands
+        ops.qk_norm_rope_store_sums(sums, M, heads, kv, qw, kw, 1e-5, inv if rotate else None, pos, seq, perm, page, kp, vp, q,
+                                    write_kv=write_kv, err=err)
+        assert int(err.item()) == 0
+        assert float(ops._tc_scratch[a.device].abs().max()) == 0.0        # every sum was set back to zero
+        assert rel(q.float().view(M, heads, D), qq) < 5e-3
+        if not write_kv:
+            assert float(kp.abs().max()) == 0.0 and float(vp.abs().max()) == 0.0
+            continue
+        blk = perm[seq.long(), (pos // page).long()].long()
+        slot = (pos % page).long()
+        assert rel(kp[blk, :, slot].float(), kk) < 5e-3
+        assert rel(vp[blk, :, slot].float(), vv) < 5e-3
+
+
 def test_bounded_wait_runs_out_and_returns():
     """The wait every TMA / tcgen05 kernel uses, on a barrier nobody arrives at, with a limit of one millisecond:
     the kernel returns, the error word holds the wait-limit bit, the wait lasted about the limit (not a poll
