@@ -178,3 +178,50 @@ def test_portions_with_and_without_the_fused_head_epilogue_agree(shape_dirs):
         results.append(got)
     for other in results[1:]:
         assert max(rel_err(other[i], results[0][i]) for i in range(len(rows))) <= TOL["bfloat16"]
+
+
+@pytest.mark.parametrize("n_requests", [24, 70])
+@pytest.mark.parametrize("name", ["1.7b", "8b"])
+def test_many_requests_decode_together_at_published_sizes(name, n_requests, shape_dirs):
+    """24 and 70 requests of different lengths decode side by side in bfloat16: steps of 17 to 128 tokens are the
+    ones where the q/k/v product leaves fp32 sums for the head kernel, the other products add their parts of K with
+    atomics, and the LM head (K in one part) turns its tile in shared memory.  Every request's rows against the
+    plain implementation, and the same request alone against itself in the crowd."""
+    from ember_b200 import StepEntry
+    from ember_b200.engine.runner import ModelRunner
+    model_dir, _, _ = shape_dirs(name)
+    rng = np.random.default_rng(5 + n_requests)
+    vocab = SHAPES[name]["vocab_size"]
+    lens = [int(x) for x in rng.integers(9, 80, size=n_requests)]
+    seqs = [rng.integers(0, vocab, size=n + 4).tolist() for n in lens]
+    plain = PlainQwen3(model_dir, torch.float32)
+    check = [0, 1, n_requests // 2, n_requests - 1]                  # requests whose rows are compared
+    want = {i: plain.logits(seqs[i]).numpy() for i in check}
+
+    def run(which):
+        r = ModelRunner.from_dir(model_dir, dtype="bfloat16", capacity_tokens=64 * (len(which) + 2) * 2, max_batch_tokens=2048,
+                                 max_requests=len(which), page_tokens=64)
+        for i in which:
+            assert r.admit(i) and r.reserve(i, lens[i])
+        for a in range(0, len(which), 20):                                      # the prompts, twenty requests a step
+            r.step([StepEntry(i, seqs[i][:lens[i]], ()) for i in which[a:a + 20]])
+        rows = {i: [] for i in which}
+        for t in range(4):
+            for i in which:
+                assert r.reserve(i, 1)
+            lg = r.step([StepEntry(i, [seqs[i][lens[i] + t]], (0,)) for i in which]).float().cpu().numpy()
+            for j, i in enumerate(which):
+                rows[i].append(lg[j].copy())
+        r.check_device()
+        return rows
+
+    crowd = run(list(range(n_requests)))
+    alone = run([check[2]])
+    rel = lambda a, b: float(np.linalg.norm(a - b) / np.linalg.norm(b))          # noqa: E731
+    worst = 0.0
+    for i in check:
+        for t in range(4):
+            worst = max(worst, rel(crowd[i][t], want[i][lens[i] + t]))
+    print(f"{name}, {n_requests} requests: worst relative error {worst:.3e}")
+    assert worst <= TOL["bfloat16"]
+    assert max(rel(crowd[check[2]][t], alone[check[2]][t]) for t in range(4)) <= TOL["bfloat16"]
